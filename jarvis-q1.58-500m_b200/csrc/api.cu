@@ -1,0 +1,151 @@
+// extern "C" surface of libjarvis_b200: argument plumbing only, the kernels live in the
+// other translation units.  Also owns the per-thread error message, the device status word
+// that bounded waits report into, and the bounded-wait self test.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "launchers.h"
+
+namespace jb {
+
+namespace {
+thread_local char g_err[512] = "";
+__device__ unsigned int g_status_word = 0;
+constexpr int MAX_DEVICES = 64;
+unsigned int* g_status_ptr[MAX_DEVICES] = {nullptr};
+int g_sm_count[MAX_DEVICES] = {0};
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+  return JB200_ERR_CUDA;
+}
+
+unsigned int* device_status_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    set_error("device_status_ptr: cudaGetDevice failed");
+    return nullptr;
+  }
+  if (!g_status_ptr[dev]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_status_word);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "cudaGetSymbolAddress(status word)");
+      return nullptr;
+    }
+    g_status_ptr[dev] = reinterpret_cast<unsigned int*>(p);
+  }
+  return g_status_ptr[dev];
+}
+
+int sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    set_error("sm_count: cudaGetDevice failed");
+    return -1;
+  }
+  if (!g_sm_count[dev]) {
+    int n = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+      cuda_fail(e, "cudaDeviceGetAttribute(SM count)");
+      return -1;
+    }
+    g_sm_count[dev] = n;
+  }
+  return g_sm_count[dev];
+}
+
+namespace {
+
+__global__ void selftest_wait_kernel(unsigned long long limit_ns, unsigned int* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+    // Nothing ever arrives on `bar`: the wait below must give up on its own.
+    const unsigned long long t0 = globaltimer_ns();
+    bool done = false;
+    for (uint32_t it = 0; !done; ++it) {
+      done = mbar_try_wait(smem_u32(&bar), 0u);
+      if (!done && (it & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) {
+        atomicCAS(status, 0u, JB200_STATUS_SELFTEST_WAIT);
+        break;
+      }
+    }
+  }
+}
+
+}  // namespace
+}  // namespace jb
+
+using namespace jb;
+
+extern "C" {
+
+const char* jb200_last_error(void) { return g_err; }
+
+int jb200_abi_version(void) { return 1; }
+
+int jb200_device_status(unsigned int* status, int clear) {
+  JB_REQUIRE(status != nullptr, "device_status: null output pointer");
+  unsigned int* p = device_status_ptr();
+  if (!p) return JB200_ERR_CUDA;
+  JB_CUDA(cudaDeviceSynchronize());
+  JB_CUDA(cudaMemcpy(status, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+  if (clear) JB_CUDA(cudaMemset(p, 0, sizeof(unsigned int)));
+  return JB200_OK;
+}
+
+int jb200_selftest_bounded_wait(int limit_ms, void* stream) {
+  JB_REQUIRE(limit_ms > 0 && limit_ms <= 2000, "selftest_bounded_wait: limit_ms (%d) must be in 1..2000", limit_ms);
+  unsigned int* p = device_status_ptr();
+  if (!p) return JB200_ERR_CUDA;
+  selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(1000000ull * (unsigned long long)limit_ms, p);
+  JB_LAUNCH_CHECK("selftest_wait_kernel");
+  return JB200_OK;
+}
+
+size_t jb200_pack_ternary_scratch_bytes(int out_features, int in_features) {
+  return pack_ternary_scratch_bytes(out_features, in_features);
+}
+
+int jb200_pack_ternary(const float* w, int out_features, int in_features, const float* alpha_in, uint8_t* packed,
+                       float* alpha_out, void* scratch, void* stream) {
+  return launch_pack_ternary(w, out_features, in_features, alpha_in, packed, alpha_out, scratch,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int jb200_pack_codes(const float* w_ternary, size_t n_elems, uint8_t* packed, void* stream) {
+  return launch_pack_codes(w_ternary, n_elems, packed, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, void* out, void* stream) {
+  return launch_unpack_ternary(packed, n_bytes, out_dtype, out, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
+                         int N, int epilogue, void* out, int token_tile, void* stream) {
+  return launch_ternary_gemm(x, M, K, packed, alpha, alpha_rows, N, 1, nullptr, epilogue, out, token_tile,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int N,
+                                 int G, const int32_t* seg_offsets, int epilogue, void* out, int token_tile,
+                                 void* stream) {
+  return launch_ternary_gemm(x, M, K, packed, alpha, N, N, G, seg_offsets, epilogue, out, token_tile,
+                             static_cast<cudaStream_t>(stream));
+}
+
+void jb200_host_decode16(uint32_t word, uint32_t* out8) { decode16_host(word, out8); }
+
+}  // extern "C"
