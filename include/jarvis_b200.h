@@ -107,6 +107,85 @@ int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* pac
                                  int G, const int32_t* seg_offsets, int epilogue, void* out, int token_tile,
                                  void* stream);
 
+/* ---- block glue --------------------------------------------------------------------- */
+
+/* RMSNorm.forward (jarvis_engine/jarvis_model.py:25-26): y = x * rsqrt(mean(x^2) + eps) * w.
+ * x: [n_rows][C] f32 (dtype 0) or bf16 (dtype 1); w: f32 [C]; y: f32 or bf16.  C % 8 == 0, C <= 4096. */
+int jb200_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* y, int y_dtype, int n_rows, int C,
+                  void* stream);
+
+/* Token embedding gather (nn.Embedding, jarvis_engine/jarvis_model.py:452, 498) into the f32
+ * residual stream.  idx: i64 [n_rows]; table: f32 [vocab][C]; out: f32 [n_rows][C]. */
+int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* out, int n_rows, int C, void* stream);
+
+/* ---- attention scan ----------------------------------------------------------------- */
+
+/* Feature map + RoPE + chunkwise decayed scan, with the carried state in and out.  Replaces
+ * fused_rope_elu_forward + the four bmm + recurrent_chunk_state_scan_forward of the CUDA drop-in
+ * (associative_attention_cuda/associative_attention_cpp.cpp:36-57, associative_attention.py:232-266)
+ * and the chunk loop of AssociativeLinearAttention.forward (jarvis_engine/jarvis_model.py:124-190).
+ * q, k, v: bf16 rows [B*T] with row stride ld_qkv elements, head h at columns [64h, 64h+64) (the raw
+ *   projection outputs: a fused q|k|v matrix is passed as three pointers into it);
+ * gamma: f32 [H] = sigmoid(gamma_raw);  cos_tab/sin_tab: f32 [n_pos][32] (first half of the RoPE cache);
+ * pos0: i32 [B] first position of each sequence, or NULL to use pos0_scalar for all (start_pos);
+ * s_in / s_out: f32 [B][H][64][64] (D_v x D_k, the layout of h_prev / h_last), each may be NULL;
+ * o: bf16 rows [B*T] with stride ld_o.  head_dim must be 64. */
+int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
+                    const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
+                    const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
+                    void* stream);
+
+/* ---- MoE routing ---------------------------------------------------------------------- */
+
+/* Eval-mode router of SparseMoELayer.forward (jarvis_engine/jarvis_model.py:218-224): logits in f32,
+ * softmax, top-2 (equal probabilities: lower expert id first), gates = p / (p0 + p1 + 1e-8).
+ * x: bf16 [N][C]; w_router: f32 [E][C] (E = 4 or 8, C % 256 == 0);
+ * topk_idx: i64 [N][2]; gates: f32 [N][2]; probs: f32 [N][E] or NULL;
+ * probs_sum: f64 [E] or NULL and top1_hist: i32 [E] or NULL are ACCUMULATED into (zero them first):
+ * the P and f of the load-balance loss (jarvis_model.py:244-247). */
+int jb200_router_top2(const void* x, const float* w_router, int N, int C, int E, int64_t* topk_idx, float* gates,
+                      float* probs, double* probs_sum, int32_t* top1_hist, void* stream);
+
+/* compute_metadata (sparse_model_cuda/sparse_model_cpp.cpp:83-90, kernel sparse_model.cu:23-90):
+ * stable partition of assignments m = token*K + k by expert.  All outputs i32:
+ * expert_counts [E], expert_offsets [E+1], scatter_map [N][K] (slot of m), gather_map [N*K]
+ * (token of slot), gate_idx_map [N*K] (k of slot).  scratch: jb200_moe_metadata_scratch_bytes. */
+size_t jb200_moe_metadata_scratch_bytes(int N, int K, int E);
+int jb200_moe_metadata(const int64_t* topk_idx, int N, int K, int E, int32_t* expert_counts,
+                       int32_t* expert_offsets, int32_t* scatter_map, int32_t* gather_map, int32_t* gate_idx_map,
+                       void* scratch, void* stream);
+
+/* dispatch_gather (sparse_model.cu:95-112): dispatched[slot][:] = x[gather_map[slot]][:], bf16 rows of C. */
+int jb200_moe_dispatch_gather(const void* x, const int32_t* gather_map, int M, int N, int C, void* dispatched,
+                              void* stream);
+
+/* scatter_combine (sparse_model.cu:117-165): out[i] = sum_k gates[i][k] * y[scatter_map[i][k]] with f32
+ * accumulation; y: bf16 [N*K][C]; out: f32 (0) or bf16 (1) [N][C].  stats: f64 [2] or NULL, ACCUMULATES
+ * sum(out) and sum(out^2) of the unrounded values (for act_mean / act_var, jarvis_model.py:249-250). */
+int jb200_moe_scatter_combine(const void* y, const float* gates, const int32_t* scatter_map, int N, int K, int C,
+                              void* out, int out_dtype, double* stats, void* stream);
+
+/* Side outputs of SparseMoELayer.forward (jarvis_model.py:244-250) from the accumulators above:
+ * scalars[0] = l_balance = balance_alpha * E * sum_e f_e * P_e, scalars[1] = act_mean,
+ * scalars[2] = act_var (unbiased).  Any accumulator may be NULL (its scalars are left untouched). */
+int jb200_moe_finalize(const double* stats, const double* probs_sum, const int32_t* top1_hist, int E,
+                       long long n_tokens, long long n_elems, float balance_alpha, float* scalars, void* stream);
+
+/* ---- Liquid State Fusion ---------------------------------------------------------------- */
+
+/* h_t = a*h_{t-1} + (1-a)*m_t along T for every (b, channel).
+ * Model semantics (LiquidStateFusion.forward, jarvis_engine/jarvis_model.py:281-314): alpha_tensor NULL;
+ *   the scalar decay is *alpha_scalar if given, else alpha_min + (alpha_max-alpha_min) *
+ *   sigmoid(-(*var_scale) * (*act_var)) -- all device scalars.
+ * Extension semantics (liquid_state_fusion_cuda.forward(alpha, M, h0),
+ *   liquid_fusion_cuda/liquid_state_fusion_cpp.cpp:67-74): alpha_tensor [B][T][D] in m's dtype.
+ * m: [B][T][D] f32 (0) or bf16 (1), D even;  h0: f32 [B][D] or NULL (zeros);
+ * out: [B][T][D] f32/bf16 or NULL;  resid: f32 [B][T][D] or NULL, updated in place resid += h (the
+ * block's residual add, jarvis_model.py:436);  h_last: f32 [B][D] or NULL. */
+int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
+                   const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
+                   float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, void* stream);
+
 /* Host-side copy of the bit manipulation the GEMM's decoder warps run: 16 two-bit codes
  * (one little-endian u32 of the packed layout) -> 16 bf16 values in out8[8] (two per u32,
  * lower in-feature in the low half).  Runs on the CPU; used by the unit tests. */

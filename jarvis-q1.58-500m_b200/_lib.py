@@ -33,6 +33,16 @@ PROTOTYPES = {
     "jb200_pack_codes": (_I, [_P, _Z, _P, _P]),
     "jb200_unpack_ternary": (_I, [_P, _Z, _I, _P, _P]),
     "jb200_ternary_linear": (_I, [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _P]),
+    "jb200_rmsnorm": (_I, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
+    "jb200_embedding": (_I, [_P, _P, _I, _P, _I, _I, _P]),
+    "jb200_attn_scan": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+    "jb200_router_top2": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "jb200_moe_metadata_scratch_bytes": (_Z, [_I, _I, _I]),
+    "jb200_moe_metadata": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "jb200_moe_dispatch_gather": (_I, [_P, _P, _I, _I, _I, _P, _P]),
+    "jb200_moe_scatter_combine": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, _P, _P]),
+    "jb200_moe_finalize": (_I, [_P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P]),
+    "jb200_lsf_scan": (_I, [_P, _I, _P, _P, _P, _P, _F, _F, _P, _P, _P, _I, _P, _I, _I, _I, _P]),
     "jb200_host_decode16": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
     "jb200_ternary_linear_grouped": (_I, [_P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P]),
 }

@@ -146,6 +146,62 @@ int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* pac
                              static_cast<cudaStream_t>(stream));
 }
 
+int jb200_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* y, int y_dtype, int n_rows, int C,
+                  void* stream) {
+  return launch_rmsnorm(x, x_dtype, w, eps, y, y_dtype, n_rows, C, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* out, int n_rows, int C, void* stream) {
+  return launch_embedding(idx, table, vocab, out, n_rows, C, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
+                    const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
+                    const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
+                    void* stream) {
+  return launch_attn_scan(q, k, v, ld_qkv, gamma, cos_tab, sin_tab, n_pos, pos0, pos0_scalar, s_in, o, ld_o, s_out, B,
+                          T, H, head_dim, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_router_top2(const void* x, const float* w_router, int N, int C, int E, int64_t* topk_idx, float* gates,
+                      float* probs, double* probs_sum, int32_t* top1_hist, void* stream) {
+  return launch_router_top2(x, w_router, N, C, E, topk_idx, gates, probs, probs_sum, top1_hist,
+                            static_cast<cudaStream_t>(stream));
+}
+
+size_t jb200_moe_metadata_scratch_bytes(int N, int K, int E) { return moe_metadata_scratch_bytes(N, K, E); }
+
+int jb200_moe_metadata(const int64_t* topk_idx, int N, int K, int E, int32_t* expert_counts,
+                       int32_t* expert_offsets, int32_t* scatter_map, int32_t* gather_map, int32_t* gate_idx_map,
+                       void* scratch, void* stream) {
+  return launch_moe_metadata(topk_idx, N, K, E, expert_counts, expert_offsets, scatter_map, gather_map, gate_idx_map,
+                             scratch, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_moe_dispatch_gather(const void* x, const int32_t* gather_map, int M, int N, int C, void* dispatched,
+                              void* stream) {
+  return launch_dispatch_gather(x, gather_map, M, N, C, dispatched, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_moe_scatter_combine(const void* y, const float* gates, const int32_t* scatter_map, int N, int K, int C,
+                              void* out, int out_dtype, double* stats, void* stream) {
+  return launch_scatter_combine(y, gates, scatter_map, N, K, C, out, out_dtype, stats,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int jb200_moe_finalize(const double* stats, const double* probs_sum, const int32_t* top1_hist, int E,
+                       long long n_tokens, long long n_elems, float balance_alpha, float* scalars, void* stream) {
+  return launch_moe_finalize(stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars,
+                             static_cast<cudaStream_t>(stream));
+}
+
+int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
+                   const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
+                   float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, void* stream) {
+  return launch_lsf_scan(m, m_dtype, alpha_tensor, alpha_scalar, act_var, var_scale, alpha_min, alpha_max, h0, resid,
+                         out, out_dtype, h_last, B, T, D, static_cast<cudaStream_t>(stream));
+}
+
 void jb200_host_decode16(uint32_t word, uint32_t* out8) { decode16_host(word, out8); }
 
 }  // extern "C"

@@ -18,4 +18,30 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
                         int bn_override, cudaStream_t stream);
 void decode16_host(uint32_t w, uint32_t* out8);
 
+int launch_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* y, int y_dtype, int n_rows, int C,
+                   cudaStream_t stream);
+int launch_embedding(const int64_t* idx, const float* table, int vocab, float* out, int n_rows, int C,
+                     cudaStream_t stream);
+
+int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, int C, int E, int64_t* topk_idx,
+                       float* gates, float* probs_out, double* probs_sum, int* top1_hist, cudaStream_t stream);
+size_t moe_metadata_scratch_bytes(int n_tokens, int K, int E);
+int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts, int* expert_offsets,
+                        int* scatter_map, int* gather_map, int* gate_idx_map, void* scratch, cudaStream_t stream);
+int launch_dispatch_gather(const void* x_bf16, const int* gather_map, int M, int n_tokens, int C, void* dispatched,
+                           cudaStream_t stream);
+int launch_scatter_combine(const void* y_bf16, const float* gates, const int* scatter_map, int n_tokens, int K, int C,
+                           void* out, int out_dtype, double* stats, cudaStream_t stream);
+int launch_moe_finalize(const double* stats, const double* probs_sum, const int* top1_hist, int E, long long n_tokens,
+                        long long n_elems, float balance_alpha, float* scalars, cudaStream_t stream);
+
+int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
+                    const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
+                    float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, cudaStream_t stream);
+
+int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
+                     const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
+                     const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
+                     cudaStream_t stream);
+
 }  // namespace jb

@@ -1,0 +1,373 @@
+// Top-2 MoE routing and token movement.
+//
+//   router      softmax(x W_r^T) -> top-2 ids + renormalised gates           jarvis_model.py:218-224
+//   metadata    stable partition of assignments m = token*K + k by expert    sparse_model.cu:23-90 (M1)
+//   gather      dispatched_x[slot] = x[gather_map[slot]]                     sparse_model.cu:95-112 (M2)
+//   combine     out[i] = sum_k gate[i,k] * y[scatter_map[i,k]]  (+ sum, sum^2 of out)
+//                                                                            sparse_model.cu:117-165 (M3),
+//                                                                            jarvis_model.py:249-250
+//   finalize    l_balance, act_mean, act_var                                 jarvis_model.py:244-250
+//
+// The reference builds the dispatch order with ONE thread walking all N*K assignments; here it
+// is a parallel stable counting sort: per-chunk histograms, a scan over (chunk, expert), and a
+// ballot-ranked scatter.  The order is a pure function of the ids and is bit-exact.
+// All of it is HBM/latency-bound integer and copy work: no tensor cores.
+#include "common.cuh"
+#include "launchers.h"
+
+namespace jb {
+
+namespace {
+
+constexpr int MAX_E = 16;
+constexpr int ROUTER_THREADS = 256;                 // 8 warps, one token per warp at a time
+constexpr int ROUTER_TOKENS_PER_CTA = 64;
+constexpr int META_CHUNK = 256;                     // assignments per CTA of the metadata kernels
+
+// ---------------------------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------------------------
+template <int E>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w_router, int n_tokens, int C,
+                   int64_t* __restrict__ topk_idx, float* __restrict__ gates, float* __restrict__ probs_out,
+                   double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
+  extern __shared__ float w_s[];  // [E][C]
+  __shared__ float p_acc[ROUTER_THREADS / 32][E];
+  __shared__ int h_acc[E];
+  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[i] = __ldg(w_router + i);
+  if (threadIdx.x < E) h_acc[threadIdx.x] = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float p_local[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) p_local[e] = 0.f;
+  const int tok0 = blockIdx.x * ROUTER_TOKENS_PER_CTA;
+  for (int tt = warp; tt < ROUTER_TOKENS_PER_CTA; tt += ROUTER_THREADS / 32) {
+    const int tok = tok0 + tt;
+    if (tok >= n_tokens) break;
+    const __nv_bfloat16* xr = x + size_t(tok) * C;
+    float acc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + c));
+      const float xv[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
+                           bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float4 wa = *reinterpret_cast<const float4*>(w_s + e * C + c);
+        const float4 wb = *reinterpret_cast<const float4*>(w_s + e * C + c + 4);
+        acc[e] += xv[0] * wa.x + xv[1] * wa.y + xv[2] * wa.z + xv[3] * wa.w + xv[4] * wb.x + xv[5] * wb.y +
+                  xv[6] * wb.z + xv[7] * wb.w;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = warp_sum(acc[e]);
+    // softmax, then top-2 with ties going to the lower expert id (every lane computes the same)
+    float mx = acc[0];
+#pragma unroll
+    for (int e = 1; e < E; ++e) mx = fmaxf(mx, acc[e]);
+    float p[E], den = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) { p[e] = expf(acc[e] - mx); den += p[e]; }
+    const float inv = 1.0f / den;
+    int i0 = 0, i1 = -1;
+    float p0 = -1.f, p1 = -1.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      p[e] *= inv;
+      if (p[e] > p0) { p1 = p0; i1 = i0; p0 = p[e]; i0 = e; }
+      else if (p[e] > p1) { p1 = p[e]; i1 = e; }
+    }
+    if (lane == 0) {
+      topk_idx[size_t(tok) * 2 + 0] = i0;
+      topk_idx[size_t(tok) * 2 + 1] = i1;
+      const float g = p0 + p1 + 1e-8f;
+      gates[size_t(tok) * 2 + 0] = p0 / g;
+      gates[size_t(tok) * 2 + 1] = p1 / g;
+      if (probs_out) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) probs_out[size_t(tok) * E + e] = p[e];
+      }
+      atomicAdd(&h_acc[i0], 1);
+#pragma unroll
+      for (int e = 0; e < E; ++e) p_local[e] += p[e];
+    }
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) p_acc[warp][e] = p_local[e];
+  }
+  __syncthreads();
+  if (threadIdx.x < E) {
+    float s = 0.f;
+    for (int w = 0; w < ROUTER_THREADS / 32; ++w) s += p_acc[w][threadIdx.x];
+    if (probs_sum) atomicAdd(&probs_sum[threadIdx.x], double(s));
+    if (top1_hist && h_acc[threadIdx.x]) atomicAdd(&top1_hist[threadIdx.x], h_acc[threadIdx.x]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// dispatch metadata: stable counting sort of M = N*K assignments by expert id
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ int clamp_expert(long long e, int E) { return e < 0 ? 0 : (e >= E ? E - 1 : int(e)); }
+
+__global__ void __launch_bounds__(META_CHUNK)
+meta_hist_kernel(const int64_t* __restrict__ flat_idx, int M, int E, int* __restrict__ chunk_counts) {
+  __shared__ int h[MAX_E];
+  if (threadIdx.x < MAX_E) h[threadIdx.x] = 0;
+  __syncthreads();
+  const int m = blockIdx.x * META_CHUNK + threadIdx.x;
+  if (m < M) atomicAdd(&h[clamp_expert(flat_idx[m], E)], 1);
+  __syncthreads();
+  if (threadIdx.x < E) chunk_counts[blockIdx.x * E + threadIdx.x] = h[threadIdx.x];
+}
+
+// One CTA, one warp per expert: exclusive scan of the per-chunk counts of that expert, then the
+// expert offsets.  chunk_base[c][e] = offsets[e] + sum_{c' < c} counts[c'][e].
+__global__ void __launch_bounds__(32 * MAX_E)
+meta_scan_kernel(const int* __restrict__ chunk_counts, int n_chunks, int E, int* __restrict__ chunk_base,
+                 int* __restrict__ expert_counts, int* __restrict__ expert_offsets) {
+  __shared__ int totals[MAX_E];
+  __shared__ int offs[MAX_E + 1];
+  const int e = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (e < E) {
+    int running = 0;
+    for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+      const int c = c0 + lane;
+      const int v = c < n_chunks ? chunk_counts[c * E + e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      if (c < n_chunks) chunk_base[c * E + e] = running + incl - v;  // offsets[e] added below
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) totals[e] = running;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < E; ++i) { offs[i] = acc; acc += totals[i]; }
+    offs[E] = acc;
+    for (int i = 0; i < E; ++i) { expert_counts[i] = totals[i]; expert_offsets[i] = offs[i]; }
+    expert_offsets[E] = acc;
+  }
+  __syncthreads();
+  if (e < E) {
+    const int add = offs[e];
+    for (int c = lane; c < n_chunks; c += 32) chunk_base[c * E + e] += add;
+  }
+}
+
+__global__ void __launch_bounds__(META_CHUNK)
+meta_assign_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, const int* __restrict__ chunk_base,
+                   int* __restrict__ scatter_map, int* __restrict__ gather_map, int* __restrict__ gate_idx_map) {
+  __shared__ int warp_cnt[META_CHUNK / 32][MAX_E];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * META_CHUNK + threadIdx.x;
+  const int e = m < M ? clamp_expert(flat_idx[m], E) : -1;
+  int rank = 0;  // assignments of the same expert earlier in this warp
+  for (int q = 0; q < E; ++q) {
+    const unsigned mask = __ballot_sync(0xffffffffu, e == q);
+    if (e == q) rank = __popc(mask & ((1u << lane) - 1u));
+    if (lane == 0) warp_cnt[warp][q] = __popc(mask);
+  }
+  __syncthreads();
+  if (m < M) {
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+    const int slot = chunk_base[blockIdx.x * E + e] + before + rank;
+    scatter_map[m] = slot;
+    gather_map[slot] = m / K;
+    gate_idx_map[slot] = m % K;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// gather / combine
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+dispatch_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ gather_map, int M, int n_tokens,
+                       int C, __nv_bfloat16* __restrict__ dispatched) {
+  const int slot = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (slot >= M) return;
+  const int lane = threadIdx.x & 31;
+  int tok = gather_map[slot];
+  tok = tok < 0 ? 0 : (tok >= n_tokens ? n_tokens - 1 : tok);
+  const uint4* src = reinterpret_cast<const uint4*>(x + size_t(tok) * C);
+  uint4* dst = reinterpret_cast<uint4*>(dispatched + size_t(slot) * C);
+  for (int c = lane; c < C / 8; c += 32) dst[c] = __ldg(src + c);
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+scatter_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ gates,
+                       const int* __restrict__ scatter_map, int n_tokens, int K, int M, int C,
+                       TOut* __restrict__ out, double* __restrict__ stats) {
+  __shared__ float red[2][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok = blockIdx.x * 8 + warp;
+  float s1 = 0.f, s2 = 0.f;
+  if (tok < n_tokens) {
+    for (int c = lane * 8; c < C; c += 256) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < K; ++k) {
+        int slot = scatter_map[size_t(tok) * K + k];
+        slot = slot < 0 ? 0 : (slot >= M ? M - 1 : slot);
+        const float g = gates[size_t(tok) * K + k];
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + size_t(slot) * C + c));
+        acc[0] += g * bf16_lo(v.x); acc[1] += g * bf16_hi(v.x); acc[2] += g * bf16_lo(v.y); acc[3] += g * bf16_hi(v.y);
+        acc[4] += g * bf16_lo(v.z); acc[5] += g * bf16_hi(v.z); acc[6] += g * bf16_lo(v.w); acc[7] += g * bf16_hi(v.w);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { s1 += acc[j]; s2 += acc[j] * acc[j]; }
+      if constexpr (sizeof(TOut) == 2) {
+        *reinterpret_cast<uint4*>(out + size_t(tok) * C + c) =
+            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      } else {
+        float4* o = reinterpret_cast<float4*>(out + size_t(tok) * C + c);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+    }
+  }
+  if (stats) {
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if (lane == 0) { red[0][warp] = s1; red[1][warp] = s2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double a = 0.0, b = 0.0;
+      for (int w = 0; w < 8; ++w) { a += double(red[0][w]); b += double(red[1][w]); }
+      atomicAdd(&stats[0], a);
+      atomicAdd(&stats[1], b);
+    }
+  }
+}
+
+// scalars[0] = l_balance, [1] = act_mean, [2] = act_var (unbiased), all f32.
+__global__ void moe_finalize_kernel(const double* __restrict__ stats, const double* __restrict__ probs_sum,
+                                    const int* __restrict__ top1_hist, int E, long long n_tokens, long long n_elems,
+                                    float balance_alpha, float* __restrict__ scalars) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (probs_sum && top1_hist) {
+    double acc = 0.0;
+    for (int e = 0; e < E; ++e)
+      acc += (double(top1_hist[e]) / double(n_tokens)) * (probs_sum[e] / double(n_tokens));
+    scalars[0] = float(double(balance_alpha) * double(E) * acc);
+  }
+  if (stats) {
+    const double mean = stats[0] / double(n_elems);
+    // torch.var of a single element is NaN; keep that
+    const double var = (stats[1] - stats[0] * mean) / double(n_elems - 1);
+    scalars[1] = float(mean);
+    scalars[2] = n_elems > 1 ? float(var > 0.0 ? var : 0.0) : __int_as_float(0x7fc00000);
+  }
+}
+
+}  // namespace
+
+int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, int C, int E, int64_t* topk_idx,
+                       float* gates, float* probs_out, double* probs_sum, int* top1_hist, cudaStream_t stream) {
+  JB_REQUIRE(n_tokens >= 0 && C > 0, "router_top2: bad shape");
+  JB_REQUIRE(E == 4 || E == 8, "router_top2: num_experts (%d) must be 4 or 8", E);
+  JB_REQUIRE(C % 256 == 0 && size_t(E) * C * 4 <= 160 * 1024, "router_top2: d_model (%d) must be a multiple of 256", C);
+  JB_REQUIRE(x_bf16 && w_router && topk_idx && gates, "router_top2: null pointer");
+  JB_REQUIRE(aligned16(x_bf16) && aligned16(w_router), "router_top2: pointers must be 16-byte aligned");
+  if (n_tokens == 0) return JB200_OK;
+  const int blocks = (n_tokens + ROUTER_TOKENS_PER_CTA - 1) / ROUTER_TOKENS_PER_CTA;
+  const size_t smem = size_t(E) * C * sizeof(float);
+  if (E == 4) {
+    JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    router_top2_kernel<4><<<blocks, ROUTER_THREADS, smem, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, topk_idx, gates, probs_out, probs_sum,
+        top1_hist);
+  } else {
+    JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    router_top2_kernel<8><<<blocks, ROUTER_THREADS, smem, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, topk_idx, gates, probs_out, probs_sum,
+        top1_hist);
+  }
+  JB_LAUNCH_CHECK("router_top2_kernel");
+  return JB200_OK;
+}
+
+size_t moe_metadata_scratch_bytes(int n_tokens, int K, int E) {
+  if (n_tokens <= 0 || K <= 0 || E <= 0) return 0;
+  const size_t chunks = (size_t(n_tokens) * K + META_CHUNK - 1) / META_CHUNK;
+  return 2 * chunks * size_t(E) * sizeof(int);
+}
+
+int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts, int* expert_offsets,
+                        int* scatter_map, int* gather_map, int* gate_idx_map, void* scratch, cudaStream_t stream) {
+  JB_REQUIRE(n_tokens >= 0 && K >= 1 && K <= 8, "moe_metadata: bad shape (N=%d, K=%d)", n_tokens, K);
+  JB_REQUIRE(E >= 1 && E <= MAX_E, "moe_metadata: num_experts (%d) must be in 1..%d", E, MAX_E);
+  JB_REQUIRE(size_t(n_tokens) * K < (size_t(1) << 31), "moe_metadata: too many assignments");
+  JB_REQUIRE(expert_counts && expert_offsets, "moe_metadata: null pointer");
+  const int M = n_tokens * K;
+  const int chunks = (M + META_CHUNK - 1) / META_CHUNK;
+  JB_REQUIRE(M == 0 || (topk_idx && scatter_map && gather_map && gate_idx_map && scratch), "moe_metadata: null pointer");
+  int* chunk_counts = reinterpret_cast<int*>(scratch);
+  int* chunk_base = chunk_counts + size_t(chunks) * E;
+  if (M > 0) {
+    meta_hist_kernel<<<chunks, META_CHUNK, 0, stream>>>(topk_idx, M, E, chunk_counts);
+    JB_LAUNCH_CHECK("meta_hist_kernel");
+  }
+  meta_scan_kernel<<<1, 32 * MAX_E, 0, stream>>>(chunk_counts, chunks, E, chunk_base, expert_counts, expert_offsets);
+  JB_LAUNCH_CHECK("meta_scan_kernel");
+  if (M > 0) {
+    meta_assign_kernel<<<chunks, META_CHUNK, 0, stream>>>(topk_idx, M, K, E, chunk_base, scatter_map, gather_map,
+                                                          gate_idx_map);
+    JB_LAUNCH_CHECK("meta_assign_kernel");
+  }
+  return JB200_OK;
+}
+
+int launch_dispatch_gather(const void* x_bf16, const int* gather_map, int M, int n_tokens, int C, void* dispatched,
+                           cudaStream_t stream) {
+  JB_REQUIRE(M >= 0 && n_tokens >= 0 && C > 0 && C % 8 == 0, "dispatch_gather: bad shape");
+  if (M == 0) return JB200_OK;
+  JB_REQUIRE(n_tokens > 0 && x_bf16 && gather_map && dispatched, "dispatch_gather: null pointer");
+  JB_REQUIRE(aligned16(x_bf16) && aligned16(dispatched), "dispatch_gather: pointers must be 16-byte aligned");
+  dispatch_gather_kernel<<<(M + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16), gather_map, M,
+                                                          n_tokens, C, reinterpret_cast<__nv_bfloat16*>(dispatched));
+  JB_LAUNCH_CHECK("dispatch_gather_kernel");
+  return JB200_OK;
+}
+
+int launch_scatter_combine(const void* y_bf16, const float* gates, const int* scatter_map, int n_tokens, int K, int C,
+                           void* out, int out_dtype, double* stats, cudaStream_t stream) {
+  JB_REQUIRE(n_tokens >= 0 && K >= 1 && K <= 8 && C > 0 && C % 8 == 0, "scatter_combine: bad shape");
+  JB_REQUIRE(out_dtype == 0 || out_dtype == 1, "scatter_combine: out_dtype must be 0 (f32) or 1 (bf16)");
+  if (n_tokens == 0) return JB200_OK;
+  JB_REQUIRE(y_bf16 && gates && scatter_map && out, "scatter_combine: null pointer");
+  JB_REQUIRE(aligned16(y_bf16) && aligned16(out), "scatter_combine: pointers must be 16-byte aligned");
+  const int blocks = (n_tokens + 7) / 8;
+  const int M = n_tokens * K;
+  if (out_dtype == 1)
+    scatter_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(y_bf16), gates, scatter_map, n_tokens, K, M, C,
+        reinterpret_cast<__nv_bfloat16*>(out), stats);
+  else
+    scatter_combine_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(y_bf16), gates,
+                                                              scatter_map, n_tokens, K, M, C,
+                                                              reinterpret_cast<float*>(out), stats);
+  JB_LAUNCH_CHECK("scatter_combine_kernel");
+  return JB200_OK;
+}
+
+int launch_moe_finalize(const double* stats, const double* probs_sum, const int* top1_hist, int E, long long n_tokens,
+                        long long n_elems, float balance_alpha, float* scalars, cudaStream_t stream) {
+  JB_REQUIRE(scalars != nullptr, "moe_finalize: null output");
+  JB_REQUIRE(n_tokens > 0 && n_elems > 0, "moe_finalize: empty batch");
+  moe_finalize_kernel<<<1, 32, 0, stream>>>(stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars);
+  JB_LAUNCH_CHECK("moe_finalize_kernel");
+  return JB200_OK;
+}
+
+}  // namespace jb

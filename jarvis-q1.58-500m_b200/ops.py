@@ -146,3 +146,178 @@ def selftest_bounded_wait(limit_ms: int = 50) -> int:
     _lib.device_status(clear=True)
     _lib.check(lib.jb200_selftest_bounded_wait(limit_ms, _stream()), "jb200_selftest_bounded_wait")
     return _lib.device_status(clear=True)
+
+
+# --------------------------------------------------------------------------- glue
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise RuntimeError(f"expected float32 or bfloat16, got {t.dtype}")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """RMSNorm.forward (jarvis_engine/jarvis_model.py:25-26) over the last axis."""
+    lib = _lib.load()
+    if not (x.is_cuda and x.is_contiguous()):
+        raise RuntimeError("rmsnorm: expected a contiguous CUDA tensor")
+    _need(weight, torch.float32, "rmsnorm.weight")
+    C = x.shape[-1]
+    y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _lib.check(lib.jb200_rmsnorm(_ptr(x), _dt(x), _ptr(weight), eps, _ptr(y), _dt(y), x.numel() // C, C, _stream()),
+               "jb200_rmsnorm")
+    return y
+
+
+def embedding(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """tok_emb gather into the f32 residual stream (jarvis_engine/jarvis_model.py:498)."""
+    lib = _lib.load()
+    _need(idx, torch.int64, "embedding.idx")
+    _need(table, torch.float32, "embedding.table")
+    out = torch.empty((*idx.shape, table.shape[1]), dtype=torch.float32, device=idx.device)
+    _lib.check(lib.jb200_embedding(_ptr(idx), _ptr(table), table.shape[0], _ptr(out), idx.numel(), table.shape[1],
+                                   _stream()), "jb200_embedding")
+    return out
+
+
+# --------------------------------------------------------------------------- attention scan
+def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, cos_tab: torch.Tensor,
+              sin_tab: torch.Tensor, B: int, T: int, H: int, *, start_pos=0, state_in: torch.Tensor | None = None,
+              want_state: bool = False, out: torch.Tensor | None = None):
+    """Feature map + RoPE + decayed causal scan.  q, k, v: bf16 2-D views (B*T, H*64) sharing one
+    row stride (e.g. column slices of a fused q|k|v matrix).  start_pos: int, or int32 (B,) tensor of
+    per-sequence first positions.  Returns (o bf16 (B*T, H*64), final state f32 (B,H,64,64) or None)."""
+    lib = _lib.load()
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1):
+            raise RuntimeError(f"attn_scan.{name}: expected a 2-D bf16 CUDA tensor with unit inner stride")
+    ld = q.stride(0)
+    if k.stride(0) != ld or v.stride(0) != ld or tuple(q.shape) != (B * T, H * 64):
+        raise RuntimeError("attn_scan: q, k, v must share shape (B*T, H*64) and row stride")
+    _need(gamma, torch.float32, "attn_scan.gamma")
+    _need(cos_tab, torch.float32, "attn_scan.cos_tab")
+    _need(sin_tab, torch.float32, "attn_scan.sin_tab")
+    if cos_tab.shape[1] != 32 or sin_tab.shape != cos_tab.shape:
+        raise RuntimeError("attn_scan: RoPE tables must be (n_pos, 32)")
+    pos_t, pos_s = None, 0
+    if torch.is_tensor(start_pos):
+        pos_t = _need(start_pos, torch.int32, "attn_scan.start_pos")
+    else:
+        pos_s = int(start_pos)
+    if state_in is not None:
+        _need(state_in, torch.float32, "attn_scan.state_in")
+        if tuple(state_in.shape) != (B, H, 64, 64):
+            raise RuntimeError("attn_scan: state_in must be (B, H, 64, 64)")
+    if out is None:
+        out = torch.empty((B * T, H * 64), dtype=torch.bfloat16, device=q.device)
+    s_out = torch.empty((B, H, 64, 64), dtype=torch.float32, device=q.device) if want_state else None
+    _lib.check(
+        lib.jb200_attn_scan(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(gamma), _ptr(cos_tab), _ptr(sin_tab), cos_tab.shape[0],
+                            _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0), _ptr(s_out), B, T, H, 64,
+                            _stream()),
+        "jb200_attn_scan",
+    )
+    return out, s_out
+
+
+# --------------------------------------------------------------------------- MoE routing
+def router_top2(x: torch.Tensor, w_router: torch.Tensor, *, want_probs: bool = False, probs_sum=None, top1_hist=None):
+    """Returns (topk_idx int64 (N, 2), gates f32 (N, 2), probs f32 (N, E) or None)."""
+    lib = _lib.load()
+    _need(x, torch.bfloat16, "router_top2.x")
+    _need(w_router, torch.float32, "router_top2.w_router")
+    N, C = x.shape
+    E = w_router.shape[0]
+    idx = torch.empty((N, 2), dtype=torch.int64, device=x.device)
+    gates = torch.empty((N, 2), dtype=torch.float32, device=x.device)
+    probs = torch.empty((N, E), dtype=torch.float32, device=x.device) if want_probs else None
+    _lib.check(lib.jb200_router_top2(_ptr(x), _ptr(w_router), N, C, E, _ptr(idx), _ptr(gates), _ptr(probs),
+                                     _ptr(probs_sum), _ptr(top1_hist), _stream()), "jb200_router_top2")
+    return idx, gates, probs
+
+
+def moe_metadata(topk_idx: torch.Tensor, num_experts: int):
+    """compute_metadata(topk_idx, E) -> (counts, offsets, scatter_map, gather_map, gate_idx_map), int32."""
+    lib = _lib.load()
+    _need(topk_idx, torch.int64, "moe_metadata.topk_idx")
+    N, K = topk_idx.shape
+    dev = topk_idx.device
+    i32 = torch.int32
+    counts = torch.empty((num_experts,), dtype=i32, device=dev)
+    offsets = torch.empty((num_experts + 1,), dtype=i32, device=dev)
+    scatter = torch.empty((N, K), dtype=i32, device=dev)
+    gather = torch.empty((N * K,), dtype=i32, device=dev)
+    gate_idx = torch.empty((N * K,), dtype=i32, device=dev)
+    nbytes = lib.jb200_moe_metadata_scratch_bytes(N, K, num_experts)
+    scratch = torch.empty((max(nbytes, 4) // 4,), dtype=i32, device=dev)
+    _lib.check(lib.jb200_moe_metadata(_ptr(topk_idx), N, K, num_experts, _ptr(counts), _ptr(offsets), _ptr(scatter),
+                                      _ptr(gather), _ptr(gate_idx), _ptr(scratch), _stream()), "jb200_moe_metadata")
+    return counts, offsets, scatter, gather, gate_idx
+
+
+def dispatch_gather(x: torch.Tensor, gather_map: torch.Tensor) -> torch.Tensor:
+    lib = _lib.load()
+    _need(x, torch.bfloat16, "dispatch_gather.x")
+    _need(gather_map, torch.int32, "dispatch_gather.gather_map")
+    N, C = x.shape
+    M = gather_map.numel()
+    out = torch.empty((M, C), dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.jb200_moe_dispatch_gather(_ptr(x), _ptr(gather_map), M, N, C, _ptr(out), _stream()),
+               "jb200_moe_dispatch_gather")
+    return out
+
+
+def scatter_combine(y: torch.Tensor, gates: torch.Tensor, scatter_map: torch.Tensor, *, out_dtype=torch.bfloat16,
+                    stats: torch.Tensor | None = None) -> torch.Tensor:
+    lib = _lib.load()
+    _need(y, torch.bfloat16, "scatter_combine.y")
+    _need(gates, torch.float32, "scatter_combine.gates")
+    _need(scatter_map, torch.int32, "scatter_combine.scatter_map")
+    N, K = scatter_map.shape
+    C = y.shape[1]
+    out = torch.empty((N, C), dtype=out_dtype, device=y.device)
+    if stats is not None:
+        _need(stats, torch.float64, "scatter_combine.stats")
+    _lib.check(lib.jb200_moe_scatter_combine(_ptr(y), _ptr(gates), _ptr(scatter_map), N, K, C, _ptr(out), _dt(out),
+                                             _ptr(stats), _stream()), "jb200_moe_scatter_combine")
+    return out
+
+
+def moe_finalize(stats, probs_sum, top1_hist, E: int, n_tokens: int, n_elems: int, balance_alpha: float,
+                 scalars: torch.Tensor | None = None) -> torch.Tensor:
+    """-> f32 (3,) = [l_balance, act_mean, act_var]."""
+    lib = _lib.load()
+    ref = stats if stats is not None else probs_sum
+    if scalars is None:
+        scalars = torch.zeros((3,), dtype=torch.float32, device=ref.device)
+    _lib.check(lib.jb200_moe_finalize(_ptr(stats), _ptr(probs_sum), _ptr(top1_hist), E, n_tokens, n_elems,
+                                      balance_alpha, _ptr(scalars), _stream()), "jb200_moe_finalize")
+    return scalars
+
+
+# --------------------------------------------------------------------------- LSF
+def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=None, var_scale=None,
+             alpha_min: float = 0.1, alpha_max: float = 0.99, h0=None, resid=None, want_out: bool = True,
+             out_dtype=None, want_last: bool = True):
+    """m: (B, T, D) f32/bf16.  Returns (h_out or None, h_last f32 (B, D) or None)."""
+    lib = _lib.load()
+    if not (m.is_cuda and m.is_contiguous() and m.dim() == 3):
+        raise RuntimeError("lsf_scan: expected a contiguous (B, T, D) CUDA tensor")
+    B, T, D = m.shape
+    if alpha_tensor is not None:
+        if alpha_tensor.dtype != m.dtype or tuple(alpha_tensor.shape) != (B, T, D) or not alpha_tensor.is_contiguous():
+            raise RuntimeError("lsf_scan: alpha tensor must match m in shape, dtype and layout")
+    for name, t in (("alpha_scalar", alpha_scalar), ("act_var", act_var), ("var_scale", var_scale), ("h0", h0),
+                    ("resid", resid)):
+        if t is not None:
+            _need(t, torch.float32, "lsf_scan." + name)
+    out = torch.empty((B, T, D), dtype=out_dtype or m.dtype, device=m.device) if want_out else None
+    h_last = torch.empty((B, D), dtype=torch.float32, device=m.device) if want_last else None
+    _lib.check(
+        lib.jb200_lsf_scan(_ptr(m), _dt(m), _ptr(alpha_tensor), _ptr(alpha_scalar), _ptr(act_var), _ptr(var_scale),
+                           alpha_min, alpha_max, _ptr(h0), _ptr(resid), _ptr(out), _dt(out) if out is not None else 0,
+                           _ptr(h_last), B, T, D, _stream()),
+        "jb200_lsf_scan",
+    )
+    return out, h_last

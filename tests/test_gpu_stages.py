@@ -1,0 +1,299 @@
+"""GPU parity of the non-GEMM stages against the CPU oracle and the reference-generated golden
+fixtures: attention scan (+ carried state), router, dispatch order, gather/combine, LSF, RMSNorm.
+Integer / index results must be bit-exact; floating-point results are compared with
+rel-L2 <= 1e-2 against the fp32 oracle (bf16 compute), tighter where the kernel runs in fp32."""
+import pytest
+import torch
+
+import jarvis_b200  # noqa: F401
+from jarvis_b200 import _lib, ops
+from oracle import jarvis_oracle as orc
+from tests.golden.loader import load
+
+pytestmark = pytest.mark.gpu
+TOL_BF16 = 1e-2
+
+
+def rel_l2(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def rope_tabs(n_pos):
+    cos, sin = orc.rope_tables(n_pos, 64)
+    return cos[:, :32].contiguous().cuda(), sin[:, :32].contiguous().cuda()
+
+
+# ------------------------------------------------------------------ rmsnorm / embedding
+@pytest.mark.parametrize("C", [128, 1024, 2048])
+def test_rmsnorm(C):
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(37, C, generator=g)
+    w = torch.rand(C, generator=g) + 0.5
+    ref = orc.rmsnorm(x, w)
+    assert rel_l2(ops.rmsnorm(x.cuda(), w.cuda(), out_dtype=torch.float32), ref) < 1e-6
+    assert rel_l2(ops.rmsnorm(x.cuda(), w.cuda()).float(), ref) < 4e-3
+    xb = x.bfloat16()
+    assert rel_l2(ops.rmsnorm(xb.cuda(), w.cuda(), out_dtype=torch.float32), orc.rmsnorm(xb.float(), w)) < 1e-6
+
+
+def test_embedding():
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(1000, 128, generator=g)
+    idx = torch.randint(0, 1000, (3, 50), generator=g)
+    assert torch.equal(ops.embedding(idx.cuda(), table.cuda()).cpu(), table[idx])
+
+
+# ------------------------------------------------------------------ attention scan
+def _scan_case(B, H, T, seed, start_pos=0, with_state=False, gammas=None):
+    g = torch.Generator().manual_seed(seed)
+    q, k, v = (torch.randn(B, T, H * 64, generator=g).bfloat16() for _ in range(3))
+    gamma = torch.rand(H, generator=g) * 0.099 + 0.9 if gammas is None else torch.tensor(gammas)
+    S0 = torch.randn(B, H, 64, 64, generator=g) if with_state else None
+
+    def heads(t):
+        return t.float().view(B, T, H, 64).transpose(1, 2)
+
+    per_seq = torch.is_tensor(start_pos)
+    o_ref = torch.empty(B, H, T, 64, dtype=torch.float64)
+    S_ref = torch.empty(B, H, 64, 64, dtype=torch.float64)
+    for b in range(B):
+        sp = int(start_pos[b]) if per_seq else start_pos
+        qf, kf = orc.feature_map_rope(heads(q)[b:b + 1], heads(k)[b:b + 1], sp)
+        o_ref[b:b + 1], S_ref[b:b + 1] = orc.attn_scan_recurrent(qf, kf, heads(v)[b:b + 1], gamma,
+                                                                 None if S0 is None else S0[b:b + 1])
+    n_pos = (int(start_pos.max()) if per_seq else start_pos) + T
+    cos, sin = rope_tabs(n_pos)
+    qkv = torch.cat((q, k, v), dim=-1).reshape(B * T, 3 * H * 64).cuda()   # fused projection layout
+    o, S = ops.attn_scan(qkv[:, :H * 64], qkv[:, H * 64:2 * H * 64], qkv[:, 2 * H * 64:], gamma.cuda(), cos, sin,
+                         B, T, H, start_pos=start_pos.cuda() if per_seq else start_pos,
+                         state_in=None if S0 is None else S0.cuda(), want_state=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    o = o.float().cpu().view(B, T, H, 64).transpose(1, 2)
+    return rel_l2(o, o_ref), rel_l2(S, S_ref)
+
+
+@pytest.mark.parametrize("T", [1, 17, 63, 64, 65, 127, 128, 289, 512])
+def test_attn_scan_lengths(T):
+    eo, es = _scan_case(2, 2, T, seed=42 + T)
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+
+
+def test_attn_scan_carried_state_and_positions():
+    eo, es = _scan_case(2, 3, 200, seed=1, start_pos=128, with_state=True)
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+    eo, es = _scan_case(3, 2, 70, seed=2, start_pos=torch.tensor([0, 5, 1000], dtype=torch.int32), with_state=True)
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+
+
+def test_attn_scan_extreme_decay():
+    eo, es = _scan_case(1, 2, 150, seed=3, gammas=[0.01, 0.99])
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+
+
+def test_attn_scan_split_equals_one_shot():
+    """prefill(T1) then prefill(T2) with the handed-off state == prefill(T1 + T2)."""
+    g = torch.Generator().manual_seed(9)
+    B, H, T = 2, 4, 192
+    qkv = torch.randn(B, T, 3 * H * 64, generator=g).bfloat16().cuda()
+    gamma = (torch.rand(H, generator=g) * 0.099 + 0.9).cuda()
+    cos, sin = rope_tabs(T)
+
+    def run(x, t, **kw):
+        flat = x.reshape(B * t, 3 * H * 64)
+        return ops.attn_scan(flat[:, :H * 64], flat[:, H * 64:2 * H * 64], flat[:, 2 * H * 64:], gamma, cos, sin, B, t,
+                             H, want_state=True, **kw)
+
+    o_full, S_full = run(qkv, T)
+    o_a, S_a = run(qkv[:, :128].contiguous(), 128)
+    o_b, S_b = run(qkv[:, 128:].contiguous(), 64, start_pos=128, state_in=S_a)
+    o_split = torch.cat((o_a.view(B, 128, -1), o_b.view(B, 64, -1)), dim=1).reshape(B * T, -1)
+    assert rel_l2(o_split.float(), o_full.float()) < 3e-3   # chunk boundaries coincide: only bf16 mirror rounding differs
+    assert rel_l2(S_b, S_full) < 1e-5
+
+
+def test_attention_module_fixture():
+    """End to end against the reference module's outputs: projections -> scan -> out_proj."""
+    gf = load("attention")
+    H = 2
+    packs = {}
+    for n in ("q_proj", "k_proj", "v_proj", "out_proj"):
+        packs[n] = ops.pack_ternary(gf[f"{n}.weight"].cuda())
+    w_qkv = torch.cat([packs[n][0] for n in ("q_proj", "k_proj", "v_proj")])
+    a_qkv = torch.cat([packs[n][1] for n in ("q_proj", "k_proj", "v_proj")])
+    gamma = torch.sigmoid(gf["gamma_raw"]).cuda()
+    cos, sin = rope_tabs(512)
+    for T in (1, 17, 64, 37, 123, 192):
+        x = gf[f"T{T}_x"]
+        B = x.shape[0]
+        xb = x.reshape(B * T, 128).bfloat16().cuda()
+        qkv = ops.ternary_linear(xb, w_qkv, a_qkv, alpha_rows=128)
+        o, _ = ops.attn_scan(qkv[:, :128], qkv[:, 128:256], qkv[:, 256:], gamma, cos, sin, B, T, H,
+                             start_pos=int(gf[f"T{T}_start_pos"]))
+        y = ops.ternary_linear(o, *packs["out_proj"], epilogue=ops.EPI_F32)
+        assert rel_l2(y.view(B, T, 128), gf[f"T{T}_y"]) <= TOL_BF16, T
+
+
+# ------------------------------------------------------------------ router / metadata / gather / combine
+def test_router_bit_exact_on_tie_free_rows():
+    g = torch.Generator().manual_seed(4)
+    N, C, E = 5000, 1024, 4
+    x = torch.randn(N, C, generator=g).bfloat16()
+    w = torch.randn(E, C, generator=g) * 0.03
+    idx_ref, gates_ref, probs_ref = orc.router_top2(x.float(), w)
+    idx, gates, probs = ops.router_top2(x.cuda(), w.cuda(), want_probs=True)
+    srt = probs_ref.sort(dim=-1, descending=True).values
+    margin = torch.minimum(srt[:, 0] - srt[:, 1], srt[:, 1] - srt[:, 2])
+    clear = margin > 1e-5
+    assert clear.float().mean() > 0.99
+    assert torch.equal(idx.cpu()[clear], idx_ref[clear])
+    assert (idx.cpu() != idx_ref).any(dim=-1).sum().item() <= (~clear).sum().item()
+    assert torch.allclose(probs.cpu(), probs_ref, atol=2e-6)
+    assert torch.allclose(gates.cpu()[clear], gates_ref[clear], atol=1e-5)
+
+
+def test_router_ties_go_to_lower_expert():
+    x = torch.zeros(64, 256, dtype=torch.bfloat16)
+    w = torch.randn(4, 256)
+    idx, gates, _ = ops.router_top2(x.cuda(), w.cuda())
+    assert torch.equal(idx.cpu(), torch.tensor([[0, 1]]).repeat(64, 1))
+    assert torch.allclose(gates.cpu(), torch.full((64, 2), 0.5), atol=1e-6)
+
+
+@pytest.mark.parametrize("N,K,E", [(1, 2, 4), (3, 2, 4), (127, 2, 4), (128, 2, 4), (129, 2, 4), (5000, 2, 4),
+                                   (65536, 2, 4), (1000, 1, 8), (777, 3, 16)])
+def test_metadata_bit_exact(N, K, E):
+    g = torch.Generator().manual_seed(N + K + E)
+    idx = torch.randint(0, E, (N, K), generator=g)
+    if N >= 100:
+        idx[: N // 2] = idx[: N // 2].clamp(max=1)        # skew
+    ref = orc.moe_metadata(idx, E)
+    got = ops.moe_metadata(idx.cuda(), E)
+    for r, t in zip(ref, got):
+        assert torch.equal(t.cpu(), r)
+
+
+def test_metadata_forced_routings_from_fixture():
+    gf = load("moe")
+    for tag in ("all_e0", "e0_empty", "imbalanced", "b2t64"):
+        idx = gf[f"{tag}_topk_idx"]
+        counts, offsets, scatter, gather, gate_idx = (t.cpu() for t in ops.moe_metadata(idx.cuda(), 4))
+        assert torch.equal(gather.long() * 2 + gate_idx.long(), gf[f"{tag}_order"]), tag
+        assert torch.equal(counts.long(), torch.bincount(idx.reshape(-1), minlength=4))
+
+
+def test_gather_and_combine():
+    g = torch.Generator().manual_seed(6)
+    N, C, E = 1000, 1024, 4
+    x = torch.randn(N, C, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(E, generator=g)[:2] for _ in range(N)])
+    gates = torch.rand(N, 2, generator=g)
+    counts, offsets, scatter, gather, gate_idx = ops.moe_metadata(idx.cuda(), E)
+    disp = ops.dispatch_gather(x.cuda(), gather)
+    assert torch.equal(disp.cpu(), x[gather.cpu().long()])
+    y = torch.randn(2 * N, C, generator=g).bfloat16()
+    stats = torch.zeros(2, dtype=torch.float64, device="cuda")
+    out = ops.scatter_combine(y.cuda(), gates.cuda(), scatter, out_dtype=torch.float32, stats=stats)
+    ref = (gates[:, :, None] * y.float()[scatter.cpu().long()]).sum(dim=1)
+    assert rel_l2(out, ref) < 1e-6
+    sc = ops.moe_finalize(stats, None, None, E, N, N * C, 0.01).cpu()
+    assert abs(float(sc[1]) - float(ref.mean())) < 1e-6 and abs(float(sc[2]) - float(ref.var())) < 1e-5 * float(ref.var())
+    out_bf = ops.scatter_combine(y.cuda(), gates.cuda(), scatter)
+    assert rel_l2(out_bf.float(), ref) < 4e-3
+
+
+def test_moe_layer_fixture():
+    """Whole MoE layer against the reference module's outputs, forced routings included."""
+    gf = load("moe")
+    E, C = 4, 128
+    w1 = [ops.pack_ternary(gf[f"w1.{e}.weight"].cuda()) for e in range(E)]
+    w2 = [ops.pack_ternary(gf[f"w2.{e}.weight"].cuda()) for e in range(E)]
+    p1, a1 = torch.stack([w[0] for w in w1]), torch.cat([w[1] for w in w1])
+    p2, a2 = torch.stack([w[0] for w in w2]), torch.cat([w[1] for w in w2])
+    for tag in ("b1t16", "b2t64", "all_e0", "e0_empty", "imbalanced"):
+        x = gf[f"{tag}_x"].reshape(-1, C)
+        N = x.shape[0]
+        idx = gf[f"{tag}_topk_idx"].cuda()     # the reference's routing: isolates the expert path
+        gates = (gf[f"{tag}_topk_probs"] / (gf[f"{tag}_topk_probs"].sum(-1, keepdim=True) + 1e-8)).cuda()
+        counts, offsets, scatter, gather, gate_idx = ops.moe_metadata(idx, E)
+        disp = ops.dispatch_gather(x.bfloat16().cuda(), gather)
+        hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16)
+        yd = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16)
+        stats = torch.zeros(2, dtype=torch.float64, device="cuda")
+        out = ops.scatter_combine(yd, gates, scatter, out_dtype=torch.float32, stats=stats)
+        assert rel_l2(out.view_as(gf[f"{tag}_y"]), gf[f"{tag}_y"]) <= TOL_BF16, tag
+        sc = ops.moe_finalize(stats, None, None, E, N, N * C, 0.01).cpu()
+        assert abs(float(sc[2]) - float(gf[f"{tag}_act_var"])) <= 3e-2 * float(gf[f"{tag}_act_var"])
+        assert _lib.device_status() == 0
+
+
+def test_router_balance_loss_fixture():
+    gf = load("moe")
+    # the fixture's d_model (128) is below the router kernel's 256-column step: embed it in 256 columns
+    for tag in ("b2t64", "imbalanced"):
+        x = torch.zeros(gf[f"{tag}_x"].numel() // 128, 256)
+        x[:, :128] = gf[f"{tag}_x"].reshape(-1, 128)
+        w = torch.zeros(4, 256)
+        w[:, :128] = gf[f"{tag}_router"]
+        xb = x.bfloat16()
+        idx_ref, _, probs_ref = orc.router_top2(xb.float(), w)
+        psum = torch.zeros(4, dtype=torch.float64, device="cuda")
+        hist = torch.zeros(4, dtype=torch.int32, device="cuda")
+        idx, gates, _ = ops.router_top2(xb.cuda(), w.cuda(), probs_sum=psum, top1_hist=hist)
+        sc = ops.moe_finalize(None, psum, hist, 4, x.shape[0], 1, 0.01).cpu()
+        f = torch.nn.functional.one_hot(idx_ref[:, 0], 4).float().mean(0)
+        lb = 0.01 * 4 * (f * probs_ref.mean(0)).sum()
+        assert abs(float(sc[0]) - float(lb)) < 1e-6
+        assert abs(float(lb) - float(gf[f"{tag}_l_balance"])) < 2e-4   # bf16 rounding of x only
+
+
+# ------------------------------------------------------------------ LSF
+def test_lsf_model_fixture():
+    gf = load("lsf")
+    vs = gf["var_scale"].reshape(1).cuda()
+    for tag in ("t1", "t65", "t200"):
+        x = gf[f"{tag}_x"].cuda()
+        h0 = gf.get(f"{tag}_h_prev")
+        out, last = ops.lsf_scan(x, act_var=gf[f"{tag}_act_var"].reshape(1).cuda(), var_scale=vs,
+                                 h0=None if h0 is None else h0.cuda())
+        assert rel_l2(out, gf[f"{tag}_h_out"]) < 2e-5, tag
+        assert rel_l2(last, gf[f"{tag}_h_last"]) < 2e-5, tag
+
+
+@pytest.mark.parametrize("T", [1, 15, 65, 127, 129, 256])
+def test_lsf_extension_fixture(T):
+    gf = load("lsf")
+    out, _ = ops.lsf_scan(gf[f"ext{T}_M"].cuda(), alpha_tensor=gf[f"ext{T}_alpha"].cuda(), h0=gf[f"ext{T}_h0"].cuda())
+    assert float((out.cpu() - gf[f"ext{T}_H"]).abs().max()) < 1e-5       # the reference's fp32 tolerance
+    outb, _ = ops.lsf_scan(gf[f"ext{T}_M"].bfloat16().cuda(), alpha_tensor=gf[f"ext{T}_alpha"].bfloat16().cuda(),
+                           h0=gf[f"ext{T}_h0"].cuda())
+    assert float((outb.float().cpu() - gf[f"ext{T}_H"]).abs().max()) < 8e-2  # the reference's bf16 tolerance
+
+
+@pytest.mark.parametrize("B,T,D", [(2, 1000, 192), (1, 2048, 1024), (3, 300, 66)])
+def test_lsf_scan_bf16_with_residual(B, T, D):
+    g = torch.Generator().manual_seed(T)
+    m = torch.randn(B, T, D, generator=g).bfloat16()
+    h0 = torch.randn(B, D, generator=g)
+    resid = torch.randn(B, T, D, generator=g)
+    alpha = torch.tensor([0.93])
+    ref = orc.lsf_scan(m.float(), float(alpha), h0)
+    r = resid.clone().cuda()
+    out, last = ops.lsf_scan(m.cuda(), alpha_scalar=alpha.cuda(), h0=h0.cuda(), resid=r, out_dtype=torch.float32)
+    assert rel_l2(out, ref) < 1e-5 and rel_l2(last, ref[:, -1]) < 1e-5
+    assert rel_l2(r, resid + ref) < 1e-6
+    outb, _ = ops.lsf_scan(m.cuda(), alpha_scalar=alpha.cuda(), h0=h0.cuda())
+    assert rel_l2(outb.float(), ref) < 4e-3
+
+
+def test_lsf_linearity_large():
+    """Size-independent property at a full-size shape: scan(a*x + y) == a*scan(x) + scan(y)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(8, 2048, 1024, generator=g, device="cuda")
+    y = torch.randn(8, 2048, 1024, generator=g, device="cuda")
+    al = torch.tensor([0.97], device="cuda")
+    sx, _ = ops.lsf_scan(x, alpha_scalar=al)
+    sy, _ = ops.lsf_scan(y, alpha_scalar=al)
+    sxy, _ = ops.lsf_scan(2.0 * x + y, alpha_scalar=al)
+    assert rel_l2(sxy, 2.0 * sx + sy) < 1e-5
