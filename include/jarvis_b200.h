@@ -139,7 +139,7 @@ int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, con
 
 /* Eval-mode router of SparseMoELayer.forward (jarvis_engine/jarvis_model.py:218-224): logits in f32,
  * softmax, top-2 (equal probabilities: lower expert id first), gates = p / (p0 + p1 + 1e-8).
- * x: bf16 [N][C]; w_router: f32 [E][C] (E = 4 or 8, C % 256 == 0);
+ * x: bf16 [N][C]; w_router: f32 [E][C] (E = 4 or 8, C % 8 == 0);
  * topk_idx: i64 [N][2]; gates: f32 [N][2]; probs: f32 [N][E] or NULL;
  * probs_sum: f64 [E] or NULL and top1_hist: i32 [E] or NULL are ACCUMULATED into (zero them first):
  * the P and f of the load-balance loss (jarvis_model.py:244-247). */

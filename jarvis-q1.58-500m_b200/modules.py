@@ -1,0 +1,488 @@
+"""Drop-in modules: the reference's PyTorch module API over the sm_100a kernels.
+
+Constructors, parameter / buffer names (so state dicts interchange: 23 tensors per block, 555 for
+the 24-layer model), forward signatures and return tuples follow jarvis_engine/jarvis_model.py and
+the CUDA drop-ins in associative_attention_cuda/associative_attention.py and
+sparse_model_cuda/sparse_model.py.  Inference only (no autograd through the kernels), CUDA only:
+a CPU tensor or a missing library raises, nothing falls back.
+
+Numerics: the residual stream is carried in fp32, GEMM inputs and scan inputs are bf16, every
+accumulation is fp32 -- the reference's autocast regime, checked against its fp32 CPU results.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+
+# ----------------------------------------------------------------------------------------------
+# small pieces
+# ----------------------------------------------------------------------------------------------
+
+
+class RMSNorm(nn.Module):
+    """jarvis_engine/jarvis_model.py:19-26."""
+
+    def __init__(self, dim: int, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x):
+        return ops.rmsnorm(x.contiguous(), self.weight.detach().float(), self.eps, out_dtype=x.dtype)
+
+
+class _PackCache:
+    """Packed form of one or more fp32 weight matrices, rebuilt when any of them changes."""
+
+    def __init__(self):
+        self.key = None
+        self.packed = None
+        self.alpha = None
+
+    def get(self, weights, stack: bool):
+        key = tuple((w.data_ptr(), w._version, w.device) for w in weights)
+        if key != self.key:
+            pa = [ops.pack_ternary(w.detach().float().contiguous()) for w in weights]
+            self.packed = torch.stack([p for p, _ in pa]) if stack else torch.cat([p for p, _ in pa])
+            self.alpha = torch.cat([a for _, a in pa])
+            self.key = key
+        return self.packed, self.alpha
+
+
+class TernaryLinear(nn.Module):
+    """jarvis_engine/utils/ternary_ops.py:42-53.  The fp32 master weight is quantised and packed
+    to 2 bits once (and again whenever it is modified), not on every forward."""
+
+    def __init__(self, in_features, out_features, bias=False):
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(out_features, in_features))
+        nn.init.kaiming_uniform_(self.weight, a=5 ** 0.5)
+        self.bias = nn.Parameter(torch.zeros(out_features)) if bias else None
+        self._cache = _PackCache()
+
+    def packed(self):
+        return self._cache.get([self.weight], stack=False)
+
+    def forward(self, x):
+        packed, alpha = self.packed()
+        x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+        if x.dtype == torch.float32:
+            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_F32)
+        else:
+            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_BF16).to(x.dtype)
+        y = y.view(*x.shape[:-1], -1)
+        return y if self.bias is None else y + self.bias
+
+
+class RotaryEmbedding(nn.Module):
+    """Same caches as jarvis_engine/jarvis_model.py:35-57 (fp32 cos/sin of shape (n, dim), grown by
+    doubling); the kernels read the first half of the last axis (the two halves are equal)."""
+
+    def __init__(self, dim: int, max_seq_len: int = 2048, base: float = 10000.0):
+        super().__init__()
+        self.dim = dim
+        self.base = base
+        inv_freq = 1.0 / (base ** (torch.arange(0, dim, 2).float() / dim))
+        self.register_buffer("inv_freq", inv_freq, persistent=False)
+        self.max_seq_len_cached = 0
+        self._half = None
+        self._build_cache(max_seq_len, device=inv_freq.device)
+
+    def _build_cache(self, seq_len: int, device):
+        self.max_seq_len_cached = max(seq_len, 256)
+        t = torch.arange(self.max_seq_len_cached, dtype=torch.float32, device=device)
+        freqs = torch.outer(t, self.inv_freq.to(device))
+        emb = torch.cat((freqs, freqs), dim=-1)
+        self.register_buffer("cos_cached", emb.cos(), persistent=False)
+        self.register_buffer("sin_cached", emb.sin(), persistent=False)
+        self._half = None
+
+    def half_tables(self, end_pos: int, device):
+        if end_pos > self.max_seq_len_cached or self.cos_cached.device != device:
+            self._build_cache(max(end_pos, self.max_seq_len_cached * 2), device=device)
+        if self._half is None:
+            h = self.dim // 2
+            self._half = (self.cos_cached[:, :h].contiguous(), self.sin_cached[:, :h].contiguous())
+        return self._half
+
+
+def _as_rows_bf16(x):
+    return x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
+
+
+# ----------------------------------------------------------------------------------------------
+# attention
+# ----------------------------------------------------------------------------------------------
+class AssociativeLinearAttention(nn.Module):
+    """jarvis_engine/jarvis_model.py:89-191; `h_prev` as in CUDAAssociativeLinearAttention.forward
+    (associative_attention_cuda/associative_attention.py:212).  `forward_with_state` additionally
+    returns the final state (B, H, D, D) for decode hand-off, which the reference computes and drops."""
+
+    CHUNK_SIZE = 64
+
+    def __init__(self, d_model, n_heads, max_seq_len=2048):
+        super().__init__()
+        self.n_heads = n_heads
+        self.head_dim = d_model // n_heads
+        if self.head_dim != 64:
+            raise ValueError("the sm_100a attention scan is built for head_dim == 64")
+        self.q_proj = TernaryLinear(d_model, d_model)
+        self.k_proj = TernaryLinear(d_model, d_model)
+        self.v_proj = TernaryLinear(d_model, d_model)
+        self.out_proj = TernaryLinear(d_model, d_model)
+        self.gamma_raw = nn.Parameter(torch.full((n_heads,), 2.94))
+        self.rotary = RotaryEmbedding(self.head_dim, max_seq_len=max_seq_len)
+        cs = self.CHUNK_SIZE
+        i = torch.arange(cs, dtype=torch.float32)
+        diff = i.unsqueeze(1) - i.unsqueeze(0)
+        # state-dict compatibility: the kernel derives its decay tables itself
+        self.register_buffer("_diff_clamp", diff.clamp(min=0))
+        self.register_buffer("_causal", (diff >= 0).float())
+        self.register_buffer("_i_idx", i)
+        self.register_buffer("_i_idx_p1", i + 1)
+        self.register_buffer("_c_m1_m_i", (cs - 1) - i)
+        self._qkv = _PackCache()
+
+    def qkv_packed(self):
+        return self._qkv.get([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], stack=False)
+
+    def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False):
+        """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None)."""
+        C = xn_rows.shape[1]
+        packed, alpha = self.qkv_packed()
+        qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C)
+        end = (int(start_pos.max()) if torch.is_tensor(start_pos) else int(start_pos)) + T
+        cos, sin = self.rotary.half_tables(end, xn_rows.device)
+        gamma = torch.sigmoid(self.gamma_raw.detach().float())
+        if h_prev is not None:
+            h_prev = h_prev.to(torch.float32).contiguous()
+        return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
+                             start_pos=start_pos, state_in=h_prev, want_state=want_state)
+
+    def forward_with_state(self, x, start_pos=0, h_prev=None):
+        B, T, C = x.shape
+        o, state = self.scan_rows(_as_rows_bf16(x), B, T, start_pos, h_prev, want_state=True)
+        return self.out_proj(o).view(B, T, C).to(x.dtype), state
+
+    def forward(self, x, start_pos: int = 0, h_prev=None):
+        B, T, C = x.shape
+        o, _ = self.scan_rows(_as_rows_bf16(x), B, T, start_pos, h_prev)
+        packed, alpha = self.out_proj.packed()
+        if x.dtype == torch.float32:
+            return ops.ternary_linear(o, packed, alpha, epilogue=ops.EPI_F32).view(B, T, C)
+        return ops.ternary_linear(o, packed, alpha).view(B, T, C).to(x.dtype)
+
+
+CUDAAssociativeLinearAttention = AssociativeLinearAttention
+
+
+# ----------------------------------------------------------------------------------------------
+# MoE
+# ----------------------------------------------------------------------------------------------
+class SparseMoELayer(nn.Module):
+    """jarvis_engine/jarvis_model.py:198-251 / sparse_model_cuda/sparse_model.py:87-178 (eval mode:
+    no routing noise).  Router -> dispatch metadata -> gather -> grouped ternary GEMMs -> combine,
+    all on the device: expert offsets never visit the host."""
+
+    def __init__(self, d_model, num_experts=4, top_k=2, hidden_mult=2, noise_std=0.1, balance_alpha=0.01):
+        super().__init__()
+        if top_k != 2:
+            raise ValueError("the router kernel implements top-2")
+        self.num_experts = num_experts
+        self.top_k = top_k
+        self.noise_std = noise_std
+        self.balance_alpha = balance_alpha
+        self.router = nn.Linear(d_model, num_experts, bias=False)
+        hidden = d_model * hidden_mult
+        self.w1 = nn.ModuleList([TernaryLinear(d_model, hidden) for _ in range(num_experts)])
+        self.w2 = nn.ModuleList([TernaryLinear(hidden, d_model) for _ in range(num_experts)])
+        self._p1 = _PackCache()
+        self._p2 = _PackCache()
+        self.last_routing = None  # (topk_idx, gates, metadata) of the most recent call, for inspection
+
+    def packed(self):
+        return (self._p1.get([m.weight for m in self.w1], stack=True),
+                self._p2.get([m.weight for m in self.w2], stack=True))
+
+    def run_rows(self, xn_rows, out_dtype=torch.bfloat16):
+        """xn_rows: bf16 (N, C) -> (out (N, C), scalars f32 [l_balance, act_mean, act_var])."""
+        if self.training:
+            raise RuntimeError("SparseMoELayer (sm_100a): inference only; call .eval() first")
+        N, C = xn_rows.shape
+        E = self.num_experts
+        dev = xn_rows.device
+        acc = torch.zeros(2 + E, dtype=torch.float64, device=dev)   # [sum, sum^2, P_0..P_{E-1}]
+        hist = torch.zeros(E, dtype=torch.int32, device=dev)
+        idx, gates, _ = ops.router_top2(xn_rows, self.router.weight.detach().float().contiguous(),
+                                        probs_sum=acc[2:], top1_hist=hist)
+        meta = ops.moe_metadata(idx, E)
+        counts, offsets, scatter, gather, gate_idx = meta
+        (p1, a1), (p2, a2) = self.packed()
+        disp = ops.dispatch_gather(xn_rows, gather)
+        hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16)
+        y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16)
+        out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
+        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, N, N * C, self.balance_alpha)
+        self.last_routing = (idx, gates, meta)
+        return out, scalars
+
+    def forward(self, x):
+        B, T, C = x.shape
+        out, sc = self.run_rows(_as_rows_bf16(x), out_dtype=torch.float32 if x.dtype == torch.float32 else torch.bfloat16)
+        return out.view(B, T, C).to(x.dtype), sc[0], sc[1], sc[2]
+
+
+CUDASparseMoELayer = SparseMoELayer
+
+
+# ----------------------------------------------------------------------------------------------
+# LSF
+# ----------------------------------------------------------------------------------------------
+class LiquidStateFusion(nn.Module):
+    """jarvis_engine/jarvis_model.py:261-314: one scalar decay per call derived from act_var."""
+
+    def __init__(self, d_model, alpha_min=0.1, alpha_max=0.99):
+        super().__init__()
+        self.alpha_min = alpha_min
+        self.alpha_max = alpha_max
+        self.var_scale = nn.Parameter(torch.tensor(1.0))
+
+    def forward(self, x, act_var, h_prev=None):
+        act_var = torch.as_tensor(act_var, dtype=torch.float32, device=x.device).reshape(1)
+        h0 = None if h_prev is None else h_prev.to(torch.float32).contiguous()
+        m = x.contiguous()
+        if m.dtype not in (torch.float32, torch.bfloat16):
+            m = m.float()
+        out, last = ops.lsf_scan(m, act_var=act_var, var_scale=self.var_scale.detach().float().reshape(1),
+                                 alpha_min=self.alpha_min, alpha_max=self.alpha_max, h0=h0)
+        return out.to(x.dtype), last.to(x.dtype)
+
+
+class LiquidStateFusionExt(nn.Module):
+    """The extension flavour, liquid_fusion_cuda/liquid_state_fusion.py:269-294:
+    forward(alpha (B,T,D), M (B,T,D), h0=None) -> H, with optional persistence of the last state."""
+
+    def __init__(self, persistent=False):
+        super().__init__()
+        self.persistent = persistent
+        self.h = None
+
+    def reset_state(self):
+        self.h = None
+
+    def forward(self, alpha, M, h0=None):
+        B, T, D = alpha.shape
+        if alpha.dtype == torch.float64:
+            raise TypeError("Double precision (float64) is not supported on CUDA for LiquidStateFusion.")
+        if h0 is not None:
+            init = h0
+        elif self.persistent and self.h is not None and self.h.shape == (B, D) and self.h.device == alpha.device:
+            init = self.h
+        else:
+            init = None
+        H, last = ops.lsf_scan(M.contiguous(), alpha_tensor=alpha.contiguous(),
+                               h0=None if init is None else init.float().contiguous())
+        self.h = last.to(alpha.dtype) if self.persistent else None
+        return H
+
+
+class ReflectivePenalty(nn.Module):
+    """jarvis_engine/jarvis_model.py:329-351 (scalar arithmetic; the EMA only moves in training)."""
+
+    def __init__(self, lam=0.01, tau_max=1.0, ema_decay=0.99):
+        super().__init__()
+        self.lam = lam
+        self.tau_max = tau_max
+        self.ema_decay = ema_decay
+        self.register_buffer("mu_t", torch.tensor(0.0))
+
+    def forward(self, act_mean, act_var):
+        l_reflect = self.lam * ((self.mu_t.detach() - act_mean) ** 2 + F.relu(act_var - self.tau_max))
+        if self.training:
+            self.mu_t = self.ema_decay * self.mu_t + (1.0 - self.ema_decay) * act_mean.detach()
+        return l_reflect
+
+
+# ----------------------------------------------------------------------------------------------
+# block and model
+# ----------------------------------------------------------------------------------------------
+class JarvisBlock(nn.Module):
+    """jarvis_engine/jarvis_model.py:399-441.  `forward` keeps the reference signature; the fused
+    path `forward_rows` works on the fp32 residual stream in place and is what `Jarvis` calls."""
+
+    def __init__(self, d_model, n_heads, num_experts=4, top_k=2, max_seq_len=2048, use_cuda_attn: bool = True,
+                 use_cuda_moe: bool = True):
+        super().__init__()
+        self.norm1 = RMSNorm(d_model)
+        self.attn = AssociativeLinearAttention(d_model, n_heads, max_seq_len=max_seq_len)
+        self.norm2 = RMSNorm(d_model)
+        self.moe = SparseMoELayer(d_model, num_experts=num_experts, top_k=top_k)
+        self.liquid = LiquidStateFusion(d_model)
+        self.reflect = ReflectivePenalty()
+
+    def forward_rows(self, x, B, T, h_prev=None, start_pos=0, attn_state=None, want_attn_state=False):
+        """x: f32 (B*T, C) residual stream, UPDATED IN PLACE.  Returns (h_last f32 (B, C), scalars f32
+        [l_balance, act_mean, act_var], attention state or None)."""
+        C = x.shape[1]
+        xn = ops.rmsnorm(x, self.norm1.weight.detach().float(), self.norm1.eps)
+        o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state)
+        po, ao = self.attn.out_proj.packed()
+        ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x)          # x += attn(norm1(x))
+        xn = ops.rmsnorm(x, self.norm2.weight.detach().float(), self.norm2.eps)
+        moe_out, scalars = self.moe.run_rows(xn)
+        _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],
+                                 var_scale=self.liquid.var_scale.detach().float().reshape(1),
+                                 alpha_min=self.liquid.alpha_min, alpha_max=self.liquid.alpha_max,
+                                 h0=None if h_prev is None else h_prev.float().contiguous(),
+                                 resid=x.view(B, T, C), want_out=False)            # x += lsf(moe(norm2(x)))
+        return h_last, scalars, state
+
+    def forward(self, x, h_prev=None, start_pos: int = 0):
+        B, T, C = x.shape
+        rows = x.reshape(B * T, C).float().clone()
+        h_last, sc, _ = self.forward_rows(rows, B, T, h_prev, start_pos)
+        l_reflect = self.reflect(sc[1], sc[2])
+        return rows.view(B, T, C).to(x.dtype), h_last.to(x.dtype), sc[0], l_reflect
+
+
+class Jarvis(nn.Module):
+    """jarvis_engine/jarvis_model.py:444-546.  forward(idx, targets=None, persist_state=False) ->
+    (logits, loss); reset_state(); get_backend_status(); param_count().  Logits are bf16
+    (`logits_dtype`).  Beyond the reference: `carry_attention_state=True` also hands the attention
+    state S across persist_state calls (the reference carries only the LSF membrane and the RoPE
+    offset, so it is off by default)."""
+
+    def __init__(self, vocab_size=50257, d_model=1024, n_layers=24, n_heads=16, num_experts=4, top_k=2,
+                 max_seq_len=1024, use_cuda_attn: bool = True, use_cuda_moe: bool = True):
+        super().__init__()
+        self.d_model = d_model
+        self.use_cuda_attn = True
+        self.use_cuda_moe = True
+        self.tok_emb = nn.Embedding(vocab_size, d_model)
+        self.blocks = nn.ModuleList([
+            JarvisBlock(d_model, n_heads, num_experts, top_k, max_seq_len=max_seq_len) for _ in range(n_layers)
+        ])
+        self.final_norm = RMSNorm(d_model)
+        self.lm_head = nn.Linear(d_model, vocab_size, bias=False)
+        self._h_states: list = [None] * n_layers
+        self._attn_states: list = [None] * n_layers
+        self._token_pos: int = 0
+        self.carry_attention_state = False
+        self.logits_dtype = torch.bfloat16
+        self._lm_head_bf16 = None
+        self.last_aux = None
+
+    def get_backend_status(self):
+        n = len(self.blocks)
+        return {
+            "has_cuda_attn_extension": True,
+            "has_cuda_moe_extension": True,
+            "attn_backend": "cuda",
+            "moe_backend": "cuda",
+            "attn_cuda_blocks": f"{n}/{n}",
+            "moe_cuda_blocks": f"{n}/{n}",
+        }
+
+    def reset_state(self):
+        self._h_states = [None] * len(self.blocks)
+        self._attn_states = [None] * len(self.blocks)
+        self._token_pos = 0
+
+    def _lm_head_weight(self):
+        w = self.lm_head.weight
+        key = (w.data_ptr(), w._version)
+        if self._lm_head_bf16 is None or self._lm_head_bf16[0] != key:
+            self._lm_head_bf16 = (key, w.detach().to(torch.bfloat16).contiguous())
+        return self._lm_head_bf16[1]
+
+    def hidden_rows(self, idx, persist_state=False):
+        """Embedding + all blocks + final norm -> bf16 (B*T, C) hidden rows."""
+        if self.training:
+            raise RuntimeError("Jarvis (sm_100a): inference only; call .eval() first")
+        B, T = idx.shape
+        x = ops.embedding(idx.contiguous(), self.tok_emb.weight.detach().float()).view(B * T, self.d_model)
+        start_pos = self._token_pos if persist_state else 0
+        if persist_state:
+            self._token_pos += T
+        h_prevs = self._h_states if persist_state else [None] * len(self.blocks)
+        s_prevs = self._attn_states if (persist_state and self.carry_attention_state) else [None] * len(self.blocks)
+        new_h, new_s, aux = [], [], []
+        for i, block in enumerate(self.blocks):
+            h_prev = h_prevs[i]
+            if h_prev is not None and h_prev.shape[0] != B:
+                h_prev = None
+            s_prev = s_prevs[i]
+            if s_prev is not None and s_prev.shape[0] != B:
+                s_prev = None
+            h_last, sc, state = block.forward_rows(x, B, T, h_prev, start_pos, s_prev,
+                                                   want_attn_state=self.carry_attention_state)
+            new_h.append(h_last)
+            new_s.append(state)
+            aux.append(sc)
+        self._h_states = new_h
+        self._attn_states = new_s
+        self.last_aux = aux
+        return ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
+
+    @torch.no_grad()
+    def forward(self, idx, targets=None, persist_state=False):
+        B, T = idx.shape
+        hidden = self.hidden_rows(idx, persist_state)
+        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)   # dense bf16 lm_head (library GEMM)
+        if self.logits_dtype != torch.bfloat16:
+            logits = logits.to(self.logits_dtype)
+        loss = None
+        if targets is not None:
+            ce = F.cross_entropy(logits.float().view(-1, logits.size(-1)), targets.view(-1))
+            aux = torch.stack(self.last_aux)
+            l_reflect = sum(b.reflect(sc[1], sc[2]) for b, sc in zip(self.blocks, self.last_aux))
+            loss = ce + aux[:, 0].sum() + l_reflect
+        return logits, loss
+
+    def param_count(self):
+        n = sum(p.numel() for p in self.parameters())
+        return n, f"{n/1e6:.1f}M parameters"
+
+
+def install(model: nn.Module) -> nn.Module:
+    """Swap the attention / MoE / LSF / norm modules of an existing reference `Jarvis` (or anything
+    with the same `.blocks[i].{norm1,attn,norm2,moe,liquid}` layout) for the sm_100a ones, keeping the
+    parameters (shared, not copied) and therefore the state-dict keys.  Mirrors the reference's own
+    attribute-replacement mechanism (experiments/architecture_matrix/modular_memory.py:353-368)."""
+
+    def adopt(dst: nn.Module, src: nn.Module):
+        missing = dst.load_state_dict(src.state_dict(), strict=False)
+        if missing.missing_keys:
+            raise RuntimeError(f"install: source module lacks {missing.missing_keys}")
+        return dst.to(next(src.parameters()).device).eval()
+
+    for blk in model.blocks:
+        d_model = blk.norm1.weight.numel()
+        blk.attn = adopt(AssociativeLinearAttention(d_model, blk.attn.n_heads,
+                                                    max_seq_len=blk.attn.rotary.max_seq_len_cached), blk.attn)
+        blk.moe = adopt(SparseMoELayer(d_model, blk.moe.num_experts, blk.moe.top_k, noise_std=blk.moe.noise_std,
+                                       balance_alpha=blk.moe.balance_alpha), blk.moe)
+        blk.liquid = adopt(LiquidStateFusion(d_model, blk.liquid.alpha_min, blk.liquid.alpha_max), blk.liquid)
+        blk.norm1 = adopt(RMSNorm(d_model, blk.norm1.eps), blk.norm1)
+        blk.norm2 = adopt(RMSNorm(d_model, blk.norm2.eps), blk.norm2)
+    return model
+
+
+def ternary_init_(module: nn.Module, std: float = 0.02, generator=None) -> nn.Module:
+    """Gaussian (std 0.02) re-initialisation of every ternary layer: the synthetic-weight recipe the
+    benchmarks and tests use in place of a trained checkpoint."""
+    with torch.no_grad():
+        for m in module.modules():
+            if isinstance(m, TernaryLinear):
+                m.weight.copy_(torch.randn(m.weight.shape, generator=generator) * std)
+    return module
+
+
+__all__ = [
+    "RMSNorm", "TernaryLinear", "RotaryEmbedding", "AssociativeLinearAttention", "CUDAAssociativeLinearAttention",
+    "SparseMoELayer", "CUDASparseMoELayer", "LiquidStateFusion", "LiquidStateFusionExt", "ReflectivePenalty",
+    "JarvisBlock", "Jarvis", "install", "ternary_init_",
+]

@@ -1,0 +1,111 @@
+"""GPU parity of the drop-in modules against outputs of the reference's own modules (golden
+fixtures) and the CPU oracle: block, tiny model, persistence semantics, state-dict contract."""
+import pytest
+import torch
+
+import jarvis_b200
+from jarvis_b200 import _lib, modules as jm
+from oracle import jarvis_oracle as orc
+from tests.golden.loader import load
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2   # rel-L2 of bf16 compute against the fp32 reference
+
+
+def rel_l2(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def test_block_fixture():
+    g = load("block")
+    sd = {k[3:]: v for k, v in g.items() if k.startswith("sd_")}
+    blk = jm.JarvisBlock(128, 2, 4, 2).eval()
+    assert set(blk.state_dict().keys()) == set(sd.keys()) and len(sd) == 23
+    blk.load_state_dict(sd)
+    blk = blk.cuda()
+    x, h_last, l_bal, l_ref = blk(g["x"].cuda(), g["h_prev"].cuda(), start_pos=int(g["start_pos"]))
+    assert _lib.device_status() == 0
+    assert rel_l2(x, g["x_out"]) <= TOL
+    assert rel_l2(h_last, g["h_last"]) <= 2e-2   # last-token membrane alone: few elements, same bf16 inputs
+    assert abs(float(l_bal) - float(g["l_balance"])) <= 2e-2 * abs(float(g["l_balance"]))
+    assert abs(float(l_ref) - float(g["l_reflect"])) <= 5e-2 * abs(float(g["l_reflect"])) + 1e-6
+
+
+def test_model_fixture_and_persistence():
+    g = load("model")
+    sd = {k[3:]: v for k, v in g.items() if k.startswith("sd_")}
+    model = jm.Jarvis(vocab_size=256, d_model=128, n_layers=2, n_heads=2, max_seq_len=256).eval()
+    assert set(model.state_dict().keys()) == set(sd.keys())
+    model.load_state_dict(sd)
+    model = model.cuda()
+    idx = g["idx"].cuda()
+    logits, loss = model(idx)
+    assert loss is None and logits.shape == (2, 96, 256)
+    assert rel_l2(logits.float(), g["logits"]) <= 1.5e-2   # + bf16 lm_head and bf16 logits
+    st = model.get_backend_status()
+    assert st["attn_backend"] == "cuda" and st["moe_backend"] == "cuda" and st["attn_cuda_blocks"] == "2/2"
+    # persist_state: LSF membrane + RoPE offset carried (reference semantics), then reset
+    model.reset_state()
+    la, _ = model(idx[:, :32], persist_state=True)
+    assert model._token_pos == 32 and all(h is not None and h.shape == (2, 128) for h in model._h_states)
+    lb, _ = model(idx[:, 32:64], persist_state=True)
+    assert model._token_pos == 64
+    assert rel_l2(la.float(), g["persist_logits_a"]) <= 1.5e-2
+    assert rel_l2(lb.float(), g["persist_logits_b"]) <= 1.5e-2
+    model.reset_state()
+    assert model._token_pos == 0 and all(h is None for h in model._h_states)
+    # targets -> loss is finite and includes the aux terms
+    _, loss = model(idx, targets=idx)
+    assert torch.isfinite(loss)
+
+
+def test_attention_state_handoff_matches_single_call():
+    """Beyond the reference: carrying S makes prefill(T1) + prefill(T2) equal one prefill of the
+    attention stage (the LSF decay stays per call, so the comparison is at the attention module)."""
+    torch.manual_seed(0)
+    attn = jm.ternary_init_(jm.AssociativeLinearAttention(256, 4)).cuda().eval()
+    x = torch.randn(2, 192, 256, device="cuda")
+    y_full = attn(x)
+    y_a, S = attn.forward_with_state(x[:, :128])
+    y_b, _ = attn.forward_with_state(x[:, 128:], start_pos=128, h_prev=S)
+    assert rel_l2(torch.cat((y_a, y_b), 1), y_full) < 5e-3
+    # oracle with the same carried state
+    ref = orc.attention_forward(x.cpu(), attn.q_proj.weight.cpu(), attn.k_proj.weight.cpu(), attn.v_proj.weight.cpu(),
+                                attn.out_proj.weight.cpu(), attn.gamma_raw.detach().cpu(), 4)
+    assert rel_l2(y_full, ref) <= TOL
+
+
+def test_moe_module_matches_oracle_with_own_routing():
+    torch.manual_seed(1)
+    moe = jm.ternary_init_(jm.SparseMoELayer(256)).cuda().eval()
+    x = torch.randn(2, 300, 256, device="cuda").bfloat16().float()
+    out, l_bal, act_mean, act_var = moe(x)
+    ref_out, ref_lb, ref_mean, ref_var, aux = orc.moe_forward(
+        x.cpu(), moe.router.weight.detach().cpu(), [m.weight.detach().cpu() for m in moe.w1],
+        [m.weight.detach().cpu() for m in moe.w2])
+    idx = moe.last_routing[0].cpu()
+    same = (idx == aux["idx"]).all(dim=-1)
+    assert same.float().mean() > 0.995          # near-ties may resolve differently
+    o, r = out.view(-1, 256).cpu()[same], ref_out.view(-1, 256)[same]
+    assert rel_l2(o, r) <= TOL
+    assert abs(float(l_bal) - float(ref_lb)) < 1e-4
+    assert abs(float(act_var) - float(ref_var)) <= 3e-2 * float(ref_var)
+
+
+def test_lsf_ext_module_persistence():
+    ext = jm.LiquidStateFusionExt(persistent=True)
+    a = torch.rand(2, 40, 8, device="cuda") * 0.98 + 0.01
+    m = torch.randn(2, 40, 8, device="cuda")
+    H = ext(a, m)
+    H2 = ext(a, m)                       # continues from the stored last state
+    ref = orc.lsf_scan(m.cpu(), a.cpu(), H[:, -1].cpu())
+    assert torch.allclose(H2.cpu(), ref, atol=1e-5)
+    ext.reset_state()
+    assert torch.allclose(ext(a, m), H, atol=0)
+
+
+def test_cpu_tensors_are_rejected():
+    lin = jm.TernaryLinear(64, 128)
+    with pytest.raises(RuntimeError, match="no CPU fallback|CUDA"):
+        lin(torch.randn(2, 64))
