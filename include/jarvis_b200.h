@@ -53,6 +53,10 @@ const char* jb200_last_error(void);
 /* ABI version of this library (bumped on any signature change). */
 int jb200_abi_version(void);
 
+/* Number of kernels this library has launched in this process since the last reset
+ * (returns the count before resetting when `reset` is non-zero). */
+long long jb200_kernel_launches(int reset);
+
 /* Reads the current device's status word into *status (synchronises the device) and,
  * when `clear` is non-zero, resets it to 0. */
 int jb200_device_status(unsigned int* status, int clear);

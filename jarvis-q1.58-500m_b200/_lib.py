@@ -26,6 +26,7 @@ _F = C.c_float
 PROTOTYPES = {
     "jb200_last_error": (C.c_char_p, []),
     "jb200_abi_version": (_I, []),
+    "jb200_kernel_launches": (C.c_longlong, [_I]),
     "jb200_device_status": (_I, [C.POINTER(C.c_uint), _I]),
     "jb200_selftest_bounded_wait": (_I, [_I, _P]),
     "jb200_pack_ternary_scratch_bytes": (_Z, [_I, _I]),
@@ -96,3 +97,7 @@ def device_status(clear: bool = True) -> int:
     st = C.c_uint(0)
     check(load().jb200_device_status(C.byref(st), 1 if clear else 0), "jb200_device_status")
     return int(st.value)
+
+
+def kernel_launches(reset: bool = False) -> int:
+    return int(load().jb200_kernel_launches(1 if reset else 0))

@@ -2,6 +2,7 @@
 // other translation units.  Also owns the per-thread error message, the device status word
 // that bounded waits report into, and the bounded-wait self test.
 #include <stdarg.h>
+#include <atomic>
 #include <string.h>
 
 #include "common.cuh"
@@ -15,7 +16,10 @@ __device__ unsigned int g_status_word = 0;
 constexpr int MAX_DEVICES = 64;
 unsigned int* g_status_ptr[MAX_DEVICES] = {nullptr};
 int g_sm_count[MAX_DEVICES] = {0};
+std::atomic<long long> g_launches{0};
 }  // namespace
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -95,6 +99,10 @@ extern "C" {
 const char* jb200_last_error(void) { return g_err; }
 
 int jb200_abi_version(void) { return 1; }
+
+long long jb200_kernel_launches(int reset) {
+  return reset ? g_launches.exchange(0) : g_launches.load();
+}
 
 int jb200_device_status(unsigned int* status, int clear) {
   JB_REQUIRE(status != nullptr, "device_status: null output pointer");

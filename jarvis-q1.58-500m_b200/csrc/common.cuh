@@ -41,11 +41,13 @@ int cuda_fail(cudaError_t e, const char* what);
   do {                                                          \
     cudaError_t e__ = cudaGetLastError();                       \
     if (e__ != cudaSuccess) return ::jb::cuda_fail(e__, name);  \
+    ::jb::count_launch();                                       \
   } while (0)
 
 // Device status word (one per device context, file-scope in api.cu).
 unsigned int* device_status_ptr();  // device address, resolved once per device
 int sm_count();
+void count_launch();  // bumps the per-process kernel-launch counter (jb200_kernel_launches)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
