@@ -159,6 +159,24 @@ int jb200_moe_metadata(const int64_t* topk_idx, int N, int K, int E, int32_t* ex
                        int32_t* expert_offsets, int32_t* scatter_map, int32_t* gather_map, int32_t* gate_idx_map,
                        void* scratch, void* stream);
 
+/* Same result as jb200_moe_metadata, but without a scratch argument and without any allocation.
+ * (No counterpart in the reference: its extension allocates its outputs and work buffers through
+ * torch on every call.)  It is meant for hosts that cannot hand this library device memory on
+ * demand -- for example an inference server that gives all device memory to its own arena at
+ * start-up and runs plugins with a fixed budget, or a latency-critical loop that must not reach
+ * cudaMalloc because that call stalls the whole device.  The work arrays live in a 128 KiB array
+ * built into the library (every GPU that loads the library carries it until the process exits),
+ * which limits N*K to jb200_moe_metadata_static_max_assignments() = 262144; larger inputs are
+ * refused with JB200_ERR_ARG.  The first call on each device looks up the array's device address
+ * (a host-side runtime query, nothing is allocated); make that first call during start-up, before
+ * any stream capture is begun.  All calls on a device share the one array: two calls whose kernels
+ * may overlap on the GPU (different streams, no ordering between them) race on it -- keep them on
+ * one stream or order them with events.  The caller still owns all inputs and outputs. */
+int jb200_moe_metadata_static_max_assignments(void);
+int jb200_moe_metadata_static(const int64_t* topk_idx, int N, int K, int E, int32_t* expert_counts,
+                              int32_t* expert_offsets, int32_t* scatter_map, int32_t* gather_map,
+                              int32_t* gate_idx_map, void* stream);
+
 /* dispatch_gather (sparse_model.cu:95-112): dispatched[slot][:] = x[gather_map[slot]][:], bf16 rows of C. */
 int jb200_moe_dispatch_gather(const void* x, const int32_t* gather_map, int M, int N, int C, void* dispatched,
                               void* stream);

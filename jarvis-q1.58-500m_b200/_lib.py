@@ -40,6 +40,8 @@ PROTOTYPES = {
     "jb200_router_top2": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "jb200_moe_metadata_scratch_bytes": (_Z, [_I, _I, _I]),
     "jb200_moe_metadata": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "jb200_moe_metadata_static_max_assignments": (_I, []),
+    "jb200_moe_metadata_static": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "jb200_moe_dispatch_gather": (_I, [_P, _P, _I, _I, _I, _P, _P]),
     "jb200_moe_scatter_combine": (_I, [_P, _P, _P, _I, _I, _I, _P, _I, _P, _P]),
     "jb200_moe_finalize": (_I, [_P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P]),

@@ -186,6 +186,15 @@ int jb200_moe_metadata(const int64_t* topk_idx, int N, int K, int E, int32_t* ex
                              scratch, static_cast<cudaStream_t>(stream));
 }
 
+int jb200_moe_metadata_static_max_assignments(void) { return moe_metadata_static_max_assignments(); }
+
+int jb200_moe_metadata_static(const int64_t* topk_idx, int N, int K, int E, int32_t* expert_counts,
+                              int32_t* expert_offsets, int32_t* scatter_map, int32_t* gather_map,
+                              int32_t* gate_idx_map, void* stream) {
+  return launch_moe_metadata_static(topk_idx, N, K, E, expert_counts, expert_offsets, scatter_map, gather_map,
+                                    gate_idx_map, static_cast<cudaStream_t>(stream));
+}
+
 int jb200_moe_dispatch_gather(const void* x, const int32_t* gather_map, int M, int N, int C, void* dispatched,
                               void* stream) {
   return launch_dispatch_gather(x, gather_map, M, N, C, dispatched, static_cast<cudaStream_t>(stream));

@@ -28,6 +28,10 @@ int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, 
 size_t moe_metadata_scratch_bytes(int n_tokens, int K, int E);
 int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts, int* expert_offsets,
                         int* scatter_map, int* gather_map, int* gate_idx_map, void* scratch, cudaStream_t stream);
+int moe_metadata_static_max_assignments();
+int launch_moe_metadata_static(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts,
+                               int* expert_offsets, int* scatter_map, int* gather_map, int* gate_idx_map,
+                               cudaStream_t stream);
 int launch_dispatch_gather(const void* x_bf16, const int* gather_map, int M, int n_tokens, int C, void* dispatched,
                            cudaStream_t stream);
 int launch_scatter_combine(const void* y_bf16, const float* gates, const int* scatter_map, int n_tokens, int K, int C,

@@ -328,6 +328,41 @@ int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int
   return JB200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the dispatch metadata: the two work arrays live in a fixed array
+// that is part of the library image, so the caller never has to provide (or allocate) scratch.
+// ---------------------------------------------------------------------------------------------
+constexpr int STATIC_META_MAX_ASSIGNMENTS = 1 << 18;                                 // N*K <= 262144
+constexpr int STATIC_META_MAX_CHUNKS = STATIC_META_MAX_ASSIGNMENTS / META_CHUNK;     // 1024
+static __device__ __align__(256) int g_meta_scratch[2 * STATIC_META_MAX_CHUNKS * MAX_E];  // 128 KiB per GPU
+static int* g_meta_scratch_ptr[64] = {nullptr};   // device address of the array, one per device ordinal
+
+int moe_metadata_static_max_assignments() { return STATIC_META_MAX_ASSIGNMENTS; }
+
+int launch_moe_metadata_static(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts,
+                               int* expert_offsets, int* scatter_map, int* gather_map, int* gate_idx_map,
+                               cudaStream_t stream) {
+  JB_REQUIRE(n_tokens >= 0 && K >= 1 && K <= 8, "moe_metadata_static: bad shape (N=%d, K=%d)", n_tokens, K);
+  JB_REQUIRE(size_t(n_tokens) * size_t(K) <= size_t(STATIC_META_MAX_ASSIGNMENTS),
+             "moe_metadata_static: N*K = %zu exceeds the built-in scratch limit of %d assignments; "
+             "use jb200_moe_metadata with caller-provided scratch",
+             size_t(n_tokens) * size_t(K), STATIC_META_MAX_ASSIGNMENTS);
+  int dev = 0;
+  JB_CUDA(cudaGetDevice(&dev));
+  JB_REQUIRE(dev >= 0 && dev < 64, "moe_metadata_static: device ordinal %d out of range", dev);
+  if (!g_meta_scratch_ptr[dev]) {
+    // First call on this device: resolve the array's DEVICE address.  In host code the name
+    // g_meta_scratch is only a handle for the runtime, not something a kernel may dereference.
+    int* ptr = nullptr;
+    JB_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_meta_scratch));
+    g_meta_scratch_ptr[dev] = ptr;
+  }
+  // Every entry the scan and assign kernels read is written by the histogram kernel of the same
+  // call first, so nothing left over from an earlier call needs clearing.
+  return launch_moe_metadata(topk_idx, n_tokens, K, E, expert_counts, expert_offsets, scatter_map, gather_map,
+                             gate_idx_map, g_meta_scratch_ptr[dev], stream);
+}
+
 int launch_dispatch_gather(const void* x_bf16, const int* gather_map, int M, int n_tokens, int C, void* dispatched,
                            cudaStream_t stream) {
   JB_REQUIRE(M >= 0 && n_tokens >= 0 && C > 0 && C % 8 == 0, "dispatch_gather: bad shape");
