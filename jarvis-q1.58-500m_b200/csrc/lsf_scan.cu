@@ -134,6 +134,16 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
     }
     carry = c;
     c = cn;
+    // residual values are loaded up front so that the read-modify-write does not serialise
+    float2 rold[TPW];
+    if (p.resid) {
+#pragma unroll
+      for (int i = 0; i < TPW; ++i) {
+        const int t = t0 + i;
+        rold[i] = (ch_ok && t < p.T) ? *reinterpret_cast<const float2*>(p.resid + seq_base + size_t(t) * p.D)
+                                     : make_float2(0.f, 0.f);
+      }
+    }
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {
       const int t = t0 + i;
@@ -144,13 +154,7 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
         const float hy = loc[i].y + fy * c.y;
         const size_t o = seq_base + size_t(t) * p.D;
         if (out) st2<TOut>(out + o, hx, hy);
-        if (p.resid) {
-          float2* r = reinterpret_cast<float2*>(p.resid + o);
-          float2 rv = *r;
-          rv.x += hx;
-          rv.y += hy;
-          *r = rv;
-        }
+        if (p.resid) *reinterpret_cast<float2*>(p.resid + o) = make_float2(rold[i].x + hx, rold[i].y + hy);
         if (t == p.T - 1 && p.h_last) *reinterpret_cast<float2*>(p.h_last + size_t(b) * p.D + ch) = make_float2(hx, hy);
       }
     }

@@ -287,10 +287,14 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
           for (int j = 0; j < 32; ++j)
             if (j < ntok) o[size_t(j) * p.N] = __float2bfloat16_rn(gelu_erf(alpha * __uint_as_float(v[j])));
         } else if (p.epilogue == JB200_EPI_RESID_F32) {
+          // all loads first: a read-modify-write per element would serialise on possible aliasing
           float* o = reinterpret_cast<float*>(p.out) + o0;
+          float old[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) old[j] = j < ntok ? __ldcs(o + size_t(j) * p.N) : 0.f;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (j < ntok) o[size_t(j) * p.N] += alpha * __uint_as_float(v[j]);
+            if (j < ntok) o[size_t(j) * p.N] = old[j] + alpha * __uint_as_float(v[j]);
         } else {  // JB200_EPI_F32
           float* o = reinterpret_cast<float*>(p.out) + o0;
 #pragma unroll

@@ -1,0 +1,166 @@
+#!/usr/bin/env python
+"""Per-kernel timing against the measured roofline (one kernel class per invocation).
+
+    python jarvis-q1.58-500m_b200/kernel_bench.py gemm --M 16384 --N 3072 --K 1024 [--groups 4] [--epilogue 0]
+    python jarvis-q1.58-500m_b200/kernel_bench.py attn --B 32 --H 16 --T 2048
+    python jarvis-q1.58-500m_b200/kernel_bench.py lsf  --B 32 --T 2048 --C 1024 [--resid]
+    python jarvis-q1.58-500m_b200/kernel_bench.py moe  --N 65536 [--zipf 1.2]
+
+Prints one JSON line: average launch time from CUDA events on the launching stream (3 warm-up
+launches, L2 flushed between timed launches by writing a 256 MiB buffer), algorithmic bytes or flops
+per launch and the fraction of the measured peak (MEASURED_PEAKS.json at the repository root, else the
+documented fallback).  The same command lines are what the ncu captures under profiles/ were taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import jarvis_b200  # noqa: E402
+from jarvis_b200 import _lib, ops  # noqa: E402
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            d = json.load(fh)
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters, flush=True):
+    scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            scratch.fill_(1)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        total += a.elapsed_time(b)
+    assert _lib.device_status() == 0
+    return total / iters
+
+
+def report(name, ms, *, bytes_=None, flops=None, extra=None):
+    hbm, tf, src = peaks()
+    out = {"kernel": name, "ms": ms}
+    if bytes_ is not None:
+        out.update(bound="hbm", achieved=bytes_ / ms / 1e6, peak=hbm, unit="GB/s", algorithmic_bytes=bytes_)
+    else:
+        out.update(bound="tensor", achieved=flops / ms / 1e9, peak=tf, unit="TFLOP/s", algorithmic_flops=flops)
+    out["frac"] = out["achieved"] / out["peak"]
+    out["peak_source"] = src + (" burst bf16" if flops is not None else " copy")
+    out.update(extra or {})
+    print(json.dumps(out), flush=True)
+
+
+def case_gemm(a):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    G = a.groups
+    x = torch.randn(a.M, a.K, generator=g, device="cuda").bfloat16()
+    codes = torch.randint(0, 3, (G, a.N, a.K // 4, 4), generator=g, device="cuda", dtype=torch.uint8)
+    packed = (codes[..., 0] | (codes[..., 1] << 2) | (codes[..., 2] << 4) | (codes[..., 3] << 6)).contiguous()
+    alpha = torch.full((G,), 0.016, device="cuda")
+    epi = a.epilogue
+    odt = torch.bfloat16 if epi in (0, 1) else torch.float32
+    out = torch.zeros(a.M, a.N, dtype=odt, device="cuda")
+    if G == 1:
+        fn = lambda: ops.ternary_linear(x, packed[0], alpha, epilogue=epi, out=out, token_tile=a.tile)  # noqa: E731
+    else:
+        cuts = torch.linspace(0, a.M, G + 1).round().to(torch.int32).cuda()
+        fn = lambda: ops.ternary_linear_grouped(x, packed, alpha, cuts, epilogue=epi, out=out, token_tile=a.tile)  # noqa: E731
+    ms = timeit(fn, a.iters)
+    report("ternary_gemm_kernel", ms, flops=2.0 * a.M * a.N * a.K, extra={"M": a.M, "N": a.N, "K": a.K, "groups": G,
+                                                                         "epilogue": epi, "token_tile": a.tile})
+
+
+def case_attn(a):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    C = a.H * 64
+    qkv = torch.randn(a.B * a.T, 3 * C, generator=g, device="cuda").bfloat16()
+    gamma = torch.rand(a.H, generator=g, device="cuda") * 0.099 + 0.9
+    t = torch.arange(a.T, dtype=torch.float32, device="cuda")
+    inv = 1.0 / (10000.0 ** (torch.arange(0, 64, 2, device="cuda").float() / 64))
+    fr = torch.outer(t, inv)
+    cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
+    o = torch.empty(a.B * a.T, C, dtype=torch.bfloat16, device="cuda")
+    fn = lambda: ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, a.B, a.T, a.H,  # noqa: E731
+                               want_state=True, out=o)
+    ms = timeit(fn, a.iters)
+    by = 512.0 * a.B * a.H * a.T + a.B * a.H * 64 * 64 * 4
+    report("attn_scan_kernel", ms, bytes_=by, extra={"B": a.B, "H": a.H, "T": a.T,
+                                                     "tflops_side": 32768.0 * a.B * a.H * a.T / ms / 1e9})
+
+
+def case_lsf(a):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    m = torch.randn(a.B, a.T, a.C, generator=g, device="cuda").bfloat16()
+    al = torch.tensor([0.95], device="cuda")
+    if a.resid:
+        r = torch.randn(a.B, a.T, a.C, generator=g, device="cuda")
+        fn = lambda: ops.lsf_scan(m, alpha_scalar=al, resid=r, want_out=False)  # noqa: E731
+        by = 10.0 * m.numel()
+    else:
+        fn = lambda: ops.lsf_scan(m, alpha_scalar=al)  # noqa: E731
+        by = 4.0 * m.numel()
+    ms = timeit(fn, a.iters)
+    report("lsf_scan_kernel", ms, bytes_=by, extra={"B": a.B, "T": a.T, "C": a.C, "fused_residual": bool(a.resid)})
+
+
+def case_moe(a):
+    """Config 4: one ternary top-2 MoE layer on N tokens, top-1 loads skewed Zipf(s) by a constant
+    input feature with per-expert router offsets."""
+    from jarvis_b200 import modules as jm
+    torch.manual_seed(0)
+    C = 1024
+    moe = jm.ternary_init_(jm.SparseMoELayer(C)).cuda().eval()
+    x = torch.randn(a.N, C, device="cuda")
+    x[:, 0] = 1.0
+    if a.zipf > 0:
+        w = torch.tensor([1.0 / (i + 1) ** a.zipf for i in range(4)])
+        with torch.no_grad():
+            moe.router.weight[:, 0] = (torch.log(w / w.sum()) * 1.6).cuda()
+    xb = x.bfloat16()
+    fn = lambda: moe.run_rows(xb)  # noqa: E731
+    ms = timeit(fn, a.iters)
+    counts = moe.last_routing[2][0].cpu().tolist()
+    report("moe_layer (router..combine)", ms, flops=2.0 * 2 * a.N * (2 * C * C) * 2,
+           extra={"N": a.N, "slot_counts": counts, "tokens_per_s": a.N / ms * 1e3})
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="case", required=True)
+    s = sub.add_parser("gemm")
+    s.add_argument("--M", type=int, default=16384); s.add_argument("--N", type=int, default=3072)
+    s.add_argument("--K", type=int, default=1024); s.add_argument("--groups", type=int, default=1)
+    s.add_argument("--epilogue", type=int, default=0); s.add_argument("--tile", type=int, default=0)
+    s = sub.add_parser("attn")
+    s.add_argument("--B", type=int, default=32); s.add_argument("--H", type=int, default=16)
+    s.add_argument("--T", type=int, default=2048)
+    s = sub.add_parser("lsf")
+    s.add_argument("--B", type=int, default=32); s.add_argument("--T", type=int, default=2048)
+    s.add_argument("--C", type=int, default=1024); s.add_argument("--resid", action="store_true")
+    s = sub.add_parser("moe")
+    s.add_argument("--N", type=int, default=65536); s.add_argument("--zipf", type=float, default=1.2)
+    for p in sub.choices.values():
+        p.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe}[a.case](a)
+
+
+if __name__ == "__main__":
+    main()

@@ -395,7 +395,11 @@ class Jarvis(nn.Module):
         w = self.lm_head.weight
         key = (w.data_ptr(), w._version)
         if self._lm_head_bf16 is None or self._lm_head_bf16[0] != key:
-            self._lm_head_bf16 = (key, w.detach().to(torch.bfloat16).contiguous())
+            # rows padded to a multiple of 128 so the library GEMM can use its aligned tensor-core kernels
+            v = w.shape[0]
+            wp = torch.zeros(((v + 127) // 128 * 128, w.shape[1]), dtype=torch.bfloat16, device=w.device)
+            wp[:v] = w.detach().to(torch.bfloat16)
+            self._lm_head_bf16 = (key, wp)
         return self._lm_head_bf16[1]
 
     def hidden_rows(self, idx, persist_state=False):
@@ -431,7 +435,9 @@ class Jarvis(nn.Module):
     def forward(self, idx, targets=None, persist_state=False):
         B, T = idx.shape
         hidden = self.hidden_rows(idx, persist_state)
-        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)   # dense bf16 lm_head (library GEMM)
+        vocab = self.lm_head.weight.shape[0]
+        # dense bf16 lm_head: a plain library GEMM; the padded columns are sliced off as a view
+        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)[..., :vocab]
         if self.logits_dtype != torch.bfloat16:
             logits = logits.to(self.logits_dtype)
         loss = None

@@ -131,7 +131,7 @@ def ternary_linear_grouped(x: torch.Tensor, packed: torch.Tensor, alpha: torch.T
         raise RuntimeError("ternary_linear_grouped: inconsistent shapes")
     if out is None:
         odt = torch.bfloat16 if epilogue in (EPI_BF16, EPI_GELU_BF16) else torch.float32
-        out = torch.zeros((M, N), dtype=odt, device=x.device)
+        out = torch.empty((M, N), dtype=odt, device=x.device)   # the segments cover every row
     _lib.check(
         lib.jb200_ternary_linear_grouped(_ptr(x), M, K, _ptr(packed), _ptr(alpha), N, G, _ptr(seg_offsets), epilogue,
                                          _ptr(out), token_tile, _stream()),
