@@ -98,9 +98,19 @@ int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, v
  * x: bf16 [M][K].  packed: u8 [N][K/4].  alpha: f32 [N / alpha_rows] (alpha_rows = N for the
  * per-tensor scale; several matrices stacked along N, e.g. q/k/v, each keep their own).
  * N % 128 == 0, K % 64 == 0, alpha_rows % 128 == 0.  out: per `epilogue`.
- * token_tile: 0 = choose, else one of 32/64/128/256. */
+ * token_tile: 0 = choose, else one of 32/64/128/256.
+ * w_layout: 0 = `packed` is the canonical weight_packing.py layout; 1 = `packed` was re-encoded by
+ * jb200_prepare_weights (same size, about 4x fewer decode instructions in the kernel). */
 int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
-                         int N, int epilogue, void* out, int token_tile, void* stream);
+                         int N, int epilogue, void* out, int token_tile, int w_layout, void* stream);
+
+/* One-time re-encoding of canonical packed weights for the GEMM's fast decode: still 2 bits per
+ * weight and the same byte count; inside each aligned group of 16 in-features (one 32-bit word) the
+ * even in-features move to the low half-word and the odd ones to the high half-word, each stored as
+ * (sign << 1 | nonzero).  Works on any number of whole words (n_bytes % 4 == 0), so stacked matrices
+ * can be converted in one call.  No counterpart in the reference (its prototype decodes byte by byte,
+ * experiments/architecture_matrix/ternary_packed/packed_kernel.cu:46-68). */
+int jb200_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, void* stream);
 
 /* Grouped form for the MoE experts: rows [seg_offsets[g], seg_offsets[g+1]) of x use weight
  * matrix g (packed: u8 [G][N][K/4], alpha: f32 [G]).  seg_offsets: i32 [G+1] on the DEVICE
@@ -109,7 +119,7 @@ int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, con
  * and loops over experts on the host (:159-164). */
 int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int N,
                                  int G, const int32_t* seg_offsets, int epilogue, void* out, int token_tile,
-                                 void* stream);
+                                 int w_layout, void* stream);
 
 /* ---- block glue --------------------------------------------------------------------- */
 
@@ -212,6 +222,9 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
  * (one little-endian u32 of the packed layout) -> 16 bf16 values in out8[8] (two per u32,
  * lower in-feature in the low half).  Runs on the CPU; used by the unit tests. */
 void jb200_host_decode16(uint32_t word, uint32_t* out8);
+/* Same for the prepared layout: takes the CANONICAL word, re-encodes it as jb200_prepare_weights does and
+ * decodes it as the kernel does; out8 holds 2 * {-1, 0, +1} as bf16 pairs. */
+void jb200_host_decode16_prepared(uint32_t word, uint32_t* out8);
 
 #ifdef __cplusplus
 }

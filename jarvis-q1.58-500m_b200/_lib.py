@@ -33,7 +33,9 @@ PROTOTYPES = {
     "jb200_pack_ternary": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "jb200_pack_codes": (_I, [_P, _Z, _P, _P]),
     "jb200_unpack_ternary": (_I, [_P, _Z, _I, _P, _P]),
-    "jb200_ternary_linear": (_I, [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _P]),
+    "jb200_ternary_linear": (_I, [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P]),
+    "jb200_prepare_weights": (_I, [_P, _Z, _P, _P]),
+    "jb200_host_decode16_prepared": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
     "jb200_rmsnorm": (_I, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "jb200_embedding": (_I, [_P, _P, _I, _P, _I, _I, _P]),
     "jb200_attn_scan": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
@@ -47,7 +49,7 @@ PROTOTYPES = {
     "jb200_moe_finalize": (_I, [_P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P]),
     "jb200_lsf_scan": (_I, [_P, _I, _P, _P, _P, _P, _F, _F, _P, _P, _P, _I, _P, _I, _I, _I, _P]),
     "jb200_host_decode16": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
-    "jb200_ternary_linear_grouped": (_I, [_P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _P]),
+    "jb200_ternary_linear_grouped": (_I, [_P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _P]),
 }
 
 

@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 1; }
+int jb200_abi_version(void) { return 2; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -142,15 +142,15 @@ int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, v
 }
 
 int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
-                         int N, int epilogue, void* out, int token_tile, void* stream) {
-  return launch_ternary_gemm(x, M, K, packed, alpha, alpha_rows, N, 1, nullptr, epilogue, out, token_tile,
+                         int N, int epilogue, void* out, int token_tile, int w_layout, void* stream) {
+  return launch_ternary_gemm(x, M, K, packed, alpha, alpha_rows, N, 1, nullptr, epilogue, out, token_tile, w_layout,
                              static_cast<cudaStream_t>(stream));
 }
 
 int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int N,
                                  int G, const int32_t* seg_offsets, int epilogue, void* out, int token_tile,
-                                 void* stream) {
-  return launch_ternary_gemm(x, M, K, packed, alpha, N, N, G, seg_offsets, epilogue, out, token_tile,
+                                 int w_layout, void* stream) {
+  return launch_ternary_gemm(x, M, K, packed, alpha, N, N, G, seg_offsets, epilogue, out, token_tile, w_layout,
                              static_cast<cudaStream_t>(stream));
 }
 
@@ -219,6 +219,11 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
                          out, out_dtype, h_last, B, T, D, static_cast<cudaStream_t>(stream));
 }
 
+int jb200_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, void* stream) {
+  return launch_prepare_weights(packed, n_bytes, prepared, static_cast<cudaStream_t>(stream));
+}
+
 void jb200_host_decode16(uint32_t word, uint32_t* out8) { decode16_host(word, out8); }
+void jb200_host_decode16_prepared(uint32_t word, uint32_t* out8) { decode16_prepared_host(word, out8); }
 
 }  // extern "C"

@@ -15,8 +15,10 @@ int launch_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, 
 
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
-                        int bn_override, cudaStream_t stream);
+                        int bn_override, int w_layout, cudaStream_t stream);
+int launch_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, cudaStream_t stream);
 void decode16_host(uint32_t w, uint32_t* out8);
+void decode16_prepared_host(uint32_t w_canonical, uint32_t* out8);
 
 int launch_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* y, int y_dtype, int n_rows, int C,
                    cudaStream_t stream);

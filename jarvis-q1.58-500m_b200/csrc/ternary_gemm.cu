@@ -19,10 +19,20 @@
 //   warp 0      TMA producer for the activation tiles (+ TMEM allocation)
 //   warp 1      MMA issuer (one elected lane)
 //   warps 2-5   weight decoders: thread r owns weight row r of the tile
-//   warps 6-9   epilogue: TMEM -> registers -> alpha / GELU / residual -> HBM
+//   warps 6-9   epilogue: TMEM -> registers -> alpha / GELU -> smem transpose -> 16-byte row stores / residual add
 // Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Token rows may be split into segments (one per expert), each
 // with its own weight matrix and alpha: the grouped form used by the MoE experts.
+//
+// Two 2-bit weight layouts are accepted (w_layout):
+//   0  canonical, exactly runtime/weight_packing.py (code k of a row at bits 2*(k%4) of byte k/4,
+//      0 -> 0, 1 -> +1, 2 -> -1): decoded with a nibble spread + PRMT byte tables (~8 ops / 2 weights);
+//   1  prepared (jb200_prepare_weights, a one-time re-encoding of the same 2 bits per weight): inside
+//      every 32-bit word the even in-features sit in the low half and the odd ones in the high half,
+//      each as (sign << 1 | nonzero), so (w << (14 - 2j)) & 0xC000C000 IS the bf16 pair
+//      {0, +2.0, -2.0} for in-features (2j, 2j+1): 2 ops / 2 weights; the factor 2 is folded into alpha.
+// The decoders share the SM's issue slots with the epilogue, and the kernel is issue-bound, so the
+// instruction count of the decode is what sets the tensor-pipe utilisation.
 #include "common.cuh"
 
 namespace jb {
@@ -48,6 +58,7 @@ struct GemmParams {
   int alpha_rows;            // out-feature rows sharing one alpha (N for per-tensor)
   int bn;                    // token tile
   int epilogue;
+  int w_layout;              // 0 canonical weight_packing.py layout, 1 prepared layout
   unsigned int* status;
 };
 
@@ -61,8 +72,9 @@ struct SmemCtl {
   int32_t seg[MAX_GROUPS + 1];
 };
 
+constexpr int STAGE_OUT_BYTES = 32 * 32 * 4;     // one epilogue warp's [32 tokens][32 features] f32 block
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + size_t(STAGES) * (A_STAGE_BYTES + B_STAGE_BYTES) +
-                              sizeof(SmemCtl);
+                              ((sizeof(SmemCtl) + 127) / 128) * 128 + 4 * STAGE_OUT_BYTES;
 
 struct TileCoord {
   int group;     // segment / expert
@@ -124,7 +136,34 @@ __host__ __device__ __forceinline__ void decode16(uint32_t w, uint32_t* out) {
   }
 }
 
-__device__ __forceinline__ float gelu_erf(float v) { return 0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)); }
+// Prepared layout: canonical word -> prepared word (host + device; the one-time re-encoding).
+__host__ __device__ __forceinline__ uint32_t prepare_word(uint32_t w) {
+  uint32_t out = 0;
+  for (int k = 0; k < 16; ++k) {
+    const uint32_t c = (w >> (2 * k)) & 3u;
+    const uint32_t f = c == 1u ? 1u : (c == 2u ? 3u : 0u);          // (sign << 1) | nonzero
+    out |= f << ((k & 1) * 16 + (k >> 1) * 2);
+  }
+  return out;
+}
+// Prepared word -> 8 bf16 pairs holding 2 * {-1, 0, +1}.
+__host__ __device__ __forceinline__ void decode16_prepared(uint32_t w, uint32_t* out) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) out[j] = (w << (14 - 2 * j)) & 0xC000C000u;
+}
+
+// Exact-erf GELU (F.gelu default) with erf from Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7, far
+// below the bf16 rounding of the result); erff itself costs ~3x the instructions in an issue-bound epilogue.
+__device__ __forceinline__ float gelu_erf(float v) {
+  const float ax = fabsf(v) * 0.70710678118654752440f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  const float erf_abs = 1.0f - poly * t * __expf(-ax * ax);
+  return 0.5f * v * (1.0f + copysignf(erf_abs, v));
+}
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
@@ -244,7 +283,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           uint32_t v[8];
-          decode16(words[wi], v);
+          if (p.w_layout) decode16_prepared(words[wi], v); else decode16(words[wi], v);
           const uint32_t c0 = uint32_t(2 * wi), c1 = uint32_t(2 * wi + 1);
           *reinterpret_cast<uint4*>(arow + ((c0 ^ swz) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
           *reinterpret_cast<uint4*>(arow + ((c1 ^ swz) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
@@ -257,6 +296,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
   } else {
     // ---------------- epilogue ----------------
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    uint8_t* stage_base = reinterpret_cast<uint8_t*>(ctl) + ((sizeof(SmemCtl) + 127) / 128) * 128;
     uint32_t tile_n = 0;
     TileCoord tc;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_n) {
@@ -267,7 +307,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         goto done;
       tc_fence_after_sync();
       const int feat = tc.ft * BM + q * 32 + lane;
-      const float alpha = __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows);
+      uint8_t* stage = stage_base + (warp - 6) * STAGE_OUT_BYTES;
+      const float alpha = __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows) *
+                          (p.w_layout ? 0.5f : 1.0f);   // prepared weights decode to +-2
       const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MAX;
       for (int c0 = 0; c0 < bn; c0 += 32) {
         if (tc.tok0 + c0 >= tc.tok_end) break;   // warp-uniform
@@ -275,32 +317,53 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         tmem_ld_32x32(t_lane + c0, v);
         tmem_ld_wait();
         const int ntok = min(32, tc.tok_end - (tc.tok0 + c0));
-        const size_t o0 = size_t(tc.tok0 + c0) * p.N + feat;
-        if (p.epilogue == JB200_EPI_BF16) {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + o0;
+        // The accumulator chunk is lane = out-feature, register = token; HBM wants token rows.  Turn
+        // it through this warp's staging block in shared memory ([32 tokens][32 features]) so that
+        // global memory sees 16-byte accesses on whole 64 B / 128 B row segments.
+        const int f0 = tc.ft * BM + q * 32;
+        const size_t row0 = size_t(tc.tok0 + c0);
+        if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16) {
+          const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;
+          __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ntok) o[size_t(j) * p.N] = __float2bfloat16_rn(alpha * __uint_as_float(v[j]));
-        } else if (p.epilogue == JB200_EPI_GELU_BF16) {
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + o0;
+          for (int j = 0; j < 32; ++j) {
+            float a = alpha * __uint_as_float(v[j]);
+            if (gelu) a = gelu_erf(a);
+            st[j * 32 + lane] = __float2bfloat16_rn(a);
+          }
+          __syncwarp();
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out);
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ntok) o[size_t(j) * p.N] = __float2bfloat16_rn(gelu_erf(alpha * __uint_as_float(v[j])));
-        } else if (p.epilogue == JB200_EPI_RESID_F32) {
-          // all loads first: a read-modify-write per element would serialise on possible aliasing
-          float* o = reinterpret_cast<float*>(p.out) + o0;
-          float old[32];
+          for (int it = 0; it < 4; ++it) {
+            const int idx = it * 32 + lane, r = idx >> 2, c16 = idx & 3;
+            const uint4 w4 = *reinterpret_cast<const uint4*>(st + r * 32 + c16 * 8);
+            if (r < ntok) *reinterpret_cast<uint4*>(o + (row0 + r) * p.N + f0 + c16 * 8) = w4;
+          }
+        } else {
+          const bool resid = p.epilogue == JB200_EPI_RESID_F32;
+          float* st = reinterpret_cast<float*>(stage);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) old[j] = j < ntok ? __ldcs(o + size_t(j) * p.N) : 0.f;
+          for (int j = 0; j < 32; ++j) st[j * 32 + lane] = alpha * __uint_as_float(v[j]);
+          __syncwarp();
+          float* o = reinterpret_cast<float*>(p.out);
+          float4 old[8];
+          if (resid) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ntok) o[size_t(j) * p.N] = old[j] + alpha * __uint_as_float(v[j]);
-        } else {  // JB200_EPI_F32
-          float* o = reinterpret_cast<float*>(p.out) + o0;
+            for (int it = 0; it < 8; ++it) {
+              const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
+              old[it] = r < ntok ? __ldcs(reinterpret_cast<const float4*>(o + (row0 + r) * p.N + f0 + c16 * 4))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+          }
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (j < ntok) o[size_t(j) * p.N] = alpha * __uint_as_float(v[j]);
+          for (int it = 0; it < 8; ++it) {
+            const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
+            float4 w4 = *reinterpret_cast<const float4*>(st + r * 32 + c16 * 4);
+            if (resid) { w4.x += old[it].x; w4.y += old[it].y; w4.z += old[it].z; w4.w += old[it].w; }
+            if (r < ntok) *reinterpret_cast<float4*>(o + (row0 + r) * p.N + f0 + c16 * 4) = w4;
+          }
         }
+        __syncwarp();   // staging block is reused by the next chunk
       }
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
@@ -349,7 +412,7 @@ int pick_bn(int M, int G, int n_ft, int sms) {
 
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
-                        int bn_override, cudaStream_t stream) {
+                        int bn_override, int w_layout, cudaStream_t stream) {
   JB_REQUIRE(M >= 0 && N > 0 && K > 0, "ternary_linear: bad sizes M=%d N=%d K=%d", M, N, K);
   JB_REQUIRE(N % BM == 0, "ternary_linear: out_features (%d) must be a multiple of %d", N, BM);
   JB_REQUIRE(K % BK == 0, "ternary_linear: in_features (%d) must be a multiple of %d", K, BK);
@@ -358,6 +421,7 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   JB_REQUIRE(alpha_rows > 0 && alpha_rows % BM == 0 && N % alpha_rows == 0,
              "ternary_linear: alpha_rows (%d) must be a multiple of %d dividing out_features", alpha_rows, BM);
   JB_REQUIRE(epilogue >= JB200_EPI_BF16 && epilogue <= JB200_EPI_F32, "ternary_linear: unknown epilogue %d", epilogue);
+  JB_REQUIRE(w_layout == 0 || w_layout == 1, "ternary_linear: weight layout must be 0 (canonical) or 1 (prepared)");
   JB_REQUIRE(x_bf16 && w_packed && alpha && out, "ternary_linear: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_packed) && aligned16(out), "ternary_linear: pointers must be 16-byte aligned");
   if (M == 0) return JB200_OK;
@@ -394,6 +458,7 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   p.alpha_rows = alpha_rows;
   p.bn = bn;
   p.epilogue = epilogue;
+  p.w_layout = w_layout;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
 
@@ -409,7 +474,30 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   return JB200_OK;
 }
 
-// Host-side view of the in-kernel decode, for the CPU unit test of the bit manipulation.
+// Host-side views of the in-kernel decodes, for the CPU unit test of the bit manipulation.
 void decode16_host(uint32_t w, uint32_t* out8) { decode16(w, out8); }
+void decode16_prepared_host(uint32_t w_canonical, uint32_t* out8) { decode16_prepared(prepare_word(w_canonical), out8); }
+
+namespace {
+__global__ void prepare_weights_kernel(const uint32_t* __restrict__ in, size_t n_words, uint32_t* __restrict__ out) {
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n_words; i += size_t(gridDim.x) * blockDim.x)
+    out[i] = prepare_word(__ldg(in + i));
+}
+}  // namespace
+
+int launch_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, cudaStream_t stream) {
+  JB_REQUIRE(n_bytes % 4 == 0, "prepare_weights: byte count must be a multiple of 4 (16 weights per word)");
+  JB_REQUIRE(packed && prepared, "prepare_weights: null pointer");
+  JB_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 3u) == 0 && (reinterpret_cast<uintptr_t>(prepared) & 3u) == 0,
+             "prepare_weights: pointers must be 4-byte aligned");
+  if (n_bytes == 0) return JB200_OK;
+  const size_t n_words = n_bytes / 4;
+  size_t blocks = (n_words + 255) / 256;
+  if (blocks > 4096) blocks = 4096;
+  prepare_weights_kernel<<<unsigned(blocks), 256, 0, stream>>>(reinterpret_cast<const uint32_t*>(packed), n_words,
+                                                              reinterpret_cast<uint32_t*>(prepared));
+  JB_LAUNCH_CHECK("prepare_weights_kernel");
+  return JB200_OK;
+}
 
 }  // namespace jb

@@ -73,18 +73,23 @@ def case_gemm(a):
     x = torch.randn(a.M, a.K, generator=g, device="cuda").bfloat16()
     codes = torch.randint(0, 3, (G, a.N, a.K // 4, 4), generator=g, device="cuda", dtype=torch.uint8)
     packed = (codes[..., 0] | (codes[..., 1] << 2) | (codes[..., 2] << 4) | (codes[..., 3] << 6)).contiguous()
+    if a.prepared:
+        packed = ops.prepare_weights(packed)
     alpha = torch.full((G,), 0.016, device="cuda")
     epi = a.epilogue
     odt = torch.bfloat16 if epi in (0, 1) else torch.float32
     out = torch.zeros(a.M, a.N, dtype=odt, device="cuda")
     if G == 1:
-        fn = lambda: ops.ternary_linear(x, packed[0], alpha, epilogue=epi, out=out, token_tile=a.tile)  # noqa: E731
+        fn = lambda: ops.ternary_linear(x, packed[0], alpha, epilogue=epi, out=out, token_tile=a.tile,
+                                        prepared=a.prepared)  # noqa: E731
     else:
         cuts = torch.linspace(0, a.M, G + 1).round().to(torch.int32).cuda()
-        fn = lambda: ops.ternary_linear_grouped(x, packed, alpha, cuts, epilogue=epi, out=out, token_tile=a.tile)  # noqa: E731
+        fn = lambda: ops.ternary_linear_grouped(x, packed, alpha, cuts, epilogue=epi, out=out, token_tile=a.tile,
+                                                prepared=a.prepared)  # noqa: E731
     ms = timeit(fn, a.iters)
     report("ternary_gemm_kernel", ms, flops=2.0 * a.M * a.N * a.K, extra={"M": a.M, "N": a.N, "K": a.K, "groups": G,
-                                                                         "epilogue": epi, "token_tile": a.tile})
+                                                                         "epilogue": epi, "token_tile": a.tile,
+                                                                         "prepared_layout": bool(a.prepared)})
 
 
 def case_attn(a):
@@ -148,6 +153,7 @@ def main():
     s.add_argument("--M", type=int, default=16384); s.add_argument("--N", type=int, default=3072)
     s.add_argument("--K", type=int, default=1024); s.add_argument("--groups", type=int, default=1)
     s.add_argument("--epilogue", type=int, default=0); s.add_argument("--tile", type=int, default=0)
+    s.add_argument("--canonical", dest="prepared", action="store_false", help="decode the weight_packing.py layout in-kernel")
     s = sub.add_parser("attn")
     s.add_argument("--B", type=int, default=32); s.add_argument("--H", type=int, default=16)
     s.add_argument("--T", type=int, default=2048)

@@ -35,18 +35,22 @@ class RMSNorm(nn.Module):
 
 
 class _PackCache:
-    """Packed form of one or more fp32 weight matrices, rebuilt when any of them changes."""
+    """Packed form of one or more fp32 weight matrices, rebuilt when any of them changes.  `packed` is
+    kept in the GEMM's prepared layout (ops.prepare_weights of the canonical weight_packing.py bytes);
+    `canonical` keeps the interchange layout."""
 
     def __init__(self):
         self.key = None
         self.packed = None
+        self.canonical = None
         self.alpha = None
 
     def get(self, weights, stack: bool):
         key = tuple((w.data_ptr(), w._version, w.device) for w in weights)
         if key != self.key:
             pa = [ops.pack_ternary(w.detach().float().contiguous()) for w in weights]
-            self.packed = torch.stack([p for p, _ in pa]) if stack else torch.cat([p for p, _ in pa])
+            self.canonical = torch.stack([p for p, _ in pa]) if stack else torch.cat([p for p, _ in pa])
+            self.packed = ops.prepare_weights(self.canonical)
             self.alpha = torch.cat([a for _, a in pa])
             self.key = key
         return self.packed, self.alpha
@@ -70,9 +74,9 @@ class TernaryLinear(nn.Module):
         packed, alpha = self.packed()
         x2 = x.reshape(-1, x.shape[-1]).to(torch.bfloat16).contiguous()
         if x.dtype == torch.float32:
-            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_F32)
+            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_F32, prepared=True)
         else:
-            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_BF16).to(x.dtype)
+            y = ops.ternary_linear(x2, packed, alpha, epilogue=ops.EPI_BF16, prepared=True).to(x.dtype)
         y = y.view(*x.shape[:-1], -1)
         return y if self.bias is None else y + self.bias
 
@@ -153,7 +157,7 @@ class AssociativeLinearAttention(nn.Module):
         """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None)."""
         C = xn_rows.shape[1]
         packed, alpha = self.qkv_packed()
-        qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C)
+        qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C, prepared=True)
         end = (int(start_pos.max()) if torch.is_tensor(start_pos) else int(start_pos)) + T
         cos, sin = self.rotary.half_tables(end, xn_rows.device)
         gamma = torch.sigmoid(self.gamma_raw.detach().float())
@@ -172,8 +176,8 @@ class AssociativeLinearAttention(nn.Module):
         o, _ = self.scan_rows(_as_rows_bf16(x), B, T, start_pos, h_prev)
         packed, alpha = self.out_proj.packed()
         if x.dtype == torch.float32:
-            return ops.ternary_linear(o, packed, alpha, epilogue=ops.EPI_F32).view(B, T, C)
-        return ops.ternary_linear(o, packed, alpha).view(B, T, C).to(x.dtype)
+            return ops.ternary_linear(o, packed, alpha, epilogue=ops.EPI_F32, prepared=True).view(B, T, C)
+        return ops.ternary_linear(o, packed, alpha, prepared=True).view(B, T, C).to(x.dtype)
 
 
 CUDAAssociativeLinearAttention = AssociativeLinearAttention
@@ -222,8 +226,8 @@ class SparseMoELayer(nn.Module):
         counts, offsets, scatter, gather, gate_idx = meta
         (p1, a1), (p2, a2) = self.packed()
         disp = ops.dispatch_gather(xn_rows, gather)
-        hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16)
-        y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16)
+        hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
+        y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16, prepared=True)
         out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
         scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, N, N * C, self.balance_alpha)
         self.last_routing = (idx, gates, meta)
@@ -330,7 +334,7 @@ class JarvisBlock(nn.Module):
         xn = ops.rmsnorm(x, self.norm1.weight.detach().float(), self.norm1.eps)
         o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state)
         po, ao = self.attn.out_proj.packed()
-        ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x)          # x += attn(norm1(x))
+        ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)          # x += attn(norm1(x))
         xn = ops.rmsnorm(x, self.norm2.weight.detach().float(), self.norm2.eps)
         moe_out, scalars = self.moe.run_rows(xn)
         _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],

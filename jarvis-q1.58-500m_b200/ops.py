@@ -86,9 +86,20 @@ def unpack_ternary(packed: torch.Tensor, shape, dtype=torch.bfloat16) -> torch.T
     return out.reshape(tuple(shape))
 
 
+def prepare_weights(packed: torch.Tensor) -> torch.Tensor:
+    """Canonical packed weights -> the GEMM's fast-decode layout (same shape and size)."""
+    lib = _lib.load()
+    _need(packed, torch.uint8, "prepare_weights.packed")
+    out = torch.empty_like(packed)
+    _lib.check(lib.jb200_prepare_weights(_ptr(packed), packed.numel(), _ptr(out), _stream()), "jb200_prepare_weights")
+    return out
+
+
 def ternary_linear(x: torch.Tensor, packed: torch.Tensor, alpha: torch.Tensor, *, epilogue: int = EPI_BF16,
-                   out: torch.Tensor | None = None, alpha_rows: int | None = None, token_tile: int = 0):
-    """epilogue(alpha * x @ unpack(packed)^T): x bf16 (M, K), packed uint8 (N, K/4)."""
+                   out: torch.Tensor | None = None, alpha_rows: int | None = None, token_tile: int = 0,
+                   prepared: bool = False):
+    """epilogue(alpha * x @ unpack(packed)^T): x bf16 (M, K), packed uint8 (N, K/4) in the canonical
+    layout, or in the prepare_weights layout when prepared=True."""
     lib = _lib.load()
     _need(x, torch.bfloat16, "ternary_linear.x")
     _need(packed, torch.uint8, "ternary_linear.packed")
@@ -110,14 +121,15 @@ def ternary_linear(x: torch.Tensor, packed: torch.Tensor, alpha: torch.Tensor, *
             raise RuntimeError("ternary_linear: out has the wrong shape")
     _lib.check(
         lib.jb200_ternary_linear(_ptr(x), M, K, _ptr(packed), _ptr(alpha), alpha_rows, N, epilogue, _ptr(out),
-                                 token_tile, _stream()),
+                                 token_tile, 1 if prepared else 0, _stream()),
         "jb200_ternary_linear",
     )
     return out
 
 
 def ternary_linear_grouped(x: torch.Tensor, packed: torch.Tensor, alpha: torch.Tensor, seg_offsets: torch.Tensor, *,
-                           epilogue: int = EPI_BF16, out: torch.Tensor | None = None, token_tile: int = 0):
+                           epilogue: int = EPI_BF16, out: torch.Tensor | None = None, token_tile: int = 0,
+                           prepared: bool = False):
     """Rows [seg_offsets[g], seg_offsets[g+1]) of x (bf16 (M, K)) go through weight g of
     packed (uint8 (G, N, K/4)) with scale alpha[g]."""
     lib = _lib.load()
@@ -134,7 +146,7 @@ def ternary_linear_grouped(x: torch.Tensor, packed: torch.Tensor, alpha: torch.T
         out = torch.empty((M, N), dtype=odt, device=x.device)   # the segments cover every row
     _lib.check(
         lib.jb200_ternary_linear_grouped(_ptr(x), M, K, _ptr(packed), _ptr(alpha), N, G, _ptr(seg_offsets), epilogue,
-                                         _ptr(out), token_tile, _stream()),
+                                         _ptr(out), token_tile, 1 if prepared else 0, _stream()),
         "jb200_ternary_linear_grouped",
     )
     return out

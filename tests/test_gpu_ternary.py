@@ -51,7 +51,7 @@ def test_pack_codes_patterns():
         assert torch.equal(ops.unpack_ternary(packed, pat.shape, torch.float32).cpu(), pat)
 
 
-def _gemm_case(M, K, N, seed, epilogue=ops.EPI_BF16, token_tile=0):
+def _gemm_case(M, K, N, seed, epilogue=ops.EPI_BF16, token_tile=0, prepared=False):
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(M, K, generator=g).bfloat16()
     w = torch.randn(N, K, generator=g) * 0.02
@@ -60,8 +60,9 @@ def _gemm_case(M, K, N, seed, epilogue=ops.EPI_BF16, token_tile=0):
     ref = orc.ternary_linear(x.float(), q, alpha)
     if epilogue == ops.EPI_GELU_BF16:
         ref = torch.nn.functional.gelu(ref)
-    y = ops.ternary_linear(x.cuda(), packed.cuda(), torch.tensor([alpha]).cuda(), epilogue=epilogue,
-                           token_tile=token_tile)
+    pk = ops.prepare_weights(packed.cuda()) if prepared else packed.cuda()
+    y = ops.ternary_linear(x.cuda(), pk, torch.tensor([alpha]).cuda(), epilogue=epilogue,
+                           token_tile=token_tile, prepared=prepared)
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
     return rel_l2(y.float().cpu(), ref)
@@ -71,6 +72,7 @@ def _gemm_case(M, K, N, seed, epilogue=ops.EPI_BF16, token_tile=0):
                                    (777, 2048, 1024), (1024, 1024, 3072), (33, 64, 128)])
 def test_ternary_linear_matches_fp32(M, K, N):
     assert _gemm_case(M, K, N, seed=M + K + N) <= REL_L2_TOL
+    assert _gemm_case(M, K, N, seed=M + K + N, prepared=True) <= REL_L2_TOL
 
 
 @pytest.mark.parametrize("tile", [32, 64, 128, 256])
@@ -80,6 +82,8 @@ def test_ternary_linear_token_tiles(tile):
 
 def test_ternary_linear_epilogues():
     assert _gemm_case(300, 1024, 2048, seed=5, epilogue=ops.EPI_GELU_BF16) <= REL_L2_TOL
+    assert _gemm_case(301, 1024, 2048, seed=5, epilogue=ops.EPI_GELU_BF16, prepared=True) <= REL_L2_TOL
+    assert _gemm_case(299, 512, 256, seed=8, epilogue=ops.EPI_BF16, prepared=True) <= REL_L2_TOL
     assert _gemm_case(300, 1024, 1024, seed=6, epilogue=ops.EPI_F32) <= 5e-3
     # residual epilogue: out += alpha * acc
     g = torch.Generator().manual_seed(7)
@@ -103,6 +107,32 @@ def test_ternary_linear_exact_on_integers():
     q = torch.randint(-1, 2, (N, K), generator=g).float()
     y = ops.ternary_linear(x.bfloat16().cuda(), orc.pack_ternary(q).cuda(), torch.ones(1).cuda(), epilogue=ops.EPI_F32)
     assert torch.equal(y.cpu(), x @ q.t())
+    # prepared layout: same result bit for bit (values decode to +-2, alpha is halved: both exact)
+    prep = ops.prepare_weights(orc.pack_ternary(q).cuda())
+    y2 = ops.ternary_linear(x.bfloat16().cuda(), prep, torch.ones(1).cuda(), epilogue=ops.EPI_F32, prepared=True)
+    assert torch.equal(y2.cpu(), x @ q.t())
+    # bf16 outputs through the paired-store epilogue (integers up to 256 are exact in bf16 for |y| small)
+    xs = torch.randint(-1, 2, (M, 64), generator=g).float()
+    qs = torch.randint(-1, 2, (N, 64), generator=g).float()
+    for prepared in (False, True):
+        pk = orc.pack_ternary(qs).cuda()
+        pk = ops.prepare_weights(pk) if prepared else pk
+        yb = ops.ternary_linear(xs.bfloat16().cuda(), pk, torch.ones(1).cuda(), prepared=prepared)
+        assert torch.equal(yb.float().cpu(), xs @ qs.t())
+
+
+def test_prepare_weights_is_a_bit_permutation():
+    g = torch.Generator().manual_seed(13)
+    q = torch.randint(-1, 2, (64, 256), generator=g).float()
+    packed = orc.pack_ternary(q)
+    prep = ops.prepare_weights(packed.cuda()).cpu()
+    assert prep.shape == packed.shape
+    w = packed.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    pw = prep.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    for k in range(16):
+        c = (w >> (2 * k)) & 3
+        f = (pw >> ((k & 1) * 16 + (k >> 1) * 2)) & 3
+        assert torch.equal(f, torch.where(c == 1, 1, torch.where(c == 2, 3, 0)))
 
 
 def test_stacked_alphas():
@@ -131,6 +161,9 @@ def test_grouped_ternary_linear(counts):
                                    epilogue=ops.EPI_F32)
     ref = torch.cat([alphas[e] * (x[offs[e]:offs[e + 1]] @ q[e].t()) for e in range(G)])
     assert torch.equal(y.cpu(), ref)
+    yp = ops.ternary_linear_grouped(x.bfloat16().cuda(), ops.prepare_weights(orc.pack_ternary(q).cuda()), alphas.cuda(),
+                                    offs.cuda(), epilogue=ops.EPI_BF16, prepared=True)
+    assert torch.equal(yp.float().cpu(), ref.bfloat16().float())
     assert _lib.device_status() == 0
 
 
