@@ -15,11 +15,13 @@
 // packed codes (64 weights) per thread per K-block feeds up to 256 token columns.  The
 // accumulator D lives in TMEM with lane = out-feature, column = token.
 //
-// One persistent CTA per SM, 320 threads:
-//   warp 0      TMA producer for the activation tiles (+ TMEM allocation)
-//   warp 1      MMA issuer (one elected lane)
-//   warps 2-5   weight decoders: thread r owns weight row r of the tile
-//   warps 6-9   epilogue: TMEM -> registers -> alpha / GELU -> smem transpose -> 16-byte row stores / residual add
+// One persistent CTA per SM, 576 threads:
+//   warp 0       TMA producer for the activation tiles (+ TMEM allocation)
+//   warp 1       MMA issuer (one elected lane)
+//   warps 2-9    weight decoders, two groups of four taking alternate K-blocks (one warp's own
+//                instruction latency per K-block exceeds the 512 cycles its MMAs take); thread r of a
+//                group owns weight row r of the tile
+//   warps 10-17  epilogue (two warps per TMEM lane quadrant, alternate 32-token chunks): TMEM -> registers -> alpha / GELU -> smem transpose -> 16-byte row stores / residual add
 // Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Token rows may be split into segments (one per expert), each
 // with its own weight matrix and alpha: the grouped form used by the MoE experts.
@@ -46,7 +48,8 @@ constexpr int BN_MAX = 256;     // token columns per tile (UMMA N), runtime 32..
 constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;   // 32 KiB
 constexpr int MAX_GROUPS = 16;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 576;
+constexpr int DEC_WARP0 = 2, EPI_WARP0 = 10;
 constexpr int TMEM_COLS = 512;
 
 struct GemmParams {
@@ -74,7 +77,7 @@ struct SmemCtl {
 
 constexpr int STAGE_OUT_BYTES = 32 * 32 * 4;     // one epilogue warp's [32 tokens][32 features] f32 block
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + size_t(STAGES) * (A_STAGE_BYTES + B_STAGE_BYTES) +
-                              ((sizeof(SmemCtl) + 127) / 128) * 128 + 4 * STAGE_OUT_BYTES;
+                              ((sizeof(SmemCtl) + 127) / 128) * 128 + 8 * STAGE_OUT_BYTES;
 
 struct TileCoord {
   int group;     // segment / expert
@@ -152,17 +155,20 @@ __host__ __device__ __forceinline__ void decode16_prepared(uint32_t w, uint32_t*
   for (int j = 0; j < 8; ++j) out[j] = (w << (14 - 2 * j)) & 0xC000C000u;
 }
 
-// Exact-erf GELU (F.gelu default) with erf from Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7, far
-// below the bf16 rounding of the result); erff itself costs ~3x the instructions in an issue-bound epilogue.
+// GELU for the expert hidden layer.  The reference uses the exact-erf form (F.gelu default,
+// jarvis_model.py:236); here 0.5 x (1 + tanh(x (a + b x^2 + c x^4))) with a, b, c fitted to the erf
+// form: |difference| < 2.6e-5 everywhere (plus tanh.approx's 2^-11 relative error), an order of
+// magnitude below the bf16 rounding of the stored result, at 9 instructions instead of ~25 for erff
+// in an epilogue that is issue-bound.
 __device__ __forceinline__ float gelu_erf(float v) {
-  const float ax = fabsf(v) * 0.70710678118654752440f;
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, ax, 1.0f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  const float erf_abs = 1.0f - poly * t * __expf(-ax * ax);
-  return 0.5f * v * (1.0f + copysignf(erf_abs, v));
+  const float xc = fminf(fmaxf(v, -8.0f), 8.0f);     // keeps the fitted polynomial in its monotone range
+  const float x2 = xc * xc;
+  float pz = fmaf(-0.0003515195915898722f, x2, 0.03700566448133039f);
+  pz = fmaf(pz, x2, 0.797507862407347f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(pz * xc));
+  const float hv = 0.5f * v;
+  return fmaf(hv, t, hv);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -188,7 +194,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctl->tmem_empty[a]), 128);
+      mbar_init(smem_u32(&ctl->tmem_empty[a]), 256);
     }
     ctl->abort_flag = 0;
     if (p.seg_offsets) {
@@ -261,9 +267,10 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         umma_commit(smem_u32(&ctl->tmem_full[acc]));
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < EPI_WARP0) {
     // ---------------- weight decoders ----------------
-    const int r = (warp - 2) * 32 + lane;  // weight row inside the tile
+    const int grp = (warp - DEC_WARP0) >> 2;                      // K-blocks with (it & 1) == grp
+    const int r = ((warp - DEC_WARP0) & 3) * 32 + lane;            // weight row inside the tile
     const size_t row_bytes = size_t(p.K) / 4;
     const uint32_t swz = uint32_t(r & 7);
     uint32_t it = 0;
@@ -271,10 +278,14 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       if (!tile_coord(ctl, t, n_ft, p.G, bn, &tc)) break;
       const uint8_t* wrow = p.w_packed + (size_t(tc.group) * p.N + size_t(tc.ft) * BM + r) * row_bytes;
-      uint4 cur = __ldg(reinterpret_cast<const uint4*>(wrow));
+      // this group's first K-block of the tile: kb0 = 0 or 1 depending on the running parity
+      const int kb0 = int((it ^ uint32_t(grp)) & 1u);
+      uint4 cur = make_uint4(0u, 0u, 0u, 0u);
+      if (kb0 < n_kb) cur = __ldg(reinterpret_cast<const uint4*>(wrow + size_t(kb0) * 16));
       for (int kb = 0; kb < n_kb; ++kb, ++it) {
+        if (((it ^ uint32_t(grp)) & 1u) != 0u) continue;    // the other group's K-block
         uint4 nxt = cur;
-        if (kb + 1 < n_kb) nxt = __ldg(reinterpret_cast<const uint4*>(wrow + size_t(kb + 1) * 16));
+        if (kb + 2 < n_kb) nxt = __ldg(reinterpret_cast<const uint4*>(wrow + size_t(kb + 2) * 16));
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1u;
         if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status, JB200_STATUS_GEMM_DECODE)) goto done;
@@ -296,6 +307,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
   } else {
     // ---------------- epilogue ----------------
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - EPI_WARP0) >> 2; // which of the alternating 32-token chunks
     uint8_t* stage_base = reinterpret_cast<uint8_t*>(ctl) + ((sizeof(SmemCtl) + 127) / 128) * 128;
     uint32_t tile_n = 0;
     TileCoord tc;
@@ -307,16 +319,28 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         goto done;
       tc_fence_after_sync();
       const int feat = tc.ft * BM + q * 32 + lane;
-      uint8_t* stage = stage_base + (warp - 6) * STAGE_OUT_BYTES;
+      uint8_t* stage = stage_base + (warp - EPI_WARP0) * STAGE_OUT_BYTES;
       const float alpha = __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows) *
                           (p.w_layout ? 0.5f : 1.0f);   // prepared weights decode to +-2
       const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MAX;
-      for (int c0 = 0; c0 < bn; c0 += 32) {
+      for (int c0 = half * 32; c0 < bn; c0 += 64) {
         if (tc.tok0 + c0 >= tc.tok_end) break;   // warp-uniform
+        const int ntok = min(32, tc.tok_end - (tc.tok0 + c0));
+        // residual epilogue: start the loads of the old values before waiting for the accumulator
+        float4 old[8];
+        if (p.epilogue == JB200_EPI_RESID_F32) {
+          const float* o = reinterpret_cast<const float*>(p.out);
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
+            old[it] = r < ntok ? __ldcs(reinterpret_cast<const float4*>(
+                                     o + size_t(tc.tok0 + c0 + r) * p.N + tc.ft * BM + q * 32 + c16 * 4))
+                               : make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+        }
         uint32_t v[32];
         tmem_ld_32x32(t_lane + c0, v);
         tmem_ld_wait();
-        const int ntok = min(32, tc.tok_end - (tc.tok0 + c0));
         // The accumulator chunk is lane = out-feature, register = token; HBM wants token rows.  Turn
         // it through this warp's staging block in shared memory ([32 tokens][32 features]) so that
         // global memory sees 16-byte accesses on whole 64 B / 128 B row segments.
@@ -346,15 +370,6 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
           for (int j = 0; j < 32; ++j) st[j * 32 + lane] = alpha * __uint_as_float(v[j]);
           __syncwarp();
           float* o = reinterpret_cast<float*>(p.out);
-          float4 old[8];
-          if (resid) {
-#pragma unroll
-            for (int it = 0; it < 8; ++it) {
-              const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
-              old[it] = r < ntok ? __ldcs(reinterpret_cast<const float4*>(o + (row0 + r) * p.N + f0 + c16 * 4))
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          }
 #pragma unroll
           for (int it = 0; it < 8; ++it) {
             const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
