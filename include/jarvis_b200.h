@@ -143,11 +143,15 @@ int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* ou
  * gamma: f32 [H] = sigmoid(gamma_raw);  cos_tab/sin_tab: f32 [n_pos][32] (first half of the RoPE cache);
  * pos0: i32 [B] first position of each sequence, or NULL to use pos0_scalar for all (start_pos);
  * s_in / s_out: f32 [B][H][64][64] (D_v x D_k, the layout of h_prev / h_last), each may be NULL;
- * o: bf16 rows [B*T] with stride ld_o.  head_dim must be 64. */
+ * o: bf16 rows [B*T] with stride ld_o.  head_dim must be 64.
+ * scratch: jb200_attn_scan_scratch_bytes(B, T, H) bytes (8-byte aligned) or NULL.  With scratch, long
+ *   sequences are cut into segments that run in parallel (a first launch computes each segment's state
+ *   contribution from k and v); with NULL every (sequence, head) is walked by one CTA. */
+size_t jb200_attn_scan_scratch_bytes(int B, int T, int H);
 int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                     const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
-                    const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
-                    void* stream);
+                    const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
+                    int head_dim, void* stream);
 
 /* ---- MoE routing ---------------------------------------------------------------------- */
 

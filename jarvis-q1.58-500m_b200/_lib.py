@@ -38,7 +38,8 @@ PROTOTYPES = {
     "jb200_host_decode16_prepared": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
     "jb200_rmsnorm": (_I, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "jb200_embedding": (_I, [_P, _P, _I, _P, _I, _I, _P]),
-    "jb200_attn_scan": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+    "jb200_attn_scan": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
+    "jb200_attn_scan_scratch_bytes": (_Z, [_I, _I, _I]),
     "jb200_router_top2": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
     "jb200_moe_metadata_scratch_bytes": (_Z, [_I, _I, _I]),
     "jb200_moe_metadata": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),

@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 2; }
+int jb200_abi_version(void) { return 3; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -165,11 +165,13 @@ int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* ou
 
 int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                     const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
-                    const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
-                    void* stream) {
-  return launch_attn_scan(q, k, v, ld_qkv, gamma, cos_tab, sin_tab, n_pos, pos0, pos0_scalar, s_in, o, ld_o, s_out, B,
-                          T, H, head_dim, static_cast<cudaStream_t>(stream));
+                    const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
+                    int head_dim, void* stream) {
+  return launch_attn_scan(q, k, v, ld_qkv, gamma, cos_tab, sin_tab, n_pos, pos0, pos0_scalar, s_in, o, ld_o, s_out,
+                          scratch, B, T, H, head_dim, static_cast<cudaStream_t>(stream));
 }
+
+size_t jb200_attn_scan_scratch_bytes(int B, int T, int H) { return attn_scan_scratch_bytes(B, T, H); }
 
 int jb200_router_top2(const void* x, const float* w_router, int N, int C, int E, int64_t* topk_idx, float* gates,
                       float* probs, double* probs_sum, int32_t* top1_hist, void* stream) {

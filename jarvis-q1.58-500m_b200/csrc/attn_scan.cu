@@ -6,7 +6,7 @@
 //   optional initial state S_in and final state S_out (B, H, D_v, D_k)  (associative_attention.py:126-152, :273-308;
 //                                                                      kernel A3, associative_attention_cuda.cu:218-265)
 //
-// One CTA per (sequence, head) walks the sequence in 64-token chunks.  The state S never leaves
+// One CTA per (sequence, head, segment) walks its part of the sequence in 64-token chunks.  The state S never leaves
 // the SM: it is carried in fp32 accumulator registers (one 16-row band per warp) and mirrored
 // as bf16 in shared memory for the cross-chunk product, so HBM traffic is the algorithmic
 // q, k, v in / o out (512 B per token-head) plus one optional state load/store per sequence-head.
@@ -20,6 +20,12 @@
 //     A  = (Q K^T) o gamma^(i-j) [j <= i]         only the causal n-tiles are computed
 //     O += A V                                    intra-chunk
 //   warp w (state rows dv 16w..16w+15):  S = gamma^c S + Vw^T K
+//
+// Sequence segments: when B*H alone cannot fill the GPU (prefill of a few long sequences), T is cut
+// into segments.  A first launch (STATE_ONLY) runs only the k/v half of the work for every non-final
+// segment from a zero state and stores its contribution D_s; the main launch starts segment s from
+// S = fold_{s' < s}(gamma^L S + D_s'), which is exact because the recurrence is linear in S.
+// Extra HBM traffic: k and v are read twice (the second time mostly from L2).
 #include "common.cuh"
 #include "launchers.h"
 
@@ -29,7 +35,7 @@ namespace {
 
 constexpr int D = 64;             // head dim (fixed by the path: 16 heads x 64)
 constexpr int CH = 64;            // chunk length, AssociativeLinearAttention.CHUNK_SIZE
-constexpr int STAGES = 3;
+constexpr int STAGES = 2;             // 73 KiB of shared memory per CTA -> three CTAs per SM
 constexpr int TILE_BYTES = CH * D * 2;          // 8 KiB
 constexpr int STAGE_BYTES = 3 * TILE_BYTES;     // q, k, v
 constexpr int ATTN_THREADS = 128;
@@ -46,6 +52,9 @@ struct AttnParams {
   __nv_bfloat16* o;        // [B*T][ld_o], head h at columns h*64
   int ld_o;
   int B, T, H;
+  int seg_chunks;          // chunks per sequence segment (grid.z walks the segments)
+  int nseg;
+  float* seg_state;        // [B][H][nseg-1][64][64]: state contribution of each non-final segment
   unsigned int* status;
 };
 
@@ -54,6 +63,7 @@ struct Smem {
   uint8_t vw[TILE_BYTES];              // v * gamma^(c-1-j)
   uint8_t s_bf16[2][TILE_BYTES];       // state mirror [dv][dk], double buffered
   float pw[CH + 1];                    // gamma^n
+  float4 mf[8][32];                    // decay-mask factors of one 16x8 score tile, by (2*warp - key_tile + 1, lane)
   uint64_t full[STAGES];
   uint32_t abort_flag;
 };
@@ -80,9 +90,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : expf(x); }  // ELU(x)+1
+// ELU(x)+1 = x+1 for x > 0, exp(x) otherwise; branch-free, exp through ex2.approx (rel. error 2^-22,
+// far below the bf16 rounding of the result).
+__device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(fminf(x, 0.f)); }
 
-__global__ void __launch_bounds__(ATTN_THREADS)
+template <bool STATE_ONLY>
+__global__ void __launch_bounds__(ATTN_THREADS, 3)
 attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -94,6 +107,9 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int h = blockIdx.x, b = blockIdx.y;
   const int T = p.T;
   const int n_chunks = (T + CH - 1) / CH;
+  const int seg = blockIdx.z;
+  const int ck_begin = seg * p.seg_chunks;
+  const int ck_end = STATE_ONLY ? ck_begin + p.seg_chunks : min(n_chunks, ck_begin + p.seg_chunks);
   const int row0 = b * T;                       // first row of this sequence in the (B*T, ld) matrices
   const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
   const float gamma = __ldg(p.gamma + h);
@@ -108,13 +124,19 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tma_prefetch_desc(&tm_v);
   }
   for (int n = tid; n <= CH; n += ATTN_THREADS) sm->pw[n] = expf(log_g * float(n));
+  for (int e = tid; e < 8 * 32; e += ATTN_THREADS) {
+    const int d = e >> 5, ln = e & 31;
+    const int diff0 = 8 * (d - 1) + (ln >> 2) - 2 * (ln & 3);   // query row - key column of c0
+    auto fac = [&](int x) { return x >= 0 ? expf(log_g * float(x)) : 0.f; };
+    sm->mf[d][ln] = make_float4(fac(diff0), fac(diff0 - 1), fac(diff0 + 8), fac(diff0 + 7));
+  }
 
   // state: fp32 accumulators, rows dv = 16*warp + lane/4 (+8), cols dk = 8*nt + 2*(lane%4) (+1)
   float S[8][4];
   {
     const int r = 16 * warp + (lane >> 2);
     const int cb = 2 * (lane & 3);
-    const float* sin_p = p.s_in ? p.s_in + (size_t(b) * p.H + h) * D * D : nullptr;
+    const float* sin_p = (!STATE_ONLY && p.s_in) ? p.s_in + (size_t(b) * p.H + h) * D * D : nullptr;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       const int c = nt * 8 + cb;
@@ -125,6 +147,17 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       } else {
         S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
       }
+      if (!STATE_ONLY && seg > 0) {
+        // state entering this segment: fold the earlier segments' contributions, oldest first
+        const float gL = expf(log_g * float(p.seg_chunks * CH));
+        const float* dp = p.seg_state + (size_t(b) * p.H + h) * (p.nseg - 1) * D * D;
+        for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
+          const float2 lo = __ldg(reinterpret_cast<const float2*>(dp + r * D + c));
+          const float2 hi = __ldg(reinterpret_cast<const float2*>(dp + (r + 8) * D + c));
+          S[nt][0] = gL * S[nt][0] + lo.x; S[nt][1] = gL * S[nt][1] + lo.y;
+          S[nt][2] = gL * S[nt][2] + hi.x; S[nt][3] = gL * S[nt][3] + hi.y;
+        }
+      }
       *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
       *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
     }
@@ -132,33 +165,34 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
 
   auto issue_chunk = [&](int ck) {  // called by thread 0 only
-    const int s = ck % STAGES;
+    const int s = (ck - ck_begin) % STAGES;
     const uint32_t bar = smem_u32(&sm->full[s]);
-    mbar_arrive_expect_tx(bar, STAGE_BYTES);
+    mbar_arrive_expect_tx(bar, STATE_ONLY ? 2 * TILE_BYTES : STAGE_BYTES);
     const uint32_t dst = smem_u32(sm->tiles[s]);
     const int r = row0 + ck * CH;
-    tma_load_2d(dst, &tm_q, h * D, r, bar);
+    if (!STATE_ONLY) tma_load_2d(dst, &tm_q, h * D, r, bar);
     tma_load_2d(dst + TILE_BYTES, &tm_k, h * D, r, bar);
     tma_load_2d(dst + 2 * TILE_BYTES, &tm_v, h * D, r, bar);
   };
   if (tid == 0) {
-    for (int ck = 0; ck < STAGES && ck < n_chunks; ++ck) issue_chunk(ck);
+    for (int ck = ck_begin; ck < ck_begin + STAGES && ck < ck_end; ++ck) issue_chunk(ck);
   }
 
   const uint32_t vw_a = smem_u32(sm->vw);
   bool ok = true;
-  for (int ck = 0; ck < n_chunks; ++ck) {
-    const int s = ck % STAGES;
+  for (int ck = ck_begin; ck < ck_end; ++ck) {
+    const int lc = ck - ck_begin;
+    const int s = lc % STAGES;
     const int c_len = min(CH, T - ck * CH);
     const uint32_t q_a = smem_u32(sm->tiles[s]);
     const uint32_t k_a = q_a + TILE_BYTES, v_a = q_a + 2 * TILE_BYTES;
     uint8_t* q_p = sm->tiles[s];
     uint8_t* k_p = q_p + TILE_BYTES;
     uint8_t* v_p = q_p + 2 * TILE_BYTES;
-    const uint32_t sb_a = smem_u32(sm->s_bf16[ck & 1]);
-    uint8_t* sb_next = sm->s_bf16[(ck + 1) & 1];
+    const uint32_t sb_a = smem_u32(sm->s_bf16[lc & 1]);
+    uint8_t* sb_next = sm->s_bf16[(lc + 1) & 1];
 
-    if (!mbar_wait(smem_u32(&sm->full[s]), uint32_t(ck / STAGES) & 1u, &sm->abort_flag, p.status,
+    if (!mbar_wait(smem_u32(&sm->full[s]), uint32_t(lc / STAGES) & 1u, &sm->abort_flag, p.status,
                    JB200_STATUS_ATTN_LOAD)) {
       ok = false;
     }
@@ -181,7 +215,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
       }
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {  // 0: q, 1: k
+      for (int which = STATE_ONLY ? 1 : 0; which < 2; ++which) {  // 0: q, 1: k
         uint8_t* tp = which == 0 ? q_p : k_p;
         uint4* lo_p = reinterpret_cast<uint4*>(tp + swz(r, cg));
         uint4* hi_p = reinterpret_cast<uint4*>(tp + swz(r, cg + 4));
@@ -214,6 +248,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
     __syncthreads();
 
+    if (!STATE_ONLY) {
     // ---- Q fragments of this warp's 16 rows (A operand, 4 k-steps over d) ---------------------------
     uint32_t qf[4][4];
     {
@@ -243,7 +278,6 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     }
 
     // ---- intra-chunk: scores over the causal key tiles, decay mask, then P V ---------------------------
-    const int n_jt = 2 * warp + 2;  // key n-tiles (8 keys each) that can be <= the last query row of this warp
     uint32_t pf[4][4];              // P as A fragments: k-step kj covers keys 16kj..16kj+15
 #pragma unroll
     for (int kj = 0; kj < 4; ++kj) {
@@ -258,17 +292,14 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ldsm_x4(k_a + swz(r, 4 + (lane >> 3)), bfr[4], bfr[5], bfr[6], bfr[7]);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) mma16816(sc, qf[ks], bfr[2 * ks], bfr[2 * ks + 1]);
-          const int j0 = jt * 8 + 2 * (lane & 3), j1 = j0 + 1;
-          sc[0] = j0 <= i_lo ? sc[0] * sm->pw[i_lo - j0] : 0.f;
-          sc[1] = j1 <= i_lo ? sc[1] * sm->pw[i_lo - j1] : 0.f;
-          sc[2] = j0 <= i_hi ? sc[2] * sm->pw[i_hi - j0] : 0.f;
-          sc[3] = j1 <= i_hi ? sc[3] * sm->pw[i_hi - j1] : 0.f;
+          const float4 f = sm->mf[2 * warp - jt + 1][lane];   // gamma^(i-j) for j <= i, else 0
+          sc[0] *= f.x; sc[1] *= f.y; sc[2] *= f.z; sc[3] *= f.w;
           pf[kj][2 * half + 0] = pack_bf16x2(sc[0], sc[1]);
           pf[kj][2 * half + 1] = pack_bf16x2(sc[2], sc[3]);
         }
       }
     }
-    (void)n_jt;
+
     // O += P V ;  B[k=j][n=dv] = V[j][dv]  (transposed load)
 #pragma unroll
     for (int kj = 0; kj < 4; ++kj) {
@@ -283,6 +314,29 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
     }
+
+    // ---- output: stage this warp's 16 rows in its own (already consumed) q rows, then 16-byte stores ------
+    __syncwarp();
+    {
+      const int r = 16 * warp + (lane >> 2);
+      const int cb = 2 * (lane & 3);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        const int c = nt * 8 + cb;
+        *reinterpret_cast<uint32_t*>(q_p + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][0], O[nt][1]);
+        *reinterpret_cast<uint32_t*>(q_p + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][2], O[nt][3]);
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int rr = 16 * warp + it * 4 + (lane >> 3), cg = lane & 7;
+      if (rr < c_len) {
+        const uint4 v = *reinterpret_cast<const uint4*>(q_p + swz(rr, cg));
+        *reinterpret_cast<uint4*>(p.o + size_t(row0 + ck * CH + rr) * p.ld_o + h * D + cg * 8) = v;
+      }
+    }
+    }  // !STATE_ONLY
 
     // ---- state update: S = gamma^c S + Vw^T K ;  A[m=dv][k=j] = Vw[j][dv], B[k=j][n=dk] = K[j][dk] -------
     {
@@ -316,35 +370,15 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
 
-    // ---- output: stage this warp's 16 rows in its own (already consumed) q rows, then 16-byte stores ------
-    __syncwarp();
-    {
-      const int r = 16 * warp + (lane >> 2);
-      const int cb = 2 * (lane & 3);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int c = nt * 8 + cb;
-        *reinterpret_cast<uint32_t*>(q_p + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][0], O[nt][1]);
-        *reinterpret_cast<uint32_t*>(q_p + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][2], O[nt][3]);
-      }
-    }
-    __syncwarp();
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int rr = 16 * warp + it * 4 + (lane >> 3), cg = lane & 7;
-      if (rr < c_len) {
-        const uint4 v = *reinterpret_cast<const uint4*>(q_p + swz(rr, cg));
-        *reinterpret_cast<uint4*>(p.o + size_t(row0 + ck * CH + rr) * p.ld_o + h * D + cg * 8) = v;
-      }
-    }
-
     fence_proxy_async_smem();  // order this thread's generic accesses to stage s before the next TMA write into it
     __syncthreads();  // tiles of stage s and vw are free; the new state mirror is complete
-    if (tid == 0 && ck + STAGES < n_chunks) issue_chunk(ck + STAGES);
+    if (tid == 0 && ck + STAGES < ck_end) issue_chunk(ck + STAGES);
   }
 
-  if (ok && p.s_out) {
-    float* so = p.s_out + (size_t(b) * p.H + h) * D * D;
+  float* so = nullptr;
+  if (STATE_ONLY) so = p.seg_state + ((size_t(b) * p.H + h) * (p.nseg - 1) + seg) * D * D;
+  else if (p.s_out && seg == p.nseg - 1) so = p.s_out + (size_t(b) * p.H + h) * D * D;
+  if (ok && so) {
     const int r = 16 * warp + (lane >> 2);
     const int cb = 2 * (lane & 3);
 #pragma unroll
@@ -388,10 +422,29 @@ int make_map(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
 
 }  // namespace
 
+// Segments: enough CTAs to fill three per SM, each segment at least four chunks long.
+static void pick_segments(int B, int T, int H, int sms, int* seg_chunks, int* nseg) {
+  const int n_chunks = (T + CH - 1) / CH;
+  long want = (long(sms) * 3) / (long(B) * H);
+  if (want < 1) want = 1;
+  if (want > n_chunks / 4) want = n_chunks / 4 > 0 ? n_chunks / 4 : 1;
+  int sc = int((n_chunks + want - 1) / want);
+  *seg_chunks = sc;
+  *nseg = (n_chunks + sc - 1) / sc;
+}
+
+size_t attn_scan_scratch_bytes(int B, int T, int H) {
+  if (B <= 0 || T <= 0 || H <= 0) return 0;
+  const int sms = sm_count();
+  int sc, ns;
+  pick_segments(B, T, H, sms > 0 ? sms : 148, &sc, &ns);
+  return size_t(B) * H * size_t(ns - 1) * D * D * sizeof(float);
+}
+
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
-                     const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
-                     cudaStream_t stream) {
+                     const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
+                     int head_dim, cudaStream_t stream) {
   JB_REQUIRE(head_dim == D, "attn_scan: head_dim (%d) must be %d", head_dim, D);
   JB_REQUIRE(B >= 0 && T >= 0 && H > 0, "attn_scan: bad shape (B=%d, T=%d, H=%d)", B, T, H);
   JB_REQUIRE(B <= 65535, "attn_scan: batch (%d) exceeds 65535", B);
@@ -417,9 +470,21 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.B = B; p.T = T; p.H = H;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
-  JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
-  dim3 grid(H, B);
-  attn_scan_kernel<<<grid, ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  const int sms = sm_count();
+  if (sms <= 0) return JB200_ERR_CUDA;
+  p.seg_chunks = (T + CH - 1) / CH;
+  p.nseg = 1;
+  p.seg_state = reinterpret_cast<float*>(scratch);
+  if (scratch) pick_segments(B, T, H, sms, &p.seg_chunks, &p.nseg);   // without scratch: one segment per sequence
+  JB_REQUIRE(p.nseg <= 65535, "attn_scan: too many segments");
+  JB_REQUIRE(!scratch || (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "attn_scan: scratch pointer misaligned");
+  JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
+  if (p.nseg > 1) {
+    JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
+    attn_scan_kernel<true><<<dim3(H, B, p.nseg - 1), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+    JB_LAUNCH_CHECK("attn_scan_kernel<state>");
+  }
+  attn_scan_kernel<false><<<dim3(H, B, p.nseg), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
   JB_LAUNCH_CHECK("attn_scan_kernel");
   return JB200_OK;
 }

@@ -47,7 +47,8 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
 
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
-                     const float* s_in, void* o, int ld_o, float* s_out, int B, int T, int H, int head_dim,
-                     cudaStream_t stream);
+                     const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
+                     int head_dim, cudaStream_t stream);
+size_t attn_scan_scratch_bytes(int B, int T, int H);
 
 }  // namespace jb

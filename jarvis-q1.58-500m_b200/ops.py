@@ -196,7 +196,7 @@ def embedding(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- attention scan
 def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, cos_tab: torch.Tensor,
               sin_tab: torch.Tensor, B: int, T: int, H: int, *, start_pos=0, state_in: torch.Tensor | None = None,
-              want_state: bool = False, out: torch.Tensor | None = None):
+              want_state: bool = False, out: torch.Tensor | None = None, segmented: bool = True):
     """Feature map + RoPE + decayed causal scan.  q, k, v: bf16 2-D views (B*T, H*64) sharing one
     row stride (e.g. column slices of a fused q|k|v matrix).  start_pos: int, or int32 (B,) tensor of
     per-sequence first positions.  Returns (o bf16 (B*T, H*64), final state f32 (B,H,64,64) or None)."""
@@ -224,10 +224,15 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
     if out is None:
         out = torch.empty((B * T, H * 64), dtype=torch.bfloat16, device=q.device)
     s_out = torch.empty((B, H, 64, 64), dtype=torch.float32, device=q.device) if want_state else None
+    scratch = None
+    if segmented:
+        nbytes = lib.jb200_attn_scan_scratch_bytes(B, T, H)
+        if nbytes:
+            scratch = torch.empty((nbytes // 4,), dtype=torch.float32, device=q.device)
     _lib.check(
         lib.jb200_attn_scan(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(gamma), _ptr(cos_tab), _ptr(sin_tab), cos_tab.shape[0],
-                            _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0), _ptr(s_out), B, T, H, 64,
-                            _stream()),
+                            _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0), _ptr(s_out), _ptr(scratch),
+                            B, T, H, 64, _stream()),
         "jb200_attn_scan",
     )
     return out, s_out

@@ -87,6 +87,24 @@ def test_attn_scan_carried_state_and_positions():
     assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
 
 
+@pytest.mark.parametrize("T", [1000, 2048])
+def test_attn_scan_segmented_long_sequences(T):
+    """Long sequences are cut into parallel segments (state pre-pass + fold); result must match the
+    oracle and the unsegmented kernel, with and without an incoming state."""
+    eo, es = _scan_case(1, 2, T, seed=T, start_pos=7, with_state=True)
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+    g = torch.Generator().manual_seed(T + 1)
+    B, H = 2, 2
+    qkv = torch.randn(B * T, 3 * H * 64, generator=g).bfloat16().cuda()
+    gamma = (torch.rand(H, generator=g) * 0.099 + 0.9).cuda()
+    S0 = torch.randn(B, H, 64, 64, generator=g).cuda()
+    cos, sin = rope_tabs(T)
+    args = (qkv[:, :H * 64], qkv[:, H * 64:2 * H * 64], qkv[:, 2 * H * 64:], gamma, cos, sin, B, T, H)
+    o1, S1 = ops.attn_scan(*args, state_in=S0, want_state=True, segmented=True)
+    o2, S2 = ops.attn_scan(*args, state_in=S0, want_state=True, segmented=False)
+    assert rel_l2(o1.float(), o2.float()) < 3e-3 and rel_l2(S1, S2) < 1e-5
+
+
 def test_attn_scan_extreme_decay():
     eo, es = _scan_case(1, 2, 150, seed=3, gammas=[0.01, 0.99])
     assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
