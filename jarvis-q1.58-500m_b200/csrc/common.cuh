@@ -128,7 +128,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// ---- TMA (non-multicast, this GPU's memory only) ----------------------------
+// ---- TMA: plain per-CTA loads of this GPU's own memory --------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

@@ -139,11 +139,39 @@ def case_moe(a):
         with torch.no_grad():
             moe.router.weight[:, 0] = (torch.log(w / w.sum()) * 1.6).cuda()
     xb = x.bfloat16()
-    fn = lambda: moe.run_rows(xb)  # noqa: E731
-    ms = timeit(fn, a.iters)
-    counts = moe.last_routing[2][0].cpu().tolist()
-    report("moe_layer (router..combine)", ms, flops=2.0 * 2 * a.N * (2 * C * C) * 2,
-           extra={"N": a.N, "slot_counts": counts, "tokens_per_s": a.N / ms * 1e3})
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world == 1:
+        fn = lambda: moe.run_rows(xb)  # noqa: E731
+        ms = timeit(fn, a.iters)
+        counts = moe.last_routing[2][0].cpu().tolist()
+        report("moe_layer (router..combine)", ms, flops=2.0 * 2 * a.N * (2 * C * C) * 2,
+               extra={"N": a.N, "slot_counts": counts, "tokens_per_s": a.N / ms * 1e3})
+        return
+    # expert parallel: tokens data-parallel (contiguous ranges), experts spread over the ranks,
+    # NCCL all-to-all for dispatch and return; time = max over ranks of the CUDA-event time
+    import torch.distributed as dist
+    from jarvis_b200 import parallel as par
+    rank = dist.get_rank()
+    n_loc = a.N // world
+    x_loc = xb[rank * n_loc:(rank + 1) * n_loc].contiguous()
+    ep = par.ExpertParallelMoE(moe)
+    out, _ = ep.run_rows(x_loc)
+    ref, _ = moe.run_rows(x_loc)
+    err = float((out.float() - ref.float()).norm() / ref.float().norm())
+    assert err < 1e-6, f"expert-parallel result differs from the single-GPU layer: {err}"
+    dist.barrier()
+    ms = timeit(lambda: ep.run_rows(x_loc), a.iters)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    recv = torch.tensor([sum(r) for r in ep.last_recv_counts], device="cuda").sum().reshape(1)
+    allrecv = [torch.zeros_like(recv) for _ in range(world)]
+    dist.all_gather(allrecv, recv)
+    if rank == 0:
+        ms = float(t[0])
+        report("moe_layer expert-parallel (router, all-to-all, experts, all-to-all, combine)", ms,
+               flops=2.0 * 2 * a.N * (2 * C * C) * 2,
+               extra={"N": a.N, "n_gpus": world, "tokens_per_s": a.N / ms * 1e3, "rel_l2_vs_single_gpu": err,
+                      "rows_received_per_rank": [int(v) for v in allrecv]})
 
 
 def main():
@@ -165,6 +193,11 @@ def main():
     for p in sub.choices.values():
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        lr = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(lr)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe}[a.case](a)
 
 

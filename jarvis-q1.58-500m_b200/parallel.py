@@ -1,0 +1,142 @@
+"""Expert-parallel execution of the top-2 MoE layer over the ranks of one node.
+
+The reference has no distributed code; this adds the one exchange the path has when the 4 experts
+live on different GPUs: an all-to-all of dispatched token rows before the expert FFN and its inverse
+after it (NCCL over NVLink on GPUs; any torch.distributed backend works, which is how the logic is
+tested with gloo on CPU).  Tokens stay data-parallel: every rank routes its own tokens with the
+replicated router, so routing and gates are those of the single-GPU layer.
+
+Ownership: with `world <= E` rank r owns the `E / world` consecutive experts starting at
+`r * E / world`; with `world > E` each expert is served by `world / E` consecutive ranks and every
+source rank cuts its rows for that expert into that many contiguous parts (the packed weights are
+1 MiB per expert, so replicas are free).  Inside an expert the rows arrive ordered by (source rank,
+local stable order): when ranks hold contiguous token ranges this is exactly the single-GPU dispatch
+order (moe_compute_metadata_kernel, sparse_model_cuda/sparse_model.cu:23-90).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def owner_plan(world: int, num_experts: int):
+    """-> (rounds, plan) with plan[round][dst_rank] = (expert, part, nparts): which slice of which
+    expert's rows a source sends to `dst_rank` in that all-to-all round."""
+    if world <= num_experts:
+        if num_experts % world:
+            raise ValueError(f"num_experts ({num_experts}) must be divisible by the world size ({world})")
+        per = num_experts // world
+        return per, [[(d * per + j, 0, 1) for d in range(world)] for j in range(per)]
+    if world % num_experts:
+        raise ValueError(f"world size ({world}) must be a multiple of num_experts ({num_experts})")
+    shards = world // num_experts
+    return 1, [[(d // shards, d % shards, shards) for d in range(world)]]
+
+
+def part_bounds(count: int, part: int, nparts: int):
+    return count * part // nparts, count * (part + 1) // nparts
+
+
+def send_layout(counts, plan_round):
+    """Row ranges (begin, end) inside the expert-sorted dispatched rows for every destination."""
+    offsets = [0]
+    for c in counts:
+        offsets.append(offsets[-1] + int(c))
+    out = []
+    for expert, part, nparts in plan_round:
+        lo, hi = part_bounds(int(counts[expert]), part, nparts)
+        out.append((offsets[expert] + lo, offsets[expert] + hi))
+    return out
+
+
+class ExpertParallelMoE:
+    """Runs a `SparseMoELayer`'s experts across a process group.
+
+    `compute(rows, owned_experts, seg_offsets) -> rows` applies w2(GELU(w1(.))) of the listed experts
+    to the contiguous row segments; the default uses the layer's packed weights and the grouped
+    tcgen05 GEMM.  `route`, `gather`, `combine` default to the CUDA kernels as well; tests on CPU pass
+    oracle implementations."""
+
+    def __init__(self, moe, group=None, route=None, gather=None, combine=None, compute=None):
+        self.moe = moe
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.rounds, self.plan = owner_plan(self.world, moe.num_experts)
+        self.owned = [self.plan[j][self.rank][0] for j in range(self.rounds)]
+        self._route = route or self._route_cuda
+        self._gather = gather or self._gather_cuda
+        self._combine = combine or self._combine_cuda
+        self._compute = compute or self._compute_cuda
+        self._owned_weights = None
+        self.last_recv_counts = None
+
+    # ---- default CUDA stages ------------------------------------------------------------------
+    def _route_cuda(self, x):
+        from . import ops
+        idx, gates, _ = ops.router_top2(x, self.moe.router.weight.detach().float().contiguous())
+        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, self.moe.num_experts)
+        return idx, gates, counts, scatter, gather
+
+    def _gather_cuda(self, x, gather_map):
+        from . import ops
+        return ops.dispatch_gather(x, gather_map)
+
+    def _combine_cuda(self, y, gates, scatter_map, out_dtype):
+        from . import ops
+        return ops.scatter_combine(y, gates, scatter_map, out_dtype=out_dtype)
+
+    def _compute_cuda(self, rows, owned, seg_offsets):
+        from . import ops
+        (p1, a1), (p2, a2) = self.moe.packed()
+        key = (p1.data_ptr(), p2.data_ptr(), tuple(owned))
+        if self._owned_weights is None or self._owned_weights[0] != key:
+            sel = torch.tensor(owned, device=p1.device)
+            self._owned_weights = (key, p1[sel].contiguous(), a1[sel].contiguous(), p2[sel].contiguous(),
+                                   a2[sel].contiguous())
+        _, q1, b1, q2, b2 = self._owned_weights
+        hid = ops.ternary_linear_grouped(rows, q1, b1, seg_offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
+        return ops.ternary_linear_grouped(hid, q2, b2, seg_offsets, epilogue=ops.EPI_BF16, prepared=True)
+
+    # ---- the exchange -------------------------------------------------------------------------
+    def run_rows(self, x, out_dtype=None):
+        """x: (N_local, C) rows of this rank -> (N_local, C) MoE output (same values as the single-GPU layer)."""
+        out_dtype = out_dtype or x.dtype
+        idx, gates, counts, scatter_map, gather_map = self._route(x)
+        dispatched = self._gather(x, gather_map)                         # expert-sorted rows
+        counts_h = [int(c) for c in counts.cpu().tolist()]               # host sync: NCCL needs split sizes
+        C = x.shape[1]
+        recv_bufs, send_sizes_all, recv_sizes_all, layouts = [], [], [], []
+        for j in range(self.rounds):
+            layout = send_layout(counts_h, self.plan[j])
+            send_sizes = [hi - lo for lo, hi in layout]
+            t_send = torch.tensor(send_sizes, dtype=torch.int64, device=x.device)
+            t_recv = torch.empty_like(t_send)
+            dist.all_to_all_single(t_recv, t_send, group=self.group)
+            recv_sizes = [int(v) for v in t_recv.cpu().tolist()]
+            contiguous = all(layout[d][1] == layout[d + 1][0] for d in range(self.world - 1))
+            send = dispatched[layout[0][0]:layout[-1][1]] if contiguous else torch.cat(
+                [dispatched[lo:hi] for lo, hi in layout])
+            recv = torch.empty((sum(recv_sizes), C), dtype=x.dtype, device=x.device)
+            dist.all_to_all_single(recv, send.contiguous(), recv_sizes, send_sizes, group=self.group)
+            recv_bufs.append(recv)
+            send_sizes_all.append(send_sizes)
+            recv_sizes_all.append(recv_sizes)
+            layouts.append(layout)
+        self.last_recv_counts = recv_sizes_all
+        rows = recv_bufs[0] if self.rounds == 1 else torch.cat(recv_bufs)
+        seg = [0]
+        for r in recv_bufs:
+            seg.append(seg[-1] + r.shape[0])
+        seg_offsets = torch.tensor(seg, dtype=torch.int32, device=x.device)
+        y_rows = self._compute(rows, self.owned, seg_offsets) if rows.shape[0] else rows
+        y_disp = torch.empty_like(dispatched)
+        for j in range(self.rounds):
+            back = torch.empty((sum(send_sizes_all[j]), C), dtype=x.dtype, device=x.device)
+            dist.all_to_all_single(back, y_rows[seg[j]:seg[j + 1]].contiguous(), send_sizes_all[j], recv_sizes_all[j],
+                                   group=self.group)
+            pos = 0
+            for lo, hi in layouts[j]:
+                y_disp[lo:hi] = back[pos:pos + hi - lo]
+                pos += hi - lo
+        return self._combine(y_disp, gates, scatter_map, out_dtype), (idx, gates)
