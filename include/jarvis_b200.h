@@ -217,10 +217,14 @@ int jb200_moe_finalize(const double* stats, const double* probs_sum, const int32
  *   liquid_fusion_cuda/liquid_state_fusion_cpp.cpp:67-74): alpha_tensor [B][T][D] in m's dtype.
  * m: [B][T][D] f32 (0) or bf16 (1), D even;  h0: f32 [B][D] or NULL (zeros);
  * out: [B][T][D] f32/bf16 or NULL;  resid: f32 [B][T][D] or NULL, updated in place resid += h (the
- * block's residual add, jarvis_model.py:436);  h_last: f32 [B][D] or NULL. */
+ * block's residual add, jarvis_model.py:436);  h_last: f32 [B][D] or NULL.
+ * scratch: jb200_lsf_scan_scratch_bytes(B, T, D) bytes (8-byte aligned) or NULL; with scratch, long
+ * sequences are cut into segments that run in parallel (a first launch computes the segment ends). */
+size_t jb200_lsf_scan_scratch_bytes(int B, int T, int D);
 int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
                    const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
-                   float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, void* stream);
+                   float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
+                   void* stream);
 
 /* Host-side copy of the bit manipulation the GEMM's decoder warps run: 16 two-bit codes
  * (one little-endian u32 of the packed layout) -> 16 bf16 values in out8[8] (two per u32,

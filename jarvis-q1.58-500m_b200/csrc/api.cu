@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 3; }
+int jb200_abi_version(void) { return 4; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -216,10 +216,13 @@ int jb200_moe_finalize(const double* stats, const double* probs_sum, const int32
 
 int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
                    const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
-                   float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, void* stream) {
+                   float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
+                   void* stream) {
   return launch_lsf_scan(m, m_dtype, alpha_tensor, alpha_scalar, act_var, var_scale, alpha_min, alpha_max, h0, resid,
-                         out, out_dtype, h_last, B, T, D, static_cast<cudaStream_t>(stream));
+                         out, out_dtype, h_last, scratch, B, T, D, static_cast<cudaStream_t>(stream));
 }
+
+size_t jb200_lsf_scan_scratch_bytes(int B, int T, int D) { return lsf_scan_scratch_bytes(B, T, D); }
 
 int jb200_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, void* stream) {
   return launch_prepare_weights(packed, n_bytes, prepared, static_cast<cudaStream_t>(stream));

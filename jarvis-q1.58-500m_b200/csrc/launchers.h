@@ -43,7 +43,9 @@ int launch_moe_finalize(const double* stats, const double* probs_sum, const int*
 
 int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
                     const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
-                    float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, cudaStream_t stream);
+                    float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
+                    cudaStream_t stream);
+size_t lsf_scan_scratch_bytes(int B, int T, int D);
 
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,

@@ -13,7 +13,10 @@
 // carry-in, publishes (product of decays, end value) in shared memory, the carries are combined in
 // warp order (the recurrence is an associative affine map), and every thread fixes its values up
 // with  h_t = local_t + P_t * carry_in.  A CTA owns 64 channels of one sequence and walks T tile by
-// tile, so HBM sees each element exactly once.
+// tile.  When B*D/64 CTAs cannot fill the GPU, T is also cut into segments: a first launch (ENDS_ONLY)
+// computes each non-final segment's end value (and decay product) from a zero carry, reading m once
+// more (it was just written by the MoE combine and is normally still in L2); the main launch folds
+// the earlier segments' ends into its carry-in, which is exact because the recurrence is affine.
 #include "common.cuh"
 #include "launchers.h"
 
@@ -37,6 +40,9 @@ struct LsfParams {
   void* out;               // [B][T][D] TOut or null
   float* h_last;           // [B][D] f32 or null
   int B, T, D;
+  int seg_len, nseg;       // tokens per segment (multiple of the tile), number of segments (grid.z)
+  float* seg_end;          // [B][nseg-1][D] end value of each non-final segment from a zero carry
+  float* seg_prod;         // [B][nseg-1][D] product of its decays (tensor mode)
 };
 
 template <typename T>
@@ -57,8 +63,8 @@ __device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, fl
   *reinterpret_cast<uint32_t*>(p) = pack_bf16x2(a, b);
 }
 
-template <bool TENSOR_ALPHA, typename TM, typename TOut, int TPW>
-__global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p) {
+template <bool TENSOR_ALPHA, typename TM, typename TOut, int TPW, bool ENDS_ONLY>
+__global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_kernel(const LsfParams p) {
   __shared__ float2 s_end[2][LSF_WARPS][32];   // end value of each warp's run
   __shared__ float2 s_prod[2][LSF_WARPS][32];  // product of decays over the run (tensor mode)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,11 +88,32 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
 #pragma unroll
     for (int i = 0; i < TPW; ++i) { pw[i] = a; a *= alpha; }
   }
+  const int seg = blockIdx.z;
+  const int t_begin = seg * p.seg_len;
+  const int t_end = min(p.T, t_begin + p.seg_len);
   float2 carry = make_float2(0.f, 0.f);
-  if (p.h0 && ch_ok) carry = __ldg(reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch));
+  float2 pcarry = make_float2(1.f, 1.f);   // running decay product of the segment (ENDS_ONLY, tensor mode)
+  if (!ENDS_ONLY) {
+    if (p.h0 && ch_ok) carry = __ldg(reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch));
+    if (seg > 0 && ch_ok) {
+      const float a_seg = TENSOR_ALPHA ? 0.f : expf(float(p.seg_len) * logf(alpha));
+      const size_t e0 = (size_t(b) * (p.nseg - 1)) * p.D + ch;
+      for (int s2 = 0; s2 < seg; ++s2) {
+        const float2 e = __ldg(reinterpret_cast<const float2*>(p.seg_end + e0 + size_t(s2) * p.D));
+        if (TENSOR_ALPHA) {
+          const float2 q = __ldg(reinterpret_cast<const float2*>(p.seg_prod + e0 + size_t(s2) * p.D));
+          carry.x = q.x * carry.x + e.x;
+          carry.y = q.y * carry.y + e.y;
+        } else {
+          carry.x = a_seg * carry.x + e.x;
+          carry.y = a_seg * carry.y + e.y;
+        }
+      }
+    }
+  }
 
   int buf = 0;
-  for (int tile0 = 0; tile0 < p.T; tile0 += LSF_WARPS * TPW, buf ^= 1) {
+  for (int tile0 = t_begin; tile0 < t_end; tile0 += LSF_WARPS * TPW, buf ^= 1) {
     const int t0 = tile0 + warp * TPW;
     float2 loc[TPW];
     float2 prod[TENSOR_ALPHA ? TPW : 1];
@@ -127,6 +154,7 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
         const float2 q = s_prod[buf][w][lane];
         c.x = q.x * c.x + e.x;
         c.y = q.y * c.y + e.y;
+        if (ENDS_ONLY) { pcarry.x *= q.x; pcarry.y *= q.y; }
       } else {
         c.x = a_run * c.x + e.x;
         c.y = a_run * c.y + e.y;
@@ -134,6 +162,7 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
     }
     carry = c;
     c = cn;
+    if (ENDS_ONLY) continue;
     // residual values are loaded up front so that the read-modify-write does not serialise
     float2 rold[TPW];
     if (p.resid) {
@@ -159,21 +188,56 @@ __global__ void __launch_bounds__(LSF_THREADS) lsf_scan_kernel(const LsfParams p
       }
     }
   }
+  if (ENDS_ONLY && ch_ok && warp == 0) {
+    const size_t e = (size_t(b) * (p.nseg - 1) + seg) * p.D + ch;
+    *reinterpret_cast<float2*>(p.seg_end + e) = carry;
+    if (TENSOR_ALPHA) *reinterpret_cast<float2*>(p.seg_prod + e) = pcarry;
+  }
 }
 
-template <bool TA, typename TM, typename TOut, int TPW>
+constexpr int LSF_TPW = 16;                       // tokens per warp per tile
+constexpr int LSF_TILE = LSF_WARPS * LSF_TPW;     // 128 tokens
+
+template <bool TA, typename TM, typename TOut>
 int launch_t(const LsfParams& p, cudaStream_t stream) {
-  dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B);
-  lsf_scan_kernel<TA, TM, TOut, TPW><<<grid, LSF_THREADS, 0, stream>>>(p);
+  if (p.nseg > 1) {
+    dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg - 1);
+    lsf_scan_kernel<TA, TM, TOut, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);
+    JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
+  }
+  dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
+  lsf_scan_kernel<TA, TM, TOut, LSF_TPW, false><<<grid, LSF_THREADS, 0, stream>>>(p);
   JB_LAUNCH_CHECK("lsf_scan_kernel");
   return JB200_OK;
 }
 
+// Segments so that about two CTAs per SM exist, each at least four tiles long.
+void pick_lsf_segments(int B, int T, int D, int sms, int* seg_len, int* nseg) {
+  const long ctas = long((D + LSF_CH - 1) / LSF_CH) * B;
+  long want = (2L * sms + ctas - 1) / ctas;
+  const long max_seg = T / (4 * LSF_TILE);
+  if (want > max_seg) want = max_seg;
+  if (want < 1) want = 1;
+  long len = (T + want - 1) / want;
+  len = (len + LSF_TILE - 1) / LSF_TILE * LSF_TILE;
+  *seg_len = int(len);
+  *nseg = int((T + len - 1) / len);
+}
+
 }  // namespace
+
+size_t lsf_scan_scratch_bytes(int B, int T, int D) {
+  if (B <= 0 || T <= 0 || D <= 0) return 0;
+  const int sms = sm_count();
+  int len, ns;
+  pick_lsf_segments(B, T, D, sms > 0 ? sms : 148, &len, &ns);
+  return size_t(2) * B * size_t(ns - 1) * D * sizeof(float);
+}
 
 int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
                     const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
-                    float* resid, void* out, int out_dtype, float* h_last, int B, int T, int D, cudaStream_t stream) {
+                    float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
+                    cudaStream_t stream) {
   JB_REQUIRE(B >= 0 && T >= 0 && D > 0, "lsf_scan: bad shape (%d, %d, %d)", B, T, D);
   JB_REQUIRE(D % 2 == 0, "lsf_scan: channel count (%d) must be even", D);
   JB_REQUIRE(B <= 65535, "lsf_scan: batch (%d) exceeds 65535", B);
@@ -193,18 +257,30 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
   p.m = m; p.alpha_t = alpha_tensor; p.alpha_s = alpha_scalar; p.act_var = act_var; p.var_scale = var_scale;
   p.alpha_min = alpha_min; p.alpha_max = alpha_max; p.h0 = h0; p.resid = resid; p.out = out; p.h_last = h_last;
   p.B = B; p.T = T; p.D = D;
+  p.seg_len = (T + LSF_TILE - 1) / LSF_TILE * LSF_TILE;
+  p.nseg = 1;
+  p.seg_end = p.seg_prod = nullptr;
+  if (scratch) {
+    JB_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & a8) == 0, "lsf_scan: scratch pointer misaligned");
+    const int sms = sm_count();
+    if (sms <= 0) return JB200_ERR_CUDA;
+    pick_lsf_segments(B, T, D, sms, &p.seg_len, &p.nseg);
+    p.seg_end = reinterpret_cast<float*>(scratch);
+    p.seg_prod = p.seg_end + size_t(B) * (p.nseg - 1) * D;
+  }
+  JB_REQUIRE(p.nseg <= 65535, "lsf_scan: too many segments");
   const bool ta = alpha_tensor != nullptr;
   using bf = __nv_bfloat16;
   if (!ta) {
-    if (m_dtype == 1 && out_dtype == 1) return launch_t<false, bf, bf, 32>(p, stream);
-    if (m_dtype == 1 && out_dtype == 0) return launch_t<false, bf, float, 32>(p, stream);
-    if (m_dtype == 0 && out_dtype == 0) return launch_t<false, float, float, 32>(p, stream);
-    return launch_t<false, float, bf, 32>(p, stream);
+    if (m_dtype == 1 && out_dtype == 1) return launch_t<false, bf, bf>(p, stream);
+    if (m_dtype == 1 && out_dtype == 0) return launch_t<false, bf, float>(p, stream);
+    if (m_dtype == 0 && out_dtype == 0) return launch_t<false, float, float>(p, stream);
+    return launch_t<false, float, bf>(p, stream);
   }
-  if (m_dtype == 1 && out_dtype == 1) return launch_t<true, bf, bf, 16>(p, stream);
-  if (m_dtype == 1 && out_dtype == 0) return launch_t<true, bf, float, 16>(p, stream);
-  if (m_dtype == 0 && out_dtype == 0) return launch_t<true, float, float, 16>(p, stream);
-  return launch_t<true, float, bf, 16>(p, stream);
+  if (m_dtype == 1 && out_dtype == 1) return launch_t<true, bf, bf>(p, stream);
+  if (m_dtype == 1 && out_dtype == 0) return launch_t<true, bf, float>(p, stream);
+  if (m_dtype == 0 && out_dtype == 0) return launch_t<true, float, float>(p, stream);
+  return launch_t<true, float, bf>(p, stream);
 }
 
 }  // namespace jb

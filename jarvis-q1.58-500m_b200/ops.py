@@ -316,7 +316,7 @@ def moe_finalize(stats, probs_sum, top1_hist, E: int, n_tokens: int, n_elems: in
 # --------------------------------------------------------------------------- LSF
 def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=None, var_scale=None,
              alpha_min: float = 0.1, alpha_max: float = 0.99, h0=None, resid=None, want_out: bool = True,
-             out_dtype=None, want_last: bool = True):
+             out_dtype=None, want_last: bool = True, segmented: bool = True):
     """m: (B, T, D) f32/bf16.  Returns (h_out or None, h_last f32 (B, D) or None)."""
     lib = _lib.load()
     if not (m.is_cuda and m.is_contiguous() and m.dim() == 3):
@@ -331,10 +331,15 @@ def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=N
             _need(t, torch.float32, "lsf_scan." + name)
     out = torch.empty((B, T, D), dtype=out_dtype or m.dtype, device=m.device) if want_out else None
     h_last = torch.empty((B, D), dtype=torch.float32, device=m.device) if want_last else None
+    scratch = None
+    if segmented:
+        nbytes = lib.jb200_lsf_scan_scratch_bytes(B, T, D)
+        if nbytes:
+            scratch = torch.empty((nbytes // 4,), dtype=torch.float32, device=m.device)
     _lib.check(
         lib.jb200_lsf_scan(_ptr(m), _dt(m), _ptr(alpha_tensor), _ptr(alpha_scalar), _ptr(act_var), _ptr(var_scale),
                            alpha_min, alpha_max, _ptr(h0), _ptr(resid), _ptr(out), _dt(out) if out is not None else 0,
-                           _ptr(h_last), B, T, D, _stream()),
+                           _ptr(h_last), _ptr(scratch), B, T, D, _stream()),
         "jb200_lsf_scan",
     )
     return out, h_last

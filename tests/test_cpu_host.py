@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     assert set(declared) == set(_lib.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.jb200_abi_version() >= 3
+    assert lib.jb200_abi_version() >= 4
     assert lib.jb200_moe_metadata_static_max_assignments() == 262144
 
 
@@ -34,7 +34,7 @@ def test_argument_errors_need_no_gpu():
     rc = lib.jb200_attn_scan(None, None, None, 64, None, None, None, 1, None, 0, None, None, 64, None, None, 1, 1, 1,
                              32, None)
     assert rc == _lib.ERR_ARG and "head_dim" in _lib.last_error()
-    rc = lib.jb200_lsf_scan(None, 0, None, None, None, None, 0.1, 0.99, None, None, None, 0, None, 1, 1, 3, None)
+    rc = lib.jb200_lsf_scan(None, 0, None, None, None, None, 0.1, 0.99, None, None, None, 0, None, None, 1, 1, 3, None)
     assert rc == _lib.ERR_ARG and "even" in _lib.last_error()
     rc = lib.jb200_moe_metadata_static(None, 1 << 20, 2, 4, None, None, None, None, None, None)
     assert rc == _lib.ERR_ARG and "built-in scratch limit" in _lib.last_error()

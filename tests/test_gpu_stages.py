@@ -305,6 +305,23 @@ def test_lsf_scan_bf16_with_residual(B, T, D):
     assert rel_l2(outb.float(), ref) < 4e-3
 
 
+def test_lsf_segmented_matches_single_pass_and_oracle():
+    g = torch.Generator().manual_seed(77)
+    B, T, D = 2, 3000, 192
+    m = torch.randn(B, T, D, generator=g)
+    a = torch.rand(B, T, D, generator=g) * 0.5 + 0.49
+    h0 = torch.randn(B, D, generator=g)
+    ref = orc.lsf_scan(m, a, h0)
+    seg, last = ops.lsf_scan(m.cuda(), alpha_tensor=a.cuda(), h0=h0.cuda(), segmented=True)
+    one, _ = ops.lsf_scan(m.cuda(), alpha_tensor=a.cuda(), h0=h0.cuda(), segmented=False)
+    assert rel_l2(seg, ref) < 1e-5 and rel_l2(one, ref) < 1e-5 and rel_l2(last, ref[:, -1]) < 1e-5
+    al = torch.tensor([0.985])
+    ref_s = orc.lsf_scan(m, float(al), h0)
+    seg_s, last_s = ops.lsf_scan(m.cuda(), alpha_scalar=al.cuda(), h0=h0.cuda(), segmented=True)
+    one_s, _ = ops.lsf_scan(m.cuda(), alpha_scalar=al.cuda(), h0=h0.cuda(), segmented=False)
+    assert rel_l2(seg_s, ref_s) < 1e-5 and rel_l2(one_s, ref_s) < 1e-5 and rel_l2(last_s, ref_s[:, -1]) < 1e-5
+
+
 def test_lsf_linearity_large():
     """Size-independent property at a full-size shape: scan(a*x + y) == a*scan(x) + scan(y)."""
     g = torch.Generator(device="cuda").manual_seed(0)
