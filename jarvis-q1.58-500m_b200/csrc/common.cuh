@@ -98,21 +98,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// try_wait that lets the hardware park the warp for up to `ns` nanoseconds while the phase is
+// incomplete.  A tight software poll instead keeps the waiter eligible every cycle, and the
+// greedy warp scheduler then starves the working warps that share its SM sub-partition.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any waiter gives up,
 // every other waiter of the CTA leaves at its next poll as well.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, unsigned int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0 = globaltimer_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
-        *abort_flag = 1u;
-        atomicCAS(status, 0u, code);
-        return false;
-      }
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+      *abort_flag = 1u;
+      atomicCAS(status, 0u, code);
+      return false;
     }
   }
 }
