@@ -174,6 +174,45 @@ def case_moe(a):
                       "rows_received_per_rank": [int(v) for v in allrecv]})
 
 
+def case_decode(a):
+    """Config 5: ragged state-carrying decode on the 606M model: B sequences, one token per step,
+    positions ~ U[1, 4096], carried attention state (B, H, 64, 64) f32 and LSF membrane per layer."""
+    from jarvis_b200 import modules as jm
+    dev = torch.device("cuda")
+    with torch.device(dev):
+        model = jm.Jarvis(max_seq_len=4096 + a.steps + 8)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for mod in model.modules():
+            if isinstance(mod, jm.TernaryLinear):
+                mod.weight.copy_(torch.randn(mod.weight.shape, generator=gen, device=dev) * 0.02)
+    model.eval()
+    B, L, H = a.B, len(model.blocks), 16
+    pos = torch.randint(1, 4097, (B,), generator=gen, device=dev, dtype=torch.int32)
+    state = {"h": [torch.randn(B, 1024, generator=gen, device=dev) for _ in range(L)],
+             "S": [torch.randn(B, H, 64, 64, generator=gen, device=dev) for _ in range(L)]}
+    idx = torch.randint(0, 50257, (a.steps, B, 1), generator=gen, device=dev)
+    sess = jm.DecodeSession(model, state, pos, max_position=4096 + a.steps + 8)
+    if not a.eager:
+        sess.capture()
+    else:
+        for w in range(3):
+            sess.step(idx[w])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for sidx in range(a.steps):
+        sess.step(idx[sidx])
+    e1.record()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    ms = e0.elapsed_time(e1) / a.steps
+    by = L * (2.0 * B * H * 64 * 64 * 4 + 5 * 2 ** 20) + 2.0 * 1024 * 50304
+    report("decode step (606M, all kernels + lm_head)", ms, bytes_=by,
+           extra={"B": B, "steps": a.steps, "tokens_per_s": B / ms * 1e3, "state_dtype": "f32",
+                  "cuda_graph": not a.eager})
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="case", required=True)
@@ -190,6 +229,9 @@ def main():
     s.add_argument("--C", type=int, default=1024); s.add_argument("--resid", action="store_true")
     s = sub.add_parser("moe")
     s.add_argument("--N", type=int, default=65536); s.add_argument("--zipf", type=float, default=1.2)
+    s = sub.add_parser("decode")
+    s.add_argument("--B", type=int, default=256); s.add_argument("--steps", type=int, default=64)
+    s.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     for p in sub.choices.values():
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
@@ -198,7 +240,7 @@ def main():
         lr = int(os.environ.get("LOCAL_RANK", "0"))
         torch.cuda.set_device(lr)
         dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
-    {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe}[a.case](a)
+    {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode}[a.case](a)
 
 
 if __name__ == "__main__":

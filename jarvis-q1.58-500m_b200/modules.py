@@ -149,22 +149,28 @@ class AssociativeLinearAttention(nn.Module):
         self.register_buffer("_i_idx_p1", i + 1)
         self.register_buffer("_c_m1_m_i", (cs - 1) - i)
         self._qkv = _PackCache()
+        self.max_position = None   # optional upper bound of per-sequence start positions (avoids a sync)
 
     def qkv_packed(self):
         return self._qkv.get([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], stack=False)
 
-    def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False):
+    def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False, inplace_state=False):
         """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None)."""
         C = xn_rows.shape[1]
         packed, alpha = self.qkv_packed()
         qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C, prepared=True)
-        end = (int(start_pos.max()) if torch.is_tensor(start_pos) else int(start_pos)) + T
+        if torch.is_tensor(start_pos):
+            # per-sequence positions: size the table from the caller's bound when given (no host sync)
+            end = (self.max_position if self.max_position is not None else int(start_pos.max())) + T
+        else:
+            end = int(start_pos) + T
         cos, sin = self.rotary.half_tables(end, xn_rows.device)
         gamma = torch.sigmoid(self.gamma_raw.detach().float())
         if h_prev is not None:
             h_prev = h_prev.to(torch.float32).contiguous()
         return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
-                             start_pos=start_pos, state_in=h_prev, want_state=want_state)
+                             start_pos=start_pos, state_in=h_prev, want_state=want_state,
+                             state_out=h_prev if (inplace_state and h_prev is not None) else None)
 
     def forward_with_state(self, x, start_pos=0, h_prev=None):
         B, T, C = x.shape
@@ -327,12 +333,13 @@ class JarvisBlock(nn.Module):
         self.liquid = LiquidStateFusion(d_model)
         self.reflect = ReflectivePenalty()
 
-    def forward_rows(self, x, B, T, h_prev=None, start_pos=0, attn_state=None, want_attn_state=False):
+    def forward_rows(self, x, B, T, h_prev=None, start_pos=0, attn_state=None, want_attn_state=False,
+                     inplace_state=False):
         """x: f32 (B*T, C) residual stream, UPDATED IN PLACE.  Returns (h_last f32 (B, C), scalars f32
         [l_balance, act_mean, act_var], attention state or None)."""
         C = x.shape[1]
         xn = ops.rmsnorm(x, self.norm1.weight.detach().float(), self.norm1.eps)
-        o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state)
+        o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state, inplace_state)
         po, ao = self.attn.out_proj.packed()
         ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)          # x += attn(norm1(x))
         xn = ops.rmsnorm(x, self.norm2.weight.detach().float(), self.norm2.eps)
@@ -341,7 +348,9 @@ class JarvisBlock(nn.Module):
                                  var_scale=self.liquid.var_scale.detach().float().reshape(1),
                                  alpha_min=self.liquid.alpha_min, alpha_max=self.liquid.alpha_max,
                                  h0=None if h_prev is None else h_prev.float().contiguous(),
-                                 resid=x.view(B, T, C), want_out=False)            # x += lsf(moe(norm2(x)))
+                                 resid=x.view(B, T, C), want_out=False,
+                                 last_out=h_prev if (inplace_state and h_prev is not None) else None)
+        # x += lsf(moe(norm2(x)))
         return h_last, scalars, state
 
     def forward(self, x, h_prev=None, start_pos: int = 0):
@@ -436,6 +445,33 @@ class Jarvis(nn.Module):
         return ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
 
     @torch.no_grad()
+    def step(self, idx, positions=None, state=None, max_position=None, inplace=False):
+        """Explicit-state step for decode / chunked prefill, beyond the reference API: `state` is None
+        (fresh sequences) or the dict returned by the previous call ({"h": LSF membranes, "S": attention
+        states (B, H, 64, 64) f32, per layer}); `positions` is an int or an int32 (B,) tensor holding each
+        sequence's first position (ragged batches).  With inplace=True (short steps only: one segment per
+        sequence) the tensors of `state` are updated in place.  Returns (logits (B, T, vocab), new state)."""
+        if self.training:
+            raise RuntimeError("Jarvis (sm_100a): inference only; call .eval() first")
+        B, T = idx.shape
+        n = len(self.blocks)
+        x = ops.embedding(idx.contiguous(), self.tok_emb.weight.detach().float()).view(B * T, self.d_model)
+        pos = 0 if positions is None else positions
+        hs = state["h"] if state is not None else [None] * n
+        Ss = state["S"] if state is not None else [None] * n
+        new_h, new_s = [], []
+        for i, block in enumerate(self.blocks):
+            block.attn.max_position = max_position
+            h_last, _, S = block.forward_rows(x, B, T, hs[i], pos, Ss[i], want_attn_state=True,
+                                              inplace_state=inplace and state is not None)
+            new_h.append(h_last)
+            new_s.append(S)
+        hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
+        vocab = self.lm_head.weight.shape[0]
+        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)[..., :vocab]
+        return logits, {"h": new_h, "S": new_s}
+
+    @torch.no_grad()
     def forward(self, idx, targets=None, persist_state=False):
         B, T = idx.shape
         hidden = self.hidden_rows(idx, persist_state)
@@ -455,6 +491,57 @@ class Jarvis(nn.Module):
     def param_count(self):
         n = sum(p.numel() for p in self.parameters())
         return n, f"{n/1e6:.1f}M parameters"
+
+
+class DecodeSession:
+    """One-token-per-step decode of B concurrent sequences with the whole step captured in a CUDA
+    graph (the pattern of the reference's runtime/cuda_graph_runner.py:47-70, applied to the real
+    model).  The carried state lives in buffers owned by the session and is updated in place, so a
+    replay costs one launch; per-sequence positions advance on the device."""
+
+    def __init__(self, model: "Jarvis", state: dict, positions: torch.Tensor, max_position: int):
+        self.model = model
+        self.state = {"h": [t.float().contiguous() for t in state["h"]], "S": [t.float().contiguous() for t in state["S"]]}
+        self.positions = positions.to(torch.int32).clone()
+        self.max_position = max_position
+        B = self.positions.shape[0]
+        self.idx = torch.zeros((B, 1), dtype=torch.int64, device=self.positions.device)
+        self.graph = None
+        self.logits = None
+
+    def _one(self):
+        logits, _ = self.model.step(self.idx, self.positions, self.state, max_position=self.max_position, inplace=True)
+        self.positions.add_(1)
+        return logits
+
+    def capture(self):
+        """Two eager warm-up steps on a side stream, then capture.  The warm-up steps advance the state:
+        call before feeding real tokens, or re-load the state afterwards with load_state()."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._one()
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self._one()
+        return self
+
+    def load_state(self, state: dict, positions: torch.Tensor):
+        for dst, src in zip(self.state["h"], state["h"]):
+            dst.copy_(src)
+        for dst, src in zip(self.state["S"], state["S"]):
+            dst.copy_(src)
+        self.positions.copy_(positions)
+
+    def step(self, idx: torch.Tensor) -> torch.Tensor:
+        """idx: int64 (B, 1) -> logits (B, 1, vocab) (a buffer reused by the next step)."""
+        self.idx.copy_(idx)
+        if self.graph is None:
+            return self._one()
+        self.graph.replay()
+        return self.logits
 
 
 def install(model: nn.Module) -> nn.Module:
@@ -494,5 +581,5 @@ def ternary_init_(module: nn.Module, std: float = 0.02, generator=None) -> nn.Mo
 __all__ = [
     "RMSNorm", "TernaryLinear", "RotaryEmbedding", "AssociativeLinearAttention", "CUDAAssociativeLinearAttention",
     "SparseMoELayer", "CUDASparseMoELayer", "LiquidStateFusion", "LiquidStateFusionExt", "ReflectivePenalty",
-    "JarvisBlock", "Jarvis", "install", "ternary_init_",
+    "JarvisBlock", "Jarvis", "DecodeSession", "install", "ternary_init_",
 ]

@@ -196,7 +196,8 @@ def embedding(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 # --------------------------------------------------------------------------- attention scan
 def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, cos_tab: torch.Tensor,
               sin_tab: torch.Tensor, B: int, T: int, H: int, *, start_pos=0, state_in: torch.Tensor | None = None,
-              want_state: bool = False, out: torch.Tensor | None = None, segmented: bool = True):
+              want_state: bool = False, out: torch.Tensor | None = None, segmented: bool = True,
+              state_out: torch.Tensor | None = None):
     """Feature map + RoPE + decayed causal scan.  q, k, v: bf16 2-D views (B*T, H*64) sharing one
     row stride (e.g. column slices of a fused q|k|v matrix).  start_pos: int, or int32 (B,) tensor of
     per-sequence first positions.  Returns (o bf16 (B*T, H*64), final state f32 (B,H,64,64) or None)."""
@@ -223,7 +224,14 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
             raise RuntimeError("attn_scan: state_in must be (B, H, 64, 64)")
     if out is None:
         out = torch.empty((B * T, H * 64), dtype=torch.bfloat16, device=q.device)
-    s_out = torch.empty((B, H, 64, 64), dtype=torch.float32, device=q.device) if want_state else None
+    if state_out is not None:
+        # may alias state_in when the call runs one segment per sequence (every CTA reads its own
+        # (sequence, head) state before it writes it): the decode step updates states in place
+        s_out = _need(state_out, torch.float32, "attn_scan.state_out")
+        if state_out is state_in:
+            segmented = False
+    else:
+        s_out = torch.empty((B, H, 64, 64), dtype=torch.float32, device=q.device) if want_state else None
     scratch = None
     if segmented:
         nbytes = lib.jb200_attn_scan_scratch_bytes(B, T, H)
@@ -316,7 +324,7 @@ def moe_finalize(stats, probs_sum, top1_hist, E: int, n_tokens: int, n_elems: in
 # --------------------------------------------------------------------------- LSF
 def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=None, var_scale=None,
              alpha_min: float = 0.1, alpha_max: float = 0.99, h0=None, resid=None, want_out: bool = True,
-             out_dtype=None, want_last: bool = True, segmented: bool = True):
+             out_dtype=None, want_last: bool = True, segmented: bool = True, last_out: torch.Tensor | None = None):
     """m: (B, T, D) f32/bf16.  Returns (h_out or None, h_last f32 (B, D) or None)."""
     lib = _lib.load()
     if not (m.is_cuda and m.is_contiguous() and m.dim() == 3):
@@ -330,7 +338,12 @@ def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=N
         if t is not None:
             _need(t, torch.float32, "lsf_scan." + name)
     out = torch.empty((B, T, D), dtype=out_dtype or m.dtype, device=m.device) if want_out else None
-    h_last = torch.empty((B, D), dtype=torch.float32, device=m.device) if want_last else None
+    if last_out is not None:
+        h_last = _need(last_out, torch.float32, "lsf_scan.last_out")   # may alias h0 in unsegmented calls
+        if last_out is h0:
+            segmented = False
+    else:
+        h_last = torch.empty((B, D), dtype=torch.float32, device=m.device) if want_last else None
     scratch = None
     if segmented:
         nbytes = lib.jb200_lsf_scan_scratch_bytes(B, T, D)

@@ -87,9 +87,17 @@ def feature_map_rope(q: torch.Tensor, k: torch.Tensor, start_pos: int = 0):
     T = q.shape[-2]
     q = (F.elu(q) + 1.0) / math.sqrt(D)
     k = F.elu(k) + 1.0
-    cos, sin = rope_tables(start_pos + T, D)
-    cos = cos[start_pos:].to(q.dtype)
-    sin = sin[start_pos:].to(q.dtype)
+    if torch.is_tensor(start_pos):
+        # per-sequence first positions (ragged decode): the reference takes one int for the whole batch
+        # (RotaryEmbedding.forward, jarvis_model.py:59-68); this is the same table, gathered per sequence
+        cos_t, sin_t = rope_tables(int(start_pos.max()) + T, D)
+        pos = start_pos.long()[:, None] + torch.arange(T)[None, :]
+        cos = cos_t[pos].to(q.dtype)[:, None]          # (B, 1, T, D)
+        sin = sin_t[pos].to(q.dtype)[:, None]
+    else:
+        cos, sin = rope_tables(start_pos + T, D)
+        cos = cos[start_pos:].to(q.dtype)
+        sin = sin[start_pos:].to(q.dtype)
 
     def rot(x):
         x1, x2 = x[..., : D // 2], x[..., D // 2:]
@@ -310,3 +318,21 @@ def model_forward(idx, sd: dict, n_layers: int, n_heads: int, h_prevs=None, star
     if return_hidden:
         return hidden, h_last
     return F.linear(hidden, sd["lm_head.weight"]), h_last
+
+
+def model_step(idx, sd: dict, n_layers: int, n_heads: int, h_prevs=None, attn_states=None, positions=0):
+    """State-carrying step: like model_forward, but every block also receives and returns its attention
+    state S (the h_prev path of associative_attention.py:273-308, which the reference model never
+    feeds) and `positions` may be a per-sequence tensor.  The LSF decay is computed from the step's own
+    batch, as in every reference call.  Returns (logits, h_last list, attention-state list)."""
+    x = F.embedding(idx, sd["tok_emb.weight"])
+    h_last, states = [], []
+    for i in range(n_layers):
+        pre = f"blocks.{i}."
+        p = {name[len(pre):]: t for name, t in sd.items() if name.startswith(pre)}
+        r = block_forward(x, p, n_heads, None if h_prevs is None else h_prevs[i], positions,
+                          None if attn_states is None else attn_states[i])
+        x = r["x"]
+        h_last.append(r["h_last"])
+        states.append(r["attn_state"])
+    return F.linear(rmsnorm(x, sd["final_norm.weight"]), sd["lm_head.weight"]), h_last, states
