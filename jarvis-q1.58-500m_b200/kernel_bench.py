@@ -197,7 +197,7 @@ def case_decode(a):
         sess.capture()
     else:
         for w in range(3):
-            sess.step(idx[w])
+            sess.step(idx[w % a.steps])
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
