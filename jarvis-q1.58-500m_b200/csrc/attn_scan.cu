@@ -390,6 +390,53 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 }
 
+// One-token step (decode): S <- gamma*S + v (x) k', o = S q' for every (sequence, head).  Pure state
+// streaming: 2 x 16 KiB of fp32 state per (sequence, head) against 384 B of q, k, v, so the kernel is a
+// coalesced read-modify-write of S with the feature map + RoPE of the single token done in shared memory.
+// Thread t owns state row t/4, columns 16*(t%4)..+15; s_out may alias s_in.
+__global__ void __launch_bounds__(256)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                   const __nv_bfloat16* __restrict__ v, int ld_qkv, const AttnParams p) {
+  __shared__ float sq[D], sk[D], sv[D], rq[D], rk[D];
+  const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+  const float gamma = __ldg(p.gamma + h);
+  if (t < D) {
+    const size_t off = size_t(b) * ld_qkv + h * D + t;
+    sq[t] = elu1(__bfloat162float(q[off])) * 0.125f;
+    sk[t] = elu1(__bfloat162float(k[off]));
+    sv[t] = __bfloat162float(v[off]);
+  }
+  __syncthreads();
+  if (t < D / 2) {
+    int pos = p.pos0 ? p.pos0[b] : p.pos0_scalar;
+    pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+    const float c = __ldg(p.cos_tab + size_t(pos) * 32 + t), sn = __ldg(p.sin_tab + size_t(pos) * 32 + t);
+    rq[t] = sq[t] * c - sq[t + 32] * sn;  rq[t + 32] = sq[t + 32] * c + sq[t] * sn;
+    rk[t] = sk[t] * c - sk[t + 32] * sn;  rk[t + 32] = sk[t + 32] * c + sk[t] * sn;
+  }
+  __syncthreads();
+  const int row = t >> 2, c0 = (t & 3) * 16;
+  const size_t so = (size_t(b) * p.H + h) * D * D + size_t(row) * D + c0;
+  const float vr = sv[row];
+  float acc = 0.f;
+  float4 st[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    st[i] = p.s_in ? *reinterpret_cast<const float4*>(p.s_in + so + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int c = c0 + 4 * i;
+    st[i].x = gamma * st[i].x + vr * rk[c];      st[i].y = gamma * st[i].y + vr * rk[c + 1];
+    st[i].z = gamma * st[i].z + vr * rk[c + 2];  st[i].w = gamma * st[i].w + vr * rk[c + 3];
+    acc += st[i].x * rq[c] + st[i].y * rq[c + 1] + st[i].z * rq[c + 2] + st[i].w * rq[c + 3];
+  }
+  if (p.s_out) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(p.s_out + so + 4 * i) = st[i];
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  if ((t & 3) == 0) p.o[size_t(b) * p.ld_o + h * D + row] = __float2bfloat16_rn(acc);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -459,6 +506,19 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   JB_REQUIRE(size_t(B) * T < (size_t(1) << 31), "attn_scan: too many rows");
   JB_REQUIRE(n_pos >= 1, "attn_scan: empty RoPE table");
   if (!pos0) JB_REQUIRE(pos0_scalar >= 0 && pos0_scalar + T <= n_pos, "attn_scan: RoPE table (%d rows) too short for positions %d..%d", n_pos, pos0_scalar, pos0_scalar + T - 1);
+  if (T == 1) {
+    JB_REQUIRE(!s_in || aligned16(s_in), "attn_scan: state pointer must be 16-byte aligned for single-token steps");
+    JB_REQUIRE(!s_out || aligned16(s_out), "attn_scan: state pointer must be 16-byte aligned for single-token steps");
+    AttnParams dp;
+    dp.gamma = gamma; dp.cos_tab = cos_tab; dp.sin_tab = sin_tab; dp.pos0 = pos0; dp.pos0_scalar = pos0_scalar;
+    dp.n_pos = n_pos; dp.s_in = s_in; dp.s_out = s_out; dp.o = reinterpret_cast<__nv_bfloat16*>(o); dp.ld_o = ld_o;
+    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.status = nullptr;
+    attn_decode_kernel<<<dim3(H, B), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q),
+                                                        reinterpret_cast<const __nv_bfloat16*>(k),
+                                                        reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
+    JB_LAUNCH_CHECK("attn_decode_kernel");
+    return JB200_OK;
+  }
   CUtensorMap tq, tk, tv;
   int rc;
   if ((rc = make_map(&tq, q, B * T, H * D, ld_qkv)) != JB200_OK) return rc;

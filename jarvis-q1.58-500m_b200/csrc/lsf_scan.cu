@@ -195,11 +195,50 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
   }
 }
 
+// Short sequences (decode steps): one thread per channel pair walks the few tokens itself.
+template <bool TENSOR_ALPHA, typename TM, typename TOut>
+__global__ void __launch_bounds__(256) lsf_short_kernel(const LsfParams p) {
+  const size_t pair = size_t(blockIdx.x) * 256 + threadIdx.x;
+  const int half_d = p.D / 2;
+  if (pair >= size_t(p.B) * half_d) return;
+  const int b = int(pair / half_d), ch = int(pair % half_d) * 2;
+  const TM* m = reinterpret_cast<const TM*>(p.m);
+  const TM* at = reinterpret_cast<const TM*>(p.alpha_t);
+  TOut* out = reinterpret_cast<TOut*>(p.out);
+  float alpha = 0.f;
+  if (!TENSOR_ALPHA) {
+    if (p.alpha_s) alpha = __ldg(p.alpha_s);
+    else alpha = p.alpha_min + (p.alpha_max - p.alpha_min) * (1.0f / (1.0f + expf(__ldg(p.var_scale) * __ldg(p.act_var))));
+  }
+  float2 h = p.h0 ? *reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch) : make_float2(0.f, 0.f);
+  for (int t = 0; t < p.T; ++t) {
+    const size_t o = (size_t(b) * p.T + t) * p.D + ch;
+    const float2 mv = ld2<TM>(m + o);
+    float2 a = make_float2(alpha, alpha);
+    if (TENSOR_ALPHA) a = ld2<TM>(at + o);
+    h.x = a.x * h.x + (1.0f - a.x) * mv.x;
+    h.y = a.y * h.y + (1.0f - a.y) * mv.y;
+    if (out) st2<TOut>(out + o, h.x, h.y);
+    if (p.resid) {
+      float2* r = reinterpret_cast<float2*>(p.resid + o);
+      const float2 rv = *r;
+      *r = make_float2(rv.x + h.x, rv.y + h.y);
+    }
+  }
+  if (p.h_last) *reinterpret_cast<float2*>(p.h_last + size_t(b) * p.D + ch) = h;
+}
+
 constexpr int LSF_TPW = 16;                       // tokens per warp per tile
 constexpr int LSF_TILE = LSF_WARPS * LSF_TPW;     // 128 tokens
 
 template <bool TA, typename TM, typename TOut>
 int launch_t(const LsfParams& p, cudaStream_t stream) {
+  if (p.T <= 8) {
+    const size_t pairs = size_t(p.B) * (p.D / 2);
+    lsf_short_kernel<TA, TM, TOut><<<unsigned((pairs + 255) / 256), 256, 0, stream>>>(p);
+    JB_LAUNCH_CHECK("lsf_short_kernel");
+    return JB200_OK;
+  }
   if (p.nseg > 1) {
     dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg - 1);
     lsf_scan_kernel<TA, TM, TOut, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);

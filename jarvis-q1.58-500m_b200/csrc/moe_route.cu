@@ -30,6 +30,7 @@ constexpr int META_CHUNK = 256;                     // assignments per CTA of th
 template <int E>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w_router, int n_tokens, int C,
+                   int tokens_per_cta,
                    int64_t* __restrict__ topk_idx, float* __restrict__ gates, float* __restrict__ probs_out,
                    double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
   extern __shared__ float w_s[];  // [E][C]
@@ -42,8 +43,8 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   float p_local[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) p_local[e] = 0.f;
-  const int tok0 = blockIdx.x * ROUTER_TOKENS_PER_CTA;
-  for (int tt = warp; tt < ROUTER_TOKENS_PER_CTA; tt += ROUTER_THREADS / 32) {
+  const int tok0 = blockIdx.x * tokens_per_cta;
+  for (int tt = warp; tt < tokens_per_cta; tt += ROUTER_THREADS / 32) {
     const int tok = tok0 + tt;
     if (tok >= n_tokens) break;
     const __nv_bfloat16* xr = x + size_t(tok) * C;
@@ -280,17 +281,19 @@ int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, 
   JB_REQUIRE(x_bf16 && w_router && topk_idx && gates, "router_top2: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_router), "router_top2: pointers must be 16-byte aligned");
   if (n_tokens == 0) return JB200_OK;
-  const int blocks = (n_tokens + ROUTER_TOKENS_PER_CTA - 1) / ROUTER_TOKENS_PER_CTA;
+  // small batches (decode steps): one token per warp so that more than a handful of CTAs exist
+  const int tpc = n_tokens <= 4096 ? ROUTER_THREADS / 32 : ROUTER_TOKENS_PER_CTA;
+  const int blocks = (n_tokens + tpc - 1) / tpc;
   const size_t smem = size_t(E) * C * sizeof(float);
   if (E == 4) {
     JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     router_top2_kernel<4><<<blocks, ROUTER_THREADS, smem, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, topk_idx, gates, probs_out, probs_sum,
+        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, tpc, topk_idx, gates, probs_out, probs_sum,
         top1_hist);
   } else {
     JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     router_top2_kernel<8><<<blocks, ROUTER_THREADS, smem, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, topk_idx, gates, probs_out, probs_sum,
+        reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, tpc, topk_idx, gates, probs_out, probs_sum,
         top1_hist);
   }
   JB_LAUNCH_CHECK("router_top2_kernel");
