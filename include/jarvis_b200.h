@@ -164,6 +164,14 @@ int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, con
 int jb200_router_top2(const void* x, const float* w_router, int N, int C, int E, int64_t* topk_idx, float* gates,
                       float* probs, double* probs_sum, int32_t* top1_hist, void* stream);
 
+/* norm2 + router in one pass over the f32 residual stream (JarvisBlock.forward, jarvis_model.py:431:
+ * self.moe(self.norm2(x)) with RMSNorm :25-26 and the router :218-224): writes xn = bf16(RMSNorm(x))
+ * for the expert GEMMs and routes from those same rounded values, bit-identical to jb200_rmsnorm followed
+ * by jb200_router_top2.  x: f32 [N][C] (C % 8 == 0, C <= 1024); other arguments as jb200_router_top2. */
+int jb200_rmsnorm_router(const float* x, const float* w_norm, float eps, void* xn, const float* w_router, int N,
+                         int C, int E, int64_t* topk_idx, float* gates, double* probs_sum, int32_t* top1_hist,
+                         void* stream);
+
 /* compute_metadata (sparse_model_cuda/sparse_model_cpp.cpp:83-90, kernel sparse_model.cu:23-90):
  * stable partition of assignments m = token*K + k by expert.  All outputs i32:
  * expert_counts [E], expert_offsets [E+1], scatter_map [N][K] (slot of m), gather_map [N*K]

@@ -41,6 +41,7 @@ PROTOTYPES = {
     "jb200_attn_scan": (_I, [_P, _P, _P, _I, _P, _P, _P, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P]),
     "jb200_attn_scan_scratch_bytes": (_Z, [_I, _I, _I]),
     "jb200_router_top2": (_I, [_P, _P, _I, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "jb200_rmsnorm_router": (_I, [_P, _P, _F, _P, _P, _I, _I, _I, _P, _P, _P, _P, _P]),
     "jb200_moe_metadata_scratch_bytes": (_Z, [_I, _I, _I]),
     "jb200_moe_metadata": (_I, [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P]),
     "jb200_moe_metadata_static_max_assignments": (_I, []),

@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 4; }
+int jb200_abi_version(void) { return 5; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -177,6 +177,13 @@ int jb200_router_top2(const void* x, const float* w_router, int N, int C, int E,
                       float* probs, double* probs_sum, int32_t* top1_hist, void* stream) {
   return launch_router_top2(x, w_router, N, C, E, topk_idx, gates, probs, probs_sum, top1_hist,
                             static_cast<cudaStream_t>(stream));
+}
+
+int jb200_rmsnorm_router(const float* x, const float* w_norm, float eps, void* xn, const float* w_router, int N,
+                         int C, int E, int64_t* topk_idx, float* gates, double* probs_sum, int32_t* top1_hist,
+                         void* stream) {
+  return launch_rmsnorm_router(x, w_norm, eps, xn, w_router, N, C, E, topk_idx, gates, probs_sum, top1_hist,
+                               static_cast<cudaStream_t>(stream));
 }
 
 size_t jb200_moe_metadata_scratch_bytes(int N, int K, int E) { return moe_metadata_scratch_bytes(N, K, E); }

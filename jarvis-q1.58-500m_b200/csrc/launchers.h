@@ -27,6 +27,9 @@ int launch_embedding(const int64_t* idx, const float* table, int vocab, float* o
 
 int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, int C, int E, int64_t* topk_idx,
                        float* gates, float* probs_out, double* probs_sum, int* top1_hist, cudaStream_t stream);
+int launch_rmsnorm_router(const float* x, const float* w_norm, float eps, void* xn_bf16, const float* w_router,
+                          int n_tokens, int C, int E, int64_t* topk_idx, float* gates, double* probs_sum,
+                          int* top1_hist, cudaStream_t stream);
 size_t moe_metadata_scratch_bytes(int n_tokens, int K, int E);
 int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int* expert_counts, int* expert_offsets,
                         int* scatter_map, int* gather_map, int* gate_idx_map, void* scratch, cudaStream_t stream);

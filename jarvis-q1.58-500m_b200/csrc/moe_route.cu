@@ -27,6 +27,54 @@ constexpr int META_CHUNK = 256;                     // assignments per CTA of th
 // ---------------------------------------------------------------------------------------------
 // router
 // ---------------------------------------------------------------------------------------------
+// logits of one token (already warp-reduced, identical in every lane) -> softmax, top-2 with ties going
+// to the lower expert id, gates, and the per-warp accumulators of P and the top-1 histogram.
+template <int E>
+__device__ __forceinline__ void router_finish(const float (&acc)[E], int lane, int tok, int64_t* topk_idx,
+                                              float* gates, float* probs_out, int* h_acc, float (&p_local)[E]) {
+  float mx = acc[0];
+#pragma unroll
+  for (int e = 1; e < E; ++e) mx = fmaxf(mx, acc[e]);
+  float p[E], den = 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) { p[e] = expf(acc[e] - mx); den += p[e]; }
+  const float inv = 1.0f / den;
+  int i0 = 0, i1 = -1;
+  float p0 = -1.f, p1 = -1.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    p[e] *= inv;
+    if (p[e] > p0) { p1 = p0; i1 = i0; p0 = p[e]; i0 = e; }
+    else if (p[e] > p1) { p1 = p[e]; i1 = e; }
+  }
+  if (lane == 0) {
+    topk_idx[size_t(tok) * 2 + 0] = i0;
+    topk_idx[size_t(tok) * 2 + 1] = i1;
+    const float g = p0 + p1 + 1e-8f;
+    gates[size_t(tok) * 2 + 0] = p0 / g;
+    gates[size_t(tok) * 2 + 1] = p1 / g;
+    if (probs_out) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) probs_out[size_t(tok) * E + e] = p[e];
+    }
+    atomicAdd(&h_acc[i0], 1);
+#pragma unroll
+    for (int e = 0; e < E; ++e) p_local[e] += p[e];
+  }
+}
+
+// 8 consecutive activations times the matching router weights of every expert
+template <int E>
+__device__ __forceinline__ void router_dot8(const float (&xv)[8], const float* w_s, int C, int c, float (&acc)[E]) {
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float4 wa = *reinterpret_cast<const float4*>(w_s + e * C + c);
+    const float4 wb = *reinterpret_cast<const float4*>(w_s + e * C + c + 4);
+    acc[e] += xv[0] * wa.x + xv[1] * wa.y + xv[2] * wa.z + xv[3] * wa.w + xv[4] * wb.x + xv[5] * wb.y +
+              xv[6] * wb.z + xv[7] * wb.w;
+  }
+}
+
 template <int E>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w_router, int n_tokens, int C,
@@ -55,46 +103,87 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(xr + c));
       const float xv[8] = {bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y),
                            bf16_lo(v.z), bf16_hi(v.z), bf16_lo(v.w), bf16_hi(v.w)};
+      router_dot8<E>(xv, w_s, C, c, acc);
+    }
 #pragma unroll
-      for (int e = 0; e < E; ++e) {
-        const float4 wa = *reinterpret_cast<const float4*>(w_s + e * C + c);
-        const float4 wb = *reinterpret_cast<const float4*>(w_s + e * C + c + 4);
-        acc[e] += xv[0] * wa.x + xv[1] * wa.y + xv[2] * wa.z + xv[3] * wa.w + xv[4] * wb.x + xv[5] * wb.y +
-                  xv[6] * wb.z + xv[7] * wb.w;
+    for (int e = 0; e < E; ++e) acc[e] = warp_sum(acc[e]);
+    router_finish<E>(acc, lane, tok, topk_idx, gates, probs_out, h_acc, p_local);
+  }
+  if (lane == 0) {
+#pragma unroll
+    for (int e = 0; e < E; ++e) p_acc[warp][e] = p_local[e];
+  }
+  __syncthreads();
+  if (threadIdx.x < E) {
+    float s = 0.f;
+    for (int w = 0; w < ROUTER_THREADS / 32; ++w) s += p_acc[w][threadIdx.x];
+    if (probs_sum) atomicAdd(&probs_sum[threadIdx.x], double(s));
+    if (top1_hist && h_acc[threadIdx.x]) atomicAdd(&top1_hist[threadIdx.x], h_acc[threadIdx.x]);
+  }
+}
+
+// RMSNorm (norm2 of the block, jarvis_model.py:25-26, :431) fused with the router: the normalised row
+// is rounded to bf16 and stored for the expert GEMMs, and the SAME rounded values feed the router
+// logits in the same summation order as router_top2_kernel, so routing is bit-identical to running
+// the two kernels separately while the row is read from HBM once.
+template <int E>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_norm, float eps,
+                      __nv_bfloat16* __restrict__ xn, const float* __restrict__ w_router, int n_tokens, int C,
+                      int tokens_per_cta, int64_t* __restrict__ topk_idx, float* __restrict__ gates,
+                      double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
+  extern __shared__ float w_s[];  // [E][C]
+  __shared__ float p_acc[ROUTER_THREADS / 32][E];
+  __shared__ int h_acc[E];
+  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[i] = __ldg(w_router + i);
+  if (threadIdx.x < E) h_acc[threadIdx.x] = 0;
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float p_local[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) p_local[e] = 0.f;
+  const int tok0 = blockIdx.x * tokens_per_cta;
+  for (int tt = warp; tt < tokens_per_cta; tt += ROUTER_THREADS / 32) {
+    const int tok = tok0 + tt;
+    if (tok >= n_tokens) break;
+    const float* xr = x + size_t(tok) * C;
+    float v[4][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(xr + c));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(xr + c) + 1);
+        v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss / float(C) + eps);
+    float acc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = (i * 32 + lane) * 8;
+      if (c < C) {
+        const float4 wa = __ldg(reinterpret_cast<const float4*>(w_norm + c));
+        const float4 wb = __ldg(reinterpret_cast<const float4*>(w_norm + c) + 1);
+        const uint4 pk = make_uint4(pack_bf16x2(v[i][0] * r * wa.x, v[i][1] * r * wa.y),
+                                    pack_bf16x2(v[i][2] * r * wa.z, v[i][3] * r * wa.w),
+                                    pack_bf16x2(v[i][4] * r * wb.x, v[i][5] * r * wb.y),
+                                    pack_bf16x2(v[i][6] * r * wb.z, v[i][7] * r * wb.w));
+        *reinterpret_cast<uint4*>(xn + size_t(tok) * C + c) = pk;
+        const float xv[8] = {bf16_lo(pk.x), bf16_hi(pk.x), bf16_lo(pk.y), bf16_hi(pk.y),
+                             bf16_lo(pk.z), bf16_hi(pk.z), bf16_lo(pk.w), bf16_hi(pk.w)};
+        router_dot8<E>(xv, w_s, C, c, acc);
       }
     }
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] = warp_sum(acc[e]);
-    // softmax, then top-2 with ties going to the lower expert id (every lane computes the same)
-    float mx = acc[0];
-#pragma unroll
-    for (int e = 1; e < E; ++e) mx = fmaxf(mx, acc[e]);
-    float p[E], den = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) { p[e] = expf(acc[e] - mx); den += p[e]; }
-    const float inv = 1.0f / den;
-    int i0 = 0, i1 = -1;
-    float p0 = -1.f, p1 = -1.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) {
-      p[e] *= inv;
-      if (p[e] > p0) { p1 = p0; i1 = i0; p0 = p[e]; i0 = e; }
-      else if (p[e] > p1) { p1 = p[e]; i1 = e; }
-    }
-    if (lane == 0) {
-      topk_idx[size_t(tok) * 2 + 0] = i0;
-      topk_idx[size_t(tok) * 2 + 1] = i1;
-      const float g = p0 + p1 + 1e-8f;
-      gates[size_t(tok) * 2 + 0] = p0 / g;
-      gates[size_t(tok) * 2 + 1] = p1 / g;
-      if (probs_out) {
-#pragma unroll
-        for (int e = 0; e < E; ++e) probs_out[size_t(tok) * E + e] = p[e];
-      }
-      atomicAdd(&h_acc[i0], 1);
-#pragma unroll
-      for (int e = 0; e < E; ++e) p_local[e] += p[e];
-    }
+    router_finish<E>(acc, lane, tok, topk_idx, gates, nullptr, h_acc, p_local);
   }
   if (lane == 0) {
 #pragma unroll
@@ -297,6 +386,30 @@ int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, 
         top1_hist);
   }
   JB_LAUNCH_CHECK("router_top2_kernel");
+  return JB200_OK;
+}
+
+int launch_rmsnorm_router(const float* x, const float* w_norm, float eps, void* xn_bf16, const float* w_router,
+                          int n_tokens, int C, int E, int64_t* topk_idx, float* gates, double* probs_sum,
+                          int* top1_hist, cudaStream_t stream) {
+  JB_REQUIRE(n_tokens >= 0 && C > 0, "rmsnorm_router: bad shape");
+  JB_REQUIRE(E == 4 || E == 8, "rmsnorm_router: num_experts (%d) must be 4 or 8", E);
+  JB_REQUIRE(C % 8 == 0 && C <= 1024, "rmsnorm_router: d_model (%d) must be a multiple of 8 and at most 1024", C);
+  JB_REQUIRE(x && w_norm && xn_bf16 && w_router && topk_idx && gates, "rmsnorm_router: null pointer");
+  JB_REQUIRE(aligned16(x) && aligned16(w_norm) && aligned16(xn_bf16) && aligned16(w_router),
+             "rmsnorm_router: pointers must be 16-byte aligned");
+  if (n_tokens == 0) return JB200_OK;
+  const int tpc = n_tokens <= 4096 ? ROUTER_THREADS / 32 : ROUTER_TOKENS_PER_CTA;
+  const int blocks = (n_tokens + tpc - 1) / tpc;
+  const size_t smem = size_t(E) * C * sizeof(float);
+  __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(xn_bf16);
+  if (E == 4)
+    rmsnorm_router_kernel<4><<<blocks, ROUTER_THREADS, smem, stream>>>(x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
+                                                                       topk_idx, gates, probs_sum, top1_hist);
+  else
+    rmsnorm_router_kernel<8><<<blocks, ROUTER_THREADS, smem, stream>>>(x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
+                                                                       topk_idx, gates, probs_sum, top1_hist);
+  JB_LAUNCH_CHECK("rmsnorm_router_kernel");
   return JB200_OK;
 }
 

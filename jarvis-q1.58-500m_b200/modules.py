@@ -149,6 +149,7 @@ class AssociativeLinearAttention(nn.Module):
         self.register_buffer("_i_idx_p1", i + 1)
         self.register_buffer("_c_m1_m_i", (cs - 1) - i)
         self._qkv = _PackCache()
+        self._gamma = None
         self.max_position = None   # optional upper bound of per-sequence start positions (avoids a sync)
 
     def qkv_packed(self):
@@ -165,7 +166,10 @@ class AssociativeLinearAttention(nn.Module):
         else:
             end = int(start_pos) + T
         cos, sin = self.rotary.half_tables(end, xn_rows.device)
-        gamma = torch.sigmoid(self.gamma_raw.detach().float())
+        gkey = (self.gamma_raw.data_ptr(), self.gamma_raw._version)
+        if self._gamma is None or self._gamma[0] != gkey:
+            self._gamma = (gkey, torch.sigmoid(self.gamma_raw.detach().float()))
+        gamma = self._gamma[1]
         if h_prev is not None:
             h_prev = h_prev.to(torch.float32).contiguous()
         return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
@@ -217,17 +221,28 @@ class SparseMoELayer(nn.Module):
         return (self._p1.get([m.weight for m in self.w1], stack=True),
                 self._p2.get([m.weight for m in self.w2], stack=True))
 
-    def run_rows(self, xn_rows, out_dtype=torch.bfloat16):
-        """xn_rows: bf16 (N, C) -> (out (N, C), scalars f32 [l_balance, act_mean, act_var])."""
+    def run_rows(self, xn_rows, out_dtype=torch.bfloat16, acc=None, hist=None, scalars=None, norm=None):
+        """xn_rows: bf16 (N, C) -> (out (N, C), scalars f32 [l_balance, act_mean, act_var]).
+        acc (f64 (2+E,)), hist (i32 (E,)) and scalars (f32 (3,)) may be passed in pre-zeroed (a model
+        zeroes one block of them per forward instead of three small fills per layer)."""
         if self.training:
             raise RuntimeError("SparseMoELayer (sm_100a): inference only; call .eval() first")
         N, C = xn_rows.shape
         E = self.num_experts
         dev = xn_rows.device
-        acc = torch.zeros(2 + E, dtype=torch.float64, device=dev)   # [sum, sum^2, P_0..P_{E-1}]
-        hist = torch.zeros(E, dtype=torch.int32, device=dev)
-        idx, gates, _ = ops.router_top2(xn_rows, self.router.weight.detach().float().contiguous(),
-                                        probs_sum=acc[2:], top1_hist=hist)
+        if acc is None:
+            acc = torch.zeros(2 + E, dtype=torch.float64, device=dev)   # [sum, sum^2, P_0..P_{E-1}]
+        if hist is None:
+            hist = torch.zeros(E, dtype=torch.int32, device=dev)
+        # norm=(weight, eps): `xn_rows` is the un-normalised f32 residual stream and RMSNorm is fused into
+        # the router kernel (one pass over the row, routing bit-identical to the separate kernels)
+        w_r = self.router.weight.detach().float().contiguous()
+        if norm is not None and C <= 1024:
+            xn_rows, idx, gates = ops.rmsnorm_router(xn_rows, norm[0], norm[1], w_r, probs_sum=acc[2:], top1_hist=hist)
+        else:
+            if norm is not None:
+                xn_rows = ops.rmsnorm(xn_rows, norm[0], norm[1])
+            idx, gates, _ = ops.router_top2(xn_rows, w_r, probs_sum=acc[2:], top1_hist=hist)
         meta = ops.moe_metadata(idx, E)
         counts, offsets, scatter, gather, gate_idx = meta
         (p1, a1), (p2, a2) = self.packed()
@@ -235,7 +250,7 @@ class SparseMoELayer(nn.Module):
         hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
         y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16, prepared=True)
         out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
-        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, N, N * C, self.balance_alpha)
+        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, N, N * C, self.balance_alpha, scalars=scalars)
         self.last_routing = (idx, gates, meta)
         return out, scalars
 
@@ -334,7 +349,7 @@ class JarvisBlock(nn.Module):
         self.reflect = ReflectivePenalty()
 
     def forward_rows(self, x, B, T, h_prev=None, start_pos=0, attn_state=None, want_attn_state=False,
-                     inplace_state=False):
+                     inplace_state=False, scratch=None):
         """x: f32 (B*T, C) residual stream, UPDATED IN PLACE.  Returns (h_last f32 (B, C), scalars f32
         [l_balance, act_mean, act_var], attention state or None)."""
         C = x.shape[1]
@@ -342,8 +357,11 @@ class JarvisBlock(nn.Module):
         o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state, inplace_state)
         po, ao = self.attn.out_proj.packed()
         ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)          # x += attn(norm1(x))
-        xn = ops.rmsnorm(x, self.norm2.weight.detach().float(), self.norm2.eps)
-        moe_out, scalars = self.moe.run_rows(xn)
+        norm2 = (self.norm2.weight.detach().float(), self.norm2.eps)
+        if scratch is None:
+            moe_out, scalars = self.moe.run_rows(x, norm=norm2)
+        else:
+            moe_out, scalars = self.moe.run_rows(x, acc=scratch[0], hist=scratch[1], scalars=scratch[2], norm=norm2)
         _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],
                                  var_scale=self.liquid.var_scale.detach().float().reshape(1),
                                  alpha_min=self.liquid.alpha_min, alpha_max=self.liquid.alpha_max,
@@ -404,6 +422,15 @@ class Jarvis(nn.Module):
         self._attn_states = [None] * len(self.blocks)
         self._token_pos = 0
 
+    def _layer_scratch(self, device):
+        """Per-forward accumulators of all layers, zeroed with three fills: (sum, sum^2, P) f64,
+        top-1 histogram i32, and the [l_balance, act_mean, act_var] outputs f32."""
+        n, E = len(self.blocks), self.blocks[0].moe.num_experts
+        acc = torch.zeros((n, 2 + E), dtype=torch.float64, device=device)
+        hist = torch.zeros((n, E), dtype=torch.int32, device=device)
+        scal = torch.zeros((n, 3), dtype=torch.float32, device=device)
+        return [(acc[i], hist[i], scal[i]) for i in range(n)]
+
     def _lm_head_weight(self):
         w = self.lm_head.weight
         key = (w.data_ptr(), w._version)
@@ -427,6 +454,7 @@ class Jarvis(nn.Module):
         h_prevs = self._h_states if persist_state else [None] * len(self.blocks)
         s_prevs = self._attn_states if (persist_state and self.carry_attention_state) else [None] * len(self.blocks)
         new_h, new_s, aux = [], [], []
+        scratch = self._layer_scratch(x.device)
         for i, block in enumerate(self.blocks):
             h_prev = h_prevs[i]
             if h_prev is not None and h_prev.shape[0] != B:
@@ -435,7 +463,7 @@ class Jarvis(nn.Module):
             if s_prev is not None and s_prev.shape[0] != B:
                 s_prev = None
             h_last, sc, state = block.forward_rows(x, B, T, h_prev, start_pos, s_prev,
-                                                   want_attn_state=self.carry_attention_state)
+                                                   want_attn_state=self.carry_attention_state, scratch=scratch[i])
             new_h.append(h_last)
             new_s.append(state)
             aux.append(sc)
@@ -460,10 +488,11 @@ class Jarvis(nn.Module):
         hs = state["h"] if state is not None else [None] * n
         Ss = state["S"] if state is not None else [None] * n
         new_h, new_s = [], []
+        scratch = self._layer_scratch(x.device)
         for i, block in enumerate(self.blocks):
             block.attn.max_position = max_position
             h_last, _, S = block.forward_rows(x, B, T, hs[i], pos, Ss[i], want_attn_state=True,
-                                              inplace_state=inplace and state is not None)
+                                              inplace_state=inplace and state is not None, scratch=scratch[i])
             new_h.append(h_last)
             new_s.append(S)
         hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)

@@ -262,6 +262,24 @@ def router_top2(x: torch.Tensor, w_router: torch.Tensor, *, want_probs: bool = F
     return idx, gates, probs
 
 
+def rmsnorm_router(x: torch.Tensor, w_norm: torch.Tensor, eps: float, w_router: torch.Tensor, *, probs_sum=None,
+                   top1_hist=None):
+    """Fused norm2 + router: x f32 (N, C) -> (xn bf16 (N, C), topk_idx int64 (N, 2), gates f32 (N, 2))."""
+    lib = _lib.load()
+    _need(x, torch.float32, "rmsnorm_router.x")
+    _need(w_norm, torch.float32, "rmsnorm_router.w_norm")
+    _need(w_router, torch.float32, "rmsnorm_router.w_router")
+    N, C = x.shape
+    E = w_router.shape[0]
+    xn = torch.empty((N, C), dtype=torch.bfloat16, device=x.device)
+    idx = torch.empty((N, 2), dtype=torch.int64, device=x.device)
+    gates = torch.empty((N, 2), dtype=torch.float32, device=x.device)
+    _lib.check(lib.jb200_rmsnorm_router(_ptr(x), _ptr(w_norm), eps, _ptr(xn), _ptr(w_router), N, C, E, _ptr(idx),
+                                        _ptr(gates), _ptr(probs_sum), _ptr(top1_hist), _stream()),
+               "jb200_rmsnorm_router")
+    return xn, idx, gates
+
+
 def moe_metadata(topk_idx: torch.Tensor, num_experts: int):
     """compute_metadata(topk_idx, E) -> (counts, offsets, scatter_map, gather_map, gate_idx_map), int32."""
     lib = _lib.load()

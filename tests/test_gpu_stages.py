@@ -171,6 +171,22 @@ def test_router_bit_exact_on_tie_free_rows():
     assert torch.allclose(gates.cpu()[clear], gates_ref[clear], atol=1e-5)
 
 
+def test_fused_rmsnorm_router_is_bit_identical_to_the_two_kernels():
+    g = torch.Generator().manual_seed(8)
+    for N, C in ((3000, 1024), (100, 256), (5000, 128)):
+        x = torch.randn(N, C, generator=g).cuda() * 3
+        wn = (torch.rand(C, generator=g) + 0.5).cuda()
+        wr = (torch.randn(4, C, generator=g) * 0.05).cuda()
+        ps1 = torch.zeros(4, dtype=torch.float64, device="cuda")
+        h1 = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ps2, h2 = torch.zeros_like(ps1), torch.zeros_like(h1)
+        xn1 = ops.rmsnorm(x, wn, 1e-6)
+        idx1, gates1, _ = ops.router_top2(xn1, wr, probs_sum=ps1, top1_hist=h1)
+        xn2, idx2, gates2 = ops.rmsnorm_router(x, wn, 1e-6, wr, probs_sum=ps2, top1_hist=h2)
+        assert torch.equal(xn1, xn2) and torch.equal(idx1, idx2) and torch.equal(gates1, gates2)
+        assert torch.equal(h1, h2) and torch.allclose(ps1, ps2, rtol=1e-12)
+
+
 def test_router_ties_go_to_lower_expert():
     x = torch.zeros(64, 256, dtype=torch.bfloat16)
     w = torch.randn(4, 256)
