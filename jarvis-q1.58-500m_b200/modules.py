@@ -215,6 +215,12 @@ class SparseMoELayer(nn.Module):
         self.w2 = nn.ModuleList([TernaryLinear(hidden, d_model) for _ in range(num_experts)])
         self._p1 = _PackCache()
         self._p2 = _PackCache()
+        # When one batch is split over data-parallel ranks, the batch-global quantities of the layer
+        # (act_mean / act_var, which set the LSF decay, and the f / P of the balance loss) need the
+        # other ranks' partial sums: set to a torch.distributed group to all-reduce them (6 doubles and
+        # 4 ints per layer).  None: the ranks' batches are independent calls.
+        self.stats_group = None
+        self._n_total_hint = None   # global token count when known (avoids a host read per layer)
         self.last_routing = None  # (topk_idx, gates, metadata) of the most recent call, for inspection
 
     def packed(self):
@@ -250,7 +256,15 @@ class SparseMoELayer(nn.Module):
         hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
         y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16, prepared=True)
         out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
-        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, N, N * C, self.balance_alpha, scalars=scalars)
+        n_total = N
+        if self.stats_group is not None:
+            import torch.distributed as dist
+            dist.all_reduce(acc, group=self.stats_group)
+            dist.all_reduce(hist, group=self.stats_group)
+            cnt = torch.tensor([N], dtype=torch.int64, device=dev)
+            dist.all_reduce(cnt, group=self.stats_group)
+            n_total = int(cnt.item()) if self._n_total_hint is None else self._n_total_hint
+        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, n_total, n_total * C, self.balance_alpha, scalars=scalars)
         self.last_routing = (idx, gates, meta)
         return out, scalars
 
@@ -516,6 +530,15 @@ class Jarvis(nn.Module):
             l_reflect = sum(b.reflect(sc[1], sc[2]) for b, sc in zip(self.blocks, self.last_aux))
             loss = ce + aux[:, 0].sum() + l_reflect
         return logits, loss
+
+    def set_batch_split(self, group, global_tokens=None):
+        """Treat the ranks of `group` as holding slices of ONE batch: every layer all-reduces its MoE
+        statistics so that the LSF decay and the auxiliary scalars equal those of the unsplit batch
+        (the reference derives one decay per call from the variance of the whole batch,
+        jarvis_model.py:249-250, 297-298).  group=None restores independent per-rank batches."""
+        for blk in self.blocks:
+            blk.moe.stats_group = group
+            blk.moe._n_total_hint = global_tokens
 
     def param_count(self):
         n = sum(p.numel() for p in self.parameters())

@@ -34,3 +34,39 @@ def test_data_parallel_bench_two_gpus():
     assert res.returncode == 0, res.stderr[-2000:]
     line = json.loads(res.stdout.strip().splitlines()[-1])
     assert line["n_gpus"] == 2 and line["scaling"] == "weak" and line["value"] > 0
+
+
+_SPLIT_SCRIPT = """
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.getcwd())
+import jarvis_b200
+from jarvis_b200 import modules as jm
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+torch.manual_seed(0)
+model = jm.ternary_init_(jm.Jarvis(vocab_size=512, d_model=256, n_layers=3, n_heads=4, max_seq_len=256)).cuda().eval()
+idx = torch.randint(0, 512, (4, 192), generator=torch.Generator().manual_seed(1)).cuda()
+full, _ = model(idx)                                   # the whole batch on every rank: the reference result
+model.set_batch_split(dist.group.WORLD, global_tokens=idx.numel())
+per = idx.shape[0] // world
+part, _ = model(idx[rank * per:(rank + 1) * per])      # this rank's slice, statistics all-reduced per layer
+err = float((part.float() - full[rank * per:(rank + 1) * per].float()).norm() / full.float().norm())
+model.set_batch_split(None)
+alone, _ = model(idx[rank * per:(rank + 1) * per])     # independent call: a different decay, a different result
+diff = float((alone.float() - full[rank * per:(rank + 1) * per].float()).norm() / full.float().norm())
+t = torch.tensor([err, diff], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+if rank == 0: print(json.dumps({"err": float(t[0]), "independent_diff": float(t[1])}))
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_batch_split_over_two_gpus_reproduces_the_unsplit_batch(tmp_path):
+    script = tmp_path / "split.py"
+    script.write_text(_SPLIT_SCRIPT)
+    res = _torchrun(2, [str(script)])
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["err"] < 2e-3            # same kernels; only the summation order of the statistics differs
+    assert line["independent_diff"] > line["err"]
