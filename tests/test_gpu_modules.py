@@ -159,6 +159,31 @@ def test_lsf_ext_module_persistence():
     assert torch.allclose(ext(a, m), H, atol=0)
 
 
+def test_packed_checkpoint_round_trip():
+    """Export in the reference exporter's key format, load into a fresh model: same logits bit for bit,
+    and the packed bytes equal the oracle's packing of the oracle's quantisation."""
+    from jarvis_b200 import checkpoint as ck
+    torch.manual_seed(11)
+    a = jm.ternary_init_(jm.Jarvis(vocab_size=256, d_model=128, n_layers=2, n_heads=2, max_seq_len=128)).cuda().eval()
+    sd = {("_orig_mod." + k if i % 2 else k): v for i, (k, v) in enumerate(a.state_dict().items())}
+    packed, meta = ck.export_packed_state_dict(sd)
+    assert "blocks.0.attn.q_proj.weight.packed_weight" in packed and "blocks.1.moe.w2.3.weight.alpha" in packed
+    assert packed["tok_emb.weight"].dtype == torch.bfloat16 and len(meta) == 2 * 12
+    w = a.state_dict()["blocks.0.moe.w1.2.weight"].cpu()
+    alpha, q = orc.absmean_quantize(w)
+    assert abs(float(packed["blocks.0.moe.w1.2.weight.alpha"]) - alpha) <= 1e-6 * alpha
+    assert (packed["blocks.0.moe.w1.2.weight.packed_weight"] != orc.pack_ternary(q)).sum() <= 2
+    b = jm.Jarvis(vocab_size=256, d_model=128, n_layers=2, n_heads=2, max_seq_len=128).cuda().eval()
+    ck.load_packed_state_dict(b, packed)
+    # the non-ternary tensors went through bf16: give model a the same rounding before comparing
+    with torch.no_grad():
+        for k, v in a.state_dict().items():
+            if not ck.is_ternary_key(k, v) and v.is_floating_point():
+                v.copy_(v.to(torch.bfloat16).float())
+    idx = torch.randint(0, 256, (2, 64), device="cuda")
+    assert torch.equal(a(idx)[0], b(idx)[0])
+
+
 def test_cpu_tensors_are_rejected():
     lin = jm.TernaryLinear(64, 128)
     with pytest.raises(RuntimeError, match="no CPU fallback|CUDA"):
