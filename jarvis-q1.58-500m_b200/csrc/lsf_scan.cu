@@ -124,6 +124,17 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
       mv[i] = ok ? ld2<TM>(m + seq_base + size_t(t0 + i) * p.D) : make_float2(0.f, 0.f);
       if (TENSOR_ALPHA) av[i] = ok ? ld2<TM>(at + seq_base + size_t(t0 + i) * p.D) : make_float2(1.f, 1.f);
     }
+    // the residual values do not depend on the scan: their loads go out together with those of m, so
+    // both streams are in flight at once and the read-modify-write never serialises
+    float2 rold[(!ENDS_ONLY) ? TPW : 1];
+    if (!ENDS_ONLY && p.resid) {
+#pragma unroll
+      for (int i = 0; i < TPW; ++i) {
+        const int t = t0 + i;
+        rold[i] = (ch_ok && t < p.T) ? *reinterpret_cast<const float2*>(p.resid + seq_base + size_t(t) * p.D)
+                                     : make_float2(0.f, 0.f);
+      }
+    }
     float2 h = make_float2(0.f, 0.f), pr = make_float2(1.f, 1.f);
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {
@@ -163,16 +174,6 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
     carry = c;
     c = cn;
     if (ENDS_ONLY) continue;
-    // residual values are loaded up front so that the read-modify-write does not serialise
-    float2 rold[TPW];
-    if (p.resid) {
-#pragma unroll
-      for (int i = 0; i < TPW; ++i) {
-        const int t = t0 + i;
-        rold[i] = (ch_ok && t < p.T) ? *reinterpret_cast<const float2*>(p.resid + seq_base + size_t(t) * p.D)
-                                     : make_float2(0.f, 0.f);
-      }
-    }
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {
       const int t = t0 + i;
