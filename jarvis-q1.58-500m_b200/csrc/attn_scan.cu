@@ -35,7 +35,7 @@ namespace {
 
 constexpr int D = 64;             // head dim (fixed by the path: 16 heads x 64)
 constexpr int CH = 64;            // chunk length, AssociativeLinearAttention.CHUNK_SIZE
-constexpr int STAGES = 2;             // 73 KiB of shared memory per CTA -> three CTAs per SM
+constexpr int STAGES = 1;             // 49 KiB of shared memory and 128 registers per CTA -> four CTAs per SM, which cover each other's load latency
 constexpr int TILE_BYTES = CH * D * 2;          // 8 KiB
 constexpr int STAGE_BYTES = 3 * TILE_BYTES;     // q, k, v
 constexpr int ATTN_THREADS = 128;
@@ -95,7 +95,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(fminf(x, 0.f)); }
 
 template <bool STATE_ONLY>
-__global__ void __launch_bounds__(ATTN_THREADS, 3)
+__global__ void __launch_bounds__(ATTN_THREADS, 4)
 attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -472,7 +472,7 @@ int make_map(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
 // Segments: enough CTAs to fill three per SM, each segment at least four chunks long.
 static void pick_segments(int B, int T, int H, int sms, int* seg_chunks, int* nseg) {
   const int n_chunks = (T + CH - 1) / CH;
-  long want = (long(sms) * 3) / (long(B) * H);
+  long want = (long(sms) * 4) / (long(B) * H);
   if (want < 1) want = 1;
   if (want > n_chunks / 4) want = n_chunks / 4 > 0 ? n_chunks / 4 : 1;
   int sc = int((n_chunks + want - 1) / want);
