@@ -349,11 +349,19 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16) {
           const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;
           __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
+          // lane pairs (features f, f+1) swap one value per token pair, so each lane writes a bf16x2 word:
+          // 16 four-byte staging stores per chunk instead of 32 two-byte ones (shared-memory bandwidth is
+          // what the tensor core's operand reads, the decoders and this epilogue compete for)
+          const bool odd = lane & 1;
+          uint32_t* stw = reinterpret_cast<uint32_t*>(st);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float a = alpha * __uint_as_float(v[j]);
-            if (gelu) a = gelu_erf(a);
-            st[j * 32 + lane] = __float2bfloat16_rn(a);
+          for (int jj = 0; jj < 16; ++jj) {
+            float a = alpha * __uint_as_float(v[2 * jj]);
+            float b = alpha * __uint_as_float(v[2 * jj + 1]);
+            if (gelu) { a = gelu_erf(a); b = gelu_erf(b); }
+            const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+            const uint32_t w2 = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
+            stw[(2 * jj + (odd ? 1 : 0)) * 16 + (lane >> 1)] = w2;   // [token][feature pair]
           }
           __syncwarp();
           __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out);
