@@ -348,3 +348,63 @@ def test_lsf_linearity_large():
     sy, _ = ops.lsf_scan(y, alpha_scalar=al)
     sxy, _ = ops.lsf_scan(2.0 * x + y, alpha_scalar=al)
     assert rel_l2(sxy, 2.0 * sx + sy) < 1e-5
+
+
+# ------------------------------------------------------------------ full-size properties (BASELINE shapes)
+def test_gemm_linearity_at_prefill_size():
+    """16384 x 3072 x 1024 (the q/k/v projection of the B=8 x T=2048 prefill): W(x1 + x2) == W x1 + W x2 up
+    to the bf16 rounding of the outputs, and rows are independent of the batch they sit in."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    M, K, N = 16384, 1024, 3072
+    x1 = torch.randint(-8, 9, (M, K), generator=g, device="cuda").float()
+    x2 = torch.randint(-8, 9, (M, K), generator=g, device="cuda").float()
+    q = torch.randint(-1, 2, (N, K), generator=g, device="cuda").float()
+    packed = ops.prepare_weights(ops.pack_codes(q))
+    one = torch.ones(1, device="cuda")
+    f = lambda x: ops.ternary_linear(x.bfloat16(), packed, one, epilogue=ops.EPI_F32, prepared=True)  # noqa: E731
+    y1, y2, y12 = f(x1), f(x2), f(x1 + x2)
+    assert torch.equal(y12, y1 + y2)                     # integers: exact
+    sub = f(x1[5000:5300].contiguous())
+    assert torch.equal(sub, y1[5000:5300])
+    # checksum against fp64 on a slice
+    ref = (x1[:64].double() @ q.double().t()).float()
+    assert torch.equal(y1[:64], ref)
+
+
+def test_attn_scan_split_equals_one_shot_at_prefill_size():
+    g = torch.Generator(device="cuda").manual_seed(1)
+    B, H, T = 8, 16, 2048
+    qkv = torch.randn(B, T, 3 * H * 64, generator=g, device="cuda").bfloat16()
+    gamma = torch.rand(H, generator=g, device="cuda") * 0.099 + 0.9
+    cos, sin = rope_tabs(T)
+    C = H * 64
+
+    def run(x, t, **kw):
+        flat = x.reshape(B * t, 3 * C)
+        return ops.attn_scan(flat[:, :C], flat[:, C:2 * C], flat[:, 2 * C:], gamma, cos, sin, B, t, H,
+                             want_state=True, **kw)
+
+    o_full, S_full = run(qkv, T)
+    o_a, S_a = run(qkv[:, :1024].contiguous(), 1024)
+    o_b, S_b = run(qkv[:, 1024:].contiguous(), 1024, start_pos=1024, state_in=S_a)
+    o_split = torch.cat((o_a.view(B, 1024, C), o_b.view(B, 1024, C)), dim=1).reshape(B * T, C)
+    assert rel_l2(o_split.float(), o_full.float()) < 3e-3
+    assert rel_l2(S_b, S_full) < 1e-5
+    assert _lib.device_status() == 0
+
+
+def test_dispatch_round_trip_at_moe_bench_size():
+    """65,536 tokens (the MoE-alone configuration): gather then combine with unit gates on one slot
+    returns the input; the maps are a permutation."""
+    g = torch.Generator(device="cuda").manual_seed(2)
+    N, C, E = 65536, 1024, 4
+    x = torch.randn(N, C, generator=g, device="cuda").bfloat16()
+    idx = torch.stack((torch.randint(0, 2, (N,), generator=g, device="cuda"),
+                       torch.randint(2, 4, (N,), generator=g, device="cuda")), dim=1)
+    counts, offsets, scatter, gather, gate_idx = ops.moe_metadata(idx, E)
+    assert int(offsets[-1]) == 2 * N and torch.equal(torch.sort(scatter.reshape(-1)).values.long(),
+                                                     torch.arange(2 * N, device="cuda"))
+    disp = ops.dispatch_gather(x, gather)
+    gates = torch.tensor([[1.0, 0.0]], device="cuda").repeat(N, 1)
+    back = ops.scatter_combine(disp, gates, scatter)
+    assert torch.equal(back, x)
