@@ -99,3 +99,85 @@ def load_packed_state_dict(model: torch.nn.Module, packed_sd: dict) -> torch.nn.
             _install(mod._p1, [m.weight for m in mod.w1], [t[0] for t in e1], [t[1] for t in e1], stack=True)
             _install(mod._p2, [m.weight for m in mod.w2], [t[0] for t in e2], [t[1] for t in e2], stack=True)
     return model
+
+
+# ---------------------------------------------------------------------------------------------------
+# .jarvis-tbin container (experiments/architecture_matrix/ternary_packed/jarvis_tbin_format.py:9-29):
+#   [0..7] magic b"JTBIN01\0", [8..11] version (u32 = 1), [12..15] JSON length (u32), JSON manifest, payload.
+#   Manifest entries: name, is_ternary, orig_shape, packed_shape, alpha, dtype ("uint8_packed" | "bfloat16"),
+#   offset, length (relative to the payload start).  Ternary tensors are the weight_packing.py bytes.
+# ---------------------------------------------------------------------------------------------------
+TBIN_MAGIC = b"JTBIN01\x00"
+TBIN_VERSION = 1
+TBIN_TERNARY_TAGS = ("q_proj", "k_proj", "v_proj", "out_proj", "w1", "w2")
+
+
+def read_tbin(path: str):
+    """-> (packed state dict in the `<key>.packed_weight` / `<key>.alpha` form, manifest dict).
+    Feed the first to load_packed_state_dict."""
+    import json
+    import struct
+
+    with open(path, "rb") as fh:
+        magic = fh.read(8)
+        if magic != TBIN_MAGIC:
+            raise ValueError(f"read_tbin: invalid magic header {magic!r}")
+        version, meta_len = struct.unpack("<II", fh.read(8))
+        if version != TBIN_VERSION:
+            raise ValueError(f"read_tbin: unsupported version {version}")
+        meta = json.loads(fh.read(meta_len).decode("utf-8"))
+        payload = fh.read()
+    out = {}
+    for e in meta["tensors"]:
+        raw = payload[e["offset"]: e["offset"] + e["length"]]
+        if len(raw) != e["length"]:
+            raise ValueError(f"read_tbin: truncated payload for {e['name']}")
+        if e["is_ternary"]:
+            if e["dtype"] != "uint8_packed":
+                raise ValueError(f"read_tbin: ternary tensor {e['name']} has dtype {e['dtype']}")
+            out[e["name"] + ".packed_weight"] = torch.frombuffer(bytearray(raw), dtype=torch.uint8).reshape(e["packed_shape"])
+            out[e["name"] + ".alpha"] = torch.tensor(e["alpha"], dtype=torch.float32)
+        else:
+            if e["dtype"] != "bfloat16":
+                raise ValueError(f"read_tbin: dense tensor {e['name']} has dtype {e['dtype']}")
+            out[e["name"]] = torch.frombuffer(bytearray(raw), dtype=torch.int16).view(torch.bfloat16).reshape(e["orig_shape"])
+    return out, meta
+
+
+def write_tbin(state_dict: dict, path: str, extra_metadata: dict | None = None, device="cuda"):
+    """Writes a model state dict as a .jarvis-tbin container (quantising + packing on the GPU)."""
+    import json
+    import struct
+    import time
+
+    manifest, buffers, offset = [], [], 0
+    n_tern = n_dense = 0
+    for name, t in state_dict.items():
+        if t.dim() == 2 and any(tag in name for tag in TBIN_TERNARY_TAGS):
+            p, alpha = ops.pack_ternary(t.detach().to(device=device, dtype=torch.float32).contiguous())
+            raw = p.cpu().numpy().tobytes()
+            entry = {"name": name, "is_ternary": True, "orig_shape": list(t.shape), "packed_shape": list(p.shape),
+                     "alpha": float(alpha), "dtype": "uint8_packed"}
+            n_tern += t.numel()
+        else:
+            raw = t.detach().cpu().to(torch.bfloat16).view(torch.int16).numpy().tobytes()
+            entry = {"name": name, "is_ternary": False, "orig_shape": list(t.shape), "packed_shape": list(t.shape),
+                     "alpha": 1.0, "dtype": "bfloat16"}
+            n_dense += t.numel()
+        entry.update(offset=offset, length=len(raw))
+        manifest.append(entry)
+        buffers.append(raw)
+        offset += len(raw)
+    meta = {"version": TBIN_VERSION, "format": "jarvis-tbin",
+            "created_at": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()),
+            "total_parameters": n_tern + n_dense, "ternary_parameters": n_tern, "dense_parameters": n_dense,
+            "ternary_fraction_pct": 100.0 * n_tern / max(n_tern + n_dense, 1), "tensors": manifest,
+            "extra": extra_metadata or {}}
+    blob = json.dumps(meta).encode("utf-8")
+    with open(path, "wb") as fh:
+        fh.write(TBIN_MAGIC)
+        fh.write(struct.pack("<II", TBIN_VERSION, len(blob)))
+        fh.write(blob)
+        for raw in buffers:
+            fh.write(raw)
+    return meta

@@ -234,9 +234,30 @@ def golden_block_model():
     save("model", **out)
 
 
+# ---- 6. the .jarvis-tbin container, written and re-read by the reference's own code ---------------
+def golden_tbin():
+    sys.path.insert(0, os.path.join(REF, "experiments", "architecture_matrix", "ternary_packed"))
+    import jarvis_tbin_format as tb
+    gen = torch.Generator().manual_seed(77)
+    model = jm.Jarvis(vocab_size=64, d_model=128, n_layers=1, n_heads=2, max_seq_len=64,
+                      use_cuda_attn=False, use_cuda_moe=False).eval()
+    ternary_init(model, gen)
+    path = os.path.join(OUT, "tiny.jarvis-tbin")
+    tb.export_to_jarvis_tbin(model, path, {"note": "golden"})
+    twin = jm.Jarvis(vocab_size=64, d_model=128, n_layers=1, n_heads=2, max_seq_len=64,
+                     use_cuda_attn=False, use_cuda_moe=False).eval()
+    tb.load_from_jarvis_tbin(twin, path, device="cpu")
+    sd = twin.state_dict()                      # effective weights alpha * q, dense tensors through bf16
+    idx = torch.randint(0, 64, (2, 40), generator=gen)
+    save("tbin", idx=idx, logits=twin(idx)[0],
+         **{"sd_" + k: sd[k] for k in ("blocks.0.attn.q_proj.weight", "blocks.0.moe.w2.3.weight", "tok_emb.weight",
+                                       "blocks.0.moe.router.weight", "blocks.0.attn.gamma_raw")})
+
+
 if __name__ == "__main__":
     golden_pack()
     golden_attention()
     golden_moe()
     golden_lsf()
     golden_block_model()
+    golden_tbin()   # last: building its models draws from the global RNG that later fixtures would see

@@ -103,3 +103,30 @@ def test_install_keeps_reference_state_dict_keys():
         assert torch.equal(v, weights[k]), k
     assert isinstance(model.blocks[0].attn, jm.AssociativeLinearAttention)
     assert isinstance(model.blocks[1].moe, jm.SparseMoELayer)
+
+
+def test_read_tbin_container_written_by_the_reference():
+    """tests/golden/tiny.jarvis-tbin was produced by the reference's export_to_jarvis_tbin; the reader must
+    recover exactly what the reference's own loader reconstructs (effective weights alpha * q, dense tensors
+    through bf16)."""
+    from jarvis_b200 import checkpoint as ck
+    from tests.golden.loader import load
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny.jarvis-tbin")
+    packed, meta = ck.read_tbin(path)
+    g = load("tbin")
+    assert meta["format"] == "jarvis-tbin" and meta["extra"] == {"note": "golden"}
+    assert len(meta["tensors"]) == 26 and sum(e["is_ternary"] for e in meta["tensors"]) == 12
+    for name in ("blocks.0.attn.q_proj.weight", "blocks.0.moe.w2.3.weight"):
+        p, a = packed[name + ".packed_weight"], packed[name + ".alpha"]
+        w_eff = orc.unpack_ternary(p, g["sd_" + name].shape) * a
+        assert torch.equal(w_eff, g["sd_" + name]), name
+    for name in ("tok_emb.weight", "blocks.0.moe.router.weight", "blocks.0.attn.gamma_raw"):
+        assert torch.equal(packed[name].float(), g["sd_" + name]), name
+    with pytest.raises(ValueError, match="magic"):
+        bad = path + ".bad"
+        try:
+            with open(bad, "wb") as fh:
+                fh.write(b"NOTATBIN" + b"\0" * 64)
+            ck.read_tbin(bad)
+        finally:
+            os.remove(bad)

@@ -184,6 +184,27 @@ def test_packed_checkpoint_round_trip():
     assert torch.equal(a(idx)[0], b(idx)[0])
 
 
+def test_tbin_container_runs_and_round_trips(tmp_path):
+    import os
+    from jarvis_b200 import checkpoint as ck
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "tiny.jarvis-tbin")
+    g = load("tbin")
+    packed, _ = ck.read_tbin(path)
+    model = jm.Jarvis(vocab_size=64, d_model=128, n_layers=1, n_heads=2, max_seq_len=64).cuda().eval()
+    ck.load_packed_state_dict(model, packed)
+    logits, _ = model(g["idx"].cuda())
+    assert rel_l2(logits.float(), g["logits"]) <= 1.5e-2          # the reference ran the same container on CPU
+    out = tmp_path / "again.jarvis-tbin"
+    ck.write_tbin(model.state_dict(), str(out))
+    again, meta = ck.read_tbin(str(out))
+    assert set(again) == set(packed) and len(meta["tensors"]) == 26
+    for k in packed:
+        if k.endswith(".packed_weight"):
+            assert torch.equal(again[k], packed[k]), k          # alpha * q re-quantises to the same codes
+        elif not k.endswith(".alpha"):
+            assert torch.equal(again[k], packed[k]), k
+
+
 def test_cpu_tensors_are_rejected():
     lin = jm.TernaryLinear(64, 128)
     with pytest.raises(RuntimeError, match="no CPU fallback|CUDA"):
