@@ -254,7 +254,7 @@ int launch_t(const LsfParams& p, cudaStream_t stream) {
 // Segments so that about two CTAs per SM exist, each at least four tiles long.
 void pick_lsf_segments(int B, int T, int D, int sms, int* seg_len, int* nseg) {
   const long ctas = long((D + LSF_CH - 1) / LSF_CH) * B;
-  long want = (2L * sms + ctas - 1) / ctas;
+  long want = (2L * sms) / ctas;   // rounded down: all CTAs resident at once, no partial second wave
   const long max_seg = T / (4 * LSF_TILE);
   if (want > max_seg) want = max_seg;
   if (want < 1) want = 1;

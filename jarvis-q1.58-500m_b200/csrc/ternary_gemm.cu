@@ -486,11 +486,8 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
-    attr_set = true;
-  }
+  // per device and cheap: set on every call rather than remembering which devices have seen it
+  JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
   const long max_tiles = long((M + bn - 1) / bn + (G - 1)) * n_ft;
   const int grid = int(max_tiles < sms ? max_tiles : sms);
   ternary_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap, p);
