@@ -35,6 +35,7 @@ extern "C" {
 #define JB200_EPI_GELU_BF16 1 /* out bf16 [M][N]  = gelu_erf(alpha * acc)             */
 #define JB200_EPI_RESID_F32 2 /* out f32  [M][N] += alpha * acc   (residual stream)   */
 #define JB200_EPI_F32 3       /* out f32  [M][N]  = alpha * acc                       */
+#define JB200_TILE_CTA_PAIR 0x1000 /* flag added to token_tile: run on CTA pairs (tcgen05 cta_group::2) */
 
 /* device status codes (0 = no bounded wait ever ran out) */
 #define JB200_STATUS_GEMM_PRODUCER 0x11u
@@ -98,7 +99,10 @@ int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, v
  * x: bf16 [M][K].  packed: u8 [N][K/4].  alpha: f32 [N / alpha_rows] (alpha_rows = N for the
  * per-tensor scale; several matrices stacked along N, e.g. q/k/v, each keep their own).
  * N % 128 == 0, K % 64 == 0, alpha_rows % 128 == 0.  out: per `epilogue`.
- * token_tile: 0 = choose, else one of 32/64/128/256.
+ * token_tile: 0 = choose, else one of 32/64/128/256.  Adding JB200_TILE_CTA_PAIR selects the variant that runs a
+ * 256 out-feature x token_tile tile on a pair of SMs (tcgen05 cta_group::2; needs N % 256 == 0 and a tile of
+ * 0, 128 or 256).  Results are identical; on the shapes of this model the one-CTA kernel is the faster one,
+ * so it is the default.
  * w_layout: 0 = `packed` is the canonical weight_packing.py layout; 1 = `packed` was re-encoded by
  * jb200_prepare_weights (same size, about 4x fewer decode instructions in the kernel). */
 int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,

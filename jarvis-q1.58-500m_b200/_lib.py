@@ -16,6 +16,7 @@ _HEADER = os.path.join(os.path.dirname(_build.PKG_DIR), "include", "jarvis_b200.
 
 OK, ERR_ARG, ERR_CUDA = 0, -1, 1
 EPI_BF16, EPI_GELU_BF16, EPI_RESID_F32, EPI_F32 = 0, 1, 2, 3
+TILE_CTA_PAIR = 0x1000  # JB200_TILE_CTA_PAIR: added to token_tile, runs the GEMM on CTA pairs (cta_group::2)
 
 _P = C.c_void_p
 _I = C.c_int

@@ -1,0 +1,156 @@
+// Device helpers shared by the one-CTA and the CTA-pair ternary GEMM kernels: the 2-bit decoders for
+// both weight layouts, the one-time re-encoding, and the GELU of the expert hidden layer.
+#pragma once
+#include "common.cuh"
+
+namespace jb {
+
+// 16 two-bit codes (one 32-bit word) -> 16 bf16 values (8 words), codes 0/1/2/3 -> 0/+1/-1/0.
+// The codes are first spread to one per nibble; the nibbles then act as PRMT selectors
+// into 4-byte tables of the high (00 3F BF 00) and low (00 80 80 00) bf16 bytes.
+__host__ __device__ __forceinline__ uint32_t byte_perm_sw(uint32_t x, uint32_t y, uint32_t s) {
+#if defined(__CUDA_ARCH__)
+  return __byte_perm(x, y, s);
+#else
+  uint64_t pool = (uint64_t(y) << 32) | x;
+  uint32_t r = 0;
+  for (int i = 0; i < 4; ++i) r |= uint32_t((pool >> (8 * ((s >> (4 * i)) & 7))) & 0xFF) << (8 * i);
+  return r;
+#endif
+}
+
+__host__ __device__ __forceinline__ void decode16(uint32_t w, uint32_t* out) {
+  constexpr uint32_t POOL_HI = 0x00BF3F00u;
+  constexpr uint32_t POOL_LO = 0x00808000u;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    uint32_t x = (w >> (16 * half)) & 0xFFFFu;
+    x = (x | (x << 8)) & 0x00FF00FFu;
+    x = (x | (x << 4)) & 0x0F0F0F0Fu;
+    x = (x | (x << 2)) & 0x33333333u;  // code j of this half sits in nibble j
+    const uint32_t h03 = byte_perm_sw(POOL_HI, 0u, x);
+    const uint32_t l03 = byte_perm_sw(POOL_LO, 0u, x);
+    const uint32_t h47 = byte_perm_sw(POOL_HI, 0u, x >> 16);
+    const uint32_t l47 = byte_perm_sw(POOL_LO, 0u, x >> 16);
+    out[half * 4 + 0] = byte_perm_sw(l03, h03, 0x5140u);
+    out[half * 4 + 1] = byte_perm_sw(l03, h03, 0x7362u);
+    out[half * 4 + 2] = byte_perm_sw(l47, h47, 0x5140u);
+    out[half * 4 + 3] = byte_perm_sw(l47, h47, 0x7362u);
+  }
+}
+
+// Prepared layout: canonical word -> prepared word (host + device; the one-time re-encoding).
+__host__ __device__ __forceinline__ uint32_t prepare_word(uint32_t w) {
+  uint32_t out = 0;
+  for (int k = 0; k < 16; ++k) {
+    const uint32_t c = (w >> (2 * k)) & 3u;
+    const uint32_t f = c == 1u ? 1u : (c == 2u ? 3u : 0u);          // (sign << 1) | nonzero
+    out |= f << ((k & 1) * 16 + (k >> 1) * 2);
+  }
+  return out;
+}
+// Prepared word -> 8 bf16 pairs holding 2 * {-1, 0, +1}.
+__host__ __device__ __forceinline__ void decode16_prepared(uint32_t w, uint32_t* out) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) out[j] = (w << (14 - 2 * j)) & 0xC000C000u;
+}
+
+// GELU for the expert hidden layer.  The reference uses the exact-erf form (F.gelu default,
+// jarvis_model.py:236); here 0.5 x (1 + tanh(x (a + b x^2 + c x^4))) with a, b, c fitted to the erf
+// form: |difference| < 2.6e-5 everywhere (plus tanh.approx's 2^-11 relative error), an order of
+// magnitude below the bf16 rounding of the stored result, at 9 instructions instead of ~25 for erff
+// in an epilogue that is issue-bound.
+__device__ __forceinline__ float gelu_erf(float v) {
+  const float xc = fminf(fmaxf(v, -8.0f), 8.0f);     // keeps the fitted polynomial in its monotone range
+  const float x2 = xc * xc;
+  float pz = fmaf(-0.0003515195915898722f, x2, 0.03700566448133039f);
+  pz = fmaf(pz, x2, 0.797507862407347f);
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(pz * xc));
+  const float hv = 0.5f * v;
+  return fmaf(hv, t, hv);
+}
+
+
+constexpr int MAX_GROUPS = 16;
+
+struct GemmParams {
+  const uint8_t* w_packed;   // [G][N][K/4]
+  const float* alpha;        // [G][N / alpha_rows]
+  const int32_t* seg_offsets;  // device [G+1] or nullptr (single segment [0, M))
+  void* out;                 // bf16 [M][N] or f32 [M][N]
+  int M, N, K, G;
+  int alpha_rows;            // out-feature rows sharing one alpha (N for per-tensor)
+  int bn;                    // token tile
+  int epilogue;
+  int w_layout;              // 0 canonical weight_packing.py layout, 1 prepared layout
+  unsigned int* status;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+
+// One [32 out-features (TMEM lanes)] x [32 tokens (columns)] accumulator chunk -> alpha / GELU / residual ->
+// global memory, straight from registers.  Lane = out-feature and register = token, so one store
+// instruction of a warp covers 32 consecutive features of a token row: 128 contiguous bytes for f32
+// outputs; for bf16 outputs lane pairs first swap one value per token pair, so that every lane stores a
+// bf16x2 word and an instruction covers two 64-byte row segments.  Nothing is staged in shared memory,
+// whose bandwidth the tensor core's operand reads, the TMA writes and the decoders already use up.
+// Called by a whole epilogue warp.
+__device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t taddr, float alpha, size_t row0, int f0,
+                                                int ntok, int lane) {
+  uint32_t v[32];
+  if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16) {
+    const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    const int odd = lane & 1;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + size_t(odd)) * p.N + f0 + (lane & ~1);
+    const size_t step = size_t(p.N) * 2;   // two token rows
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      float a = alpha * __uint_as_float(v[2 * jj]);
+      float b = alpha * __uint_as_float(v[2 * jj + 1]);
+      if (gelu) { a = gelu_erf(a); b = gelu_erf(b); }
+      const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+      const uint32_t w2 = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);   // features (f & ~1, f | 1)
+      if (2 * jj + odd < ntok) *reinterpret_cast<uint32_t*>(o) = w2;       // token 2jj (even lanes) / 2jj+1 (odd)
+      o += step;
+    }
+  } else {
+    float* o = reinterpret_cast<float*>(p.out) + row0 * p.N + f0 + lane;
+    if (p.epilogue == JB200_EPI_RESID_F32) {
+      // start the loads of the old values before waiting for the accumulator
+      float old[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) old[j] = j < ntok ? __ldcs(o + size_t(j) * p.N) : 0.f;
+      tmem_ld_32x32(taddr, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ntok) o[size_t(j) * p.N] = __fadd_rn(__fmul_rn(alpha, __uint_as_float(v[j])), old[j]);
+    } else {
+      tmem_ld_32x32(taddr, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ntok) o[size_t(j) * p.N] = alpha * __uint_as_float(v[j]);
+    }
+  }
+}
+
+}  // namespace jb

@@ -21,7 +21,8 @@
 //   warps 2-9    weight decoders, two groups of four taking alternate K-blocks (one warp's own
 //                instruction latency per K-block exceeds the 512 cycles its MMAs take); thread r of a
 //                group owns weight row r of the tile
-//   warps 10-17  epilogue (two warps per TMEM lane quadrant, alternate 32-token chunks): TMEM -> registers -> alpha / GELU -> smem transpose -> 16-byte row stores / residual add
+//   warps 10-17  epilogue (two warps per TMEM lane quadrant, alternate 32-token chunks): TMEM -> registers ->
+//                alpha / GELU / residual add -> row-segment stores straight from registers
 // Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Token rows may be split into segments (one per expert), each
 // with its own weight matrix and alpha: the grouped form used by the MoE experts.
@@ -36,6 +37,7 @@
 // The decoders share the SM's issue slots with the epilogue, and the kernel is issue-bound, so the
 // instruction count of the decode is what sets the tensor-pipe utilisation.
 #include "common.cuh"
+#include "gemm_shared.cuh"
 
 namespace jb {
 
@@ -47,23 +49,9 @@ constexpr int STAGES = 4;
 constexpr int BN_MAX = 256;     // token columns per tile (UMMA N), runtime 32..256
 constexpr int A_STAGE_BYTES = BM * BK * 2;       // 16 KiB
 constexpr int B_STAGE_BYTES = BN_MAX * BK * 2;   // 32 KiB
-constexpr int MAX_GROUPS = 16;
 constexpr int NUM_THREADS = 576;
 constexpr int DEC_WARP0 = 2, EPI_WARP0 = 10;
 constexpr int TMEM_COLS = 512;
-
-struct GemmParams {
-  const uint8_t* w_packed;   // [G][N][K/4]
-  const float* alpha;        // [G][N / alpha_rows]
-  const int32_t* seg_offsets;  // device [G+1] or nullptr (single segment [0, M))
-  void* out;                 // bf16 [M][N] or f32 [M][N]
-  int M, N, K, G;
-  int alpha_rows;            // out-feature rows sharing one alpha (N for per-tensor)
-  int bn;                    // token tile
-  int epilogue;
-  int w_layout;              // 0 canonical weight_packing.py layout, 1 prepared layout
-  unsigned int* status;
-};
 
 struct SmemCtl {
   uint64_t full[STAGES];
@@ -75,9 +63,8 @@ struct SmemCtl {
   int32_t seg[MAX_GROUPS + 1];
 };
 
-constexpr int STAGE_OUT_BYTES = 32 * 32 * 4;     // one epilogue warp's [32 tokens][32 features] f32 block
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + size_t(STAGES) * (A_STAGE_BYTES + B_STAGE_BYTES) +
-                              ((sizeof(SmemCtl) + 127) / 128) * 128 + 8 * STAGE_OUT_BYTES;
+                              ((sizeof(SmemCtl) + 127) / 128) * 128;
 
 struct TileCoord {
   int group;     // segment / expert
@@ -103,72 +90,6 @@ __device__ __forceinline__ bool tile_coord(const SmemCtl* ctl, int t, int n_ft, 
     tt -= tiles;
   }
   return false;
-}
-
-// 16 two-bit codes (one 32-bit word) -> 16 bf16 values (8 words), codes 0/1/2/3 -> 0/+1/-1/0.
-// The codes are first spread to one per nibble; the nibbles then act as PRMT selectors
-// into 4-byte tables of the high (00 3F BF 00) and low (00 80 80 00) bf16 bytes.
-__host__ __device__ __forceinline__ uint32_t byte_perm_sw(uint32_t x, uint32_t y, uint32_t s) {
-#if defined(__CUDA_ARCH__)
-  return __byte_perm(x, y, s);
-#else
-  uint64_t pool = (uint64_t(y) << 32) | x;
-  uint32_t r = 0;
-  for (int i = 0; i < 4; ++i) r |= uint32_t((pool >> (8 * ((s >> (4 * i)) & 7))) & 0xFF) << (8 * i);
-  return r;
-#endif
-}
-
-__host__ __device__ __forceinline__ void decode16(uint32_t w, uint32_t* out) {
-  constexpr uint32_t POOL_HI = 0x00BF3F00u;
-  constexpr uint32_t POOL_LO = 0x00808000u;
-#pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    uint32_t x = (w >> (16 * half)) & 0xFFFFu;
-    x = (x | (x << 8)) & 0x00FF00FFu;
-    x = (x | (x << 4)) & 0x0F0F0F0Fu;
-    x = (x | (x << 2)) & 0x33333333u;  // code j of this half sits in nibble j
-    const uint32_t h03 = byte_perm_sw(POOL_HI, 0u, x);
-    const uint32_t l03 = byte_perm_sw(POOL_LO, 0u, x);
-    const uint32_t h47 = byte_perm_sw(POOL_HI, 0u, x >> 16);
-    const uint32_t l47 = byte_perm_sw(POOL_LO, 0u, x >> 16);
-    out[half * 4 + 0] = byte_perm_sw(l03, h03, 0x5140u);
-    out[half * 4 + 1] = byte_perm_sw(l03, h03, 0x7362u);
-    out[half * 4 + 2] = byte_perm_sw(l47, h47, 0x5140u);
-    out[half * 4 + 3] = byte_perm_sw(l47, h47, 0x7362u);
-  }
-}
-
-// Prepared layout: canonical word -> prepared word (host + device; the one-time re-encoding).
-__host__ __device__ __forceinline__ uint32_t prepare_word(uint32_t w) {
-  uint32_t out = 0;
-  for (int k = 0; k < 16; ++k) {
-    const uint32_t c = (w >> (2 * k)) & 3u;
-    const uint32_t f = c == 1u ? 1u : (c == 2u ? 3u : 0u);          // (sign << 1) | nonzero
-    out |= f << ((k & 1) * 16 + (k >> 1) * 2);
-  }
-  return out;
-}
-// Prepared word -> 8 bf16 pairs holding 2 * {-1, 0, +1}.
-__host__ __device__ __forceinline__ void decode16_prepared(uint32_t w, uint32_t* out) {
-#pragma unroll
-  for (int j = 0; j < 8; ++j) out[j] = (w << (14 - 2 * j)) & 0xC000C000u;
-}
-
-// GELU for the expert hidden layer.  The reference uses the exact-erf form (F.gelu default,
-// jarvis_model.py:236); here 0.5 x (1 + tanh(x (a + b x^2 + c x^4))) with a, b, c fitted to the erf
-// form: |difference| < 2.6e-5 everywhere (plus tanh.approx's 2^-11 relative error), an order of
-// magnitude below the bf16 rounding of the stored result, at 9 instructions instead of ~25 for erff
-// in an epilogue that is issue-bound.
-__device__ __forceinline__ float gelu_erf(float v) {
-  const float xc = fminf(fmaxf(v, -8.0f), 8.0f);     // keeps the fitted polynomial in its monotone range
-  const float x2 = xc * xc;
-  float pz = fmaf(-0.0003515195915898722f, x2, 0.03700566448133039f);
-  pz = fmaf(pz, x2, 0.797507862407347f);
-  float t;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(pz * xc));
-  const float hv = 0.5f * v;
-  return fmaf(hv, t, hv);
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -308,7 +229,6 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     // ---------------- epilogue ----------------
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int half = (warp - EPI_WARP0) >> 2; // which of the alternating 32-token chunks
-    uint8_t* stage_base = reinterpret_cast<uint8_t*>(ctl) + ((sizeof(SmemCtl) + 127) / 128) * 128;
     uint32_t tile_n = 0;
     TileCoord tc;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_n) {
@@ -319,74 +239,13 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         goto done;
       tc_fence_after_sync();
       const int feat = tc.ft * BM + q * 32 + lane;
-      uint8_t* stage = stage_base + (warp - EPI_WARP0) * STAGE_OUT_BYTES;
       const float alpha = __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows) *
                           (p.w_layout ? 0.5f : 1.0f);   // prepared weights decode to +-2
       const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MAX;
       for (int c0 = half * 32; c0 < bn; c0 += 64) {
         if (tc.tok0 + c0 >= tc.tok_end) break;   // warp-uniform
         const int ntok = min(32, tc.tok_end - (tc.tok0 + c0));
-        // residual epilogue: start the loads of the old values before waiting for the accumulator
-        float4 old[8];
-        if (p.epilogue == JB200_EPI_RESID_F32) {
-          const float* o = reinterpret_cast<const float*>(p.out);
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
-            old[it] = r < ntok ? __ldcs(reinterpret_cast<const float4*>(
-                                     o + size_t(tc.tok0 + c0 + r) * p.N + tc.ft * BM + q * 32 + c16 * 4))
-                               : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-        uint32_t v[32];
-        tmem_ld_32x32(t_lane + c0, v);
-        tmem_ld_wait();
-        // The accumulator chunk is lane = out-feature, register = token; HBM wants token rows.  Turn
-        // it through this warp's staging block in shared memory ([32 tokens][32 features]) so that
-        // global memory sees 16-byte accesses on whole 64 B / 128 B row segments.
-        const int f0 = tc.ft * BM + q * 32;
-        const size_t row0 = size_t(tc.tok0 + c0);
-        if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16) {
-          const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;
-          __nv_bfloat16* st = reinterpret_cast<__nv_bfloat16*>(stage);
-          // lane pairs (features f, f+1) swap one value per token pair, so each lane writes a bf16x2 word:
-          // 16 four-byte staging stores per chunk instead of 32 two-byte ones (shared-memory bandwidth is
-          // what the tensor core's operand reads, the decoders and this epilogue compete for)
-          const bool odd = lane & 1;
-          uint32_t* stw = reinterpret_cast<uint32_t*>(st);
-#pragma unroll
-          for (int jj = 0; jj < 16; ++jj) {
-            float a = alpha * __uint_as_float(v[2 * jj]);
-            float b = alpha * __uint_as_float(v[2 * jj + 1]);
-            if (gelu) { a = gelu_erf(a); b = gelu_erf(b); }
-            const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
-            const uint32_t w2 = odd ? pack_bf16x2(got, b) : pack_bf16x2(a, got);
-            stw[(2 * jj + (odd ? 1 : 0)) * 16 + (lane >> 1)] = w2;   // [token][feature pair]
-          }
-          __syncwarp();
-          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out);
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int idx = it * 32 + lane, r = idx >> 2, c16 = idx & 3;
-            const uint4 w4 = *reinterpret_cast<const uint4*>(st + r * 32 + c16 * 8);
-            if (r < ntok) *reinterpret_cast<uint4*>(o + (row0 + r) * p.N + f0 + c16 * 8) = w4;
-          }
-        } else {
-          const bool resid = p.epilogue == JB200_EPI_RESID_F32;
-          float* st = reinterpret_cast<float*>(stage);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) st[j * 32 + lane] = alpha * __uint_as_float(v[j]);
-          __syncwarp();
-          float* o = reinterpret_cast<float*>(p.out);
-#pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int idx = it * 32 + lane, r = idx >> 3, c16 = idx & 7;
-            float4 w4 = *reinterpret_cast<const float4*>(st + r * 32 + c16 * 4);
-            if (resid) { w4.x += old[it].x; w4.y += old[it].y; w4.z += old[it].z; w4.w += old[it].w; }
-            if (r < ntok) *reinterpret_cast<float4*>(o + (row0 + r) * p.N + f0 + c16 * 4) = w4;
-          }
-        }
-        __syncwarp();   // staging block is reused by the next chunk
+        store_acc_chunk(p, t_lane + c0, alpha, size_t(tc.tok0 + c0), tc.ft * BM + q * 32, ntok, lane);
       }
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
@@ -400,22 +259,6 @@ done:
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
 }
 
 int pick_bn(int M, int G, int n_ft, int sms) {
@@ -433,6 +276,9 @@ int pick_bn(int M, int G, int n_ft, int sms) {
 }
 
 }  // namespace
+
+int pair_token_tile(int M, int N, int G, int bn_override, int sms);
+int launch_ternary_gemm_pair(const void* x_bf16, const GemmParams& p, cudaStream_t stream);
 
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
@@ -452,8 +298,28 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   const int sms = sm_count();
   if (sms <= 0) return JB200_ERR_CUDA;
   const int n_ft = N / BM;
-  int bn = bn_override > 0 ? bn_override : pick_bn(M, G, n_ft, sms);
-  JB_REQUIRE(bn == 32 || bn == 64 || bn == 128 || bn == 256, "ternary_linear: token tile %d not in {32,64,128,256}", bn);
+  const bool want_pair = (bn_override & JB200_TILE_CTA_PAIR) != 0;
+  bn_override &= ~JB200_TILE_CTA_PAIR;
+  JB_REQUIRE(bn_override == 0 || bn_override == 32 || bn_override == 64 || bn_override == 128 || bn_override == 256,
+             "ternary_linear: token tile %d not in {32,64,128,256}", bn_override);
+  const int pair_bn = want_pair ? pair_token_tile(M, N, G, bn_override, sms) : 0;
+  JB_REQUIRE(!want_pair || pair_bn != 0,
+             "ternary_linear: the CTA-pair kernel needs out_features %% 256 == 0 and a token tile of 0, 128 or 256");
+  const int bn = pair_bn ? pair_bn : (bn_override > 0 ? bn_override : pick_bn(M, G, n_ft, sms));
+
+  GemmParams p;
+  p.w_packed = w_packed;
+  p.alpha = alpha;
+  p.seg_offsets = seg_offsets;
+  p.out = out;
+  p.M = M; p.N = N; p.K = K; p.G = G;
+  p.alpha_rows = alpha_rows;
+  p.bn = bn;
+  p.epilogue = epilogue;
+  p.w_layout = w_layout;
+  p.status = device_status_ptr();
+  if (!p.status) return JB200_ERR_CUDA;
+  if (pair_bn) return launch_ternary_gemm_pair(x_bf16, p, stream);
 
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) {
@@ -473,18 +339,6 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
     return JB200_ERR_CUDA;
   }
 
-  GemmParams p;
-  p.w_packed = w_packed;
-  p.alpha = alpha;
-  p.seg_offsets = seg_offsets;
-  p.out = out;
-  p.M = M; p.N = N; p.K = K; p.G = G;
-  p.alpha_rows = alpha_rows;
-  p.bn = bn;
-  p.epilogue = epilogue;
-  p.w_layout = w_layout;
-  p.status = device_status_ptr();
-  if (!p.status) return JB200_ERR_CUDA;
 
   // per device and cheap: set on every call rather than remembering which devices have seen it
   JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));

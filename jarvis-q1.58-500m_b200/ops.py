@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32  # noqa: F401
+from ._lib import EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32, TILE_CTA_PAIR  # noqa: F401
 
 
 def _stream() -> int:

@@ -167,6 +167,58 @@ def test_grouped_ternary_linear(counts):
     assert _lib.device_status() == 0
 
 
+@pytest.mark.parametrize("tile", [0, 128, 256])
+@pytest.mark.parametrize("M,K,N", [(256, 64, 256), (300, 512, 512), (1000, 1024, 1024), (77, 128, 256)])
+def test_cta_pair_kernel_exact_on_integers(M, K, N, tile):
+    """The cta_group::2 variant (two SMs per 256-feature tile) must give the one-CTA kernel's results
+    bit for bit: exact integer GEMM in f32, and the same bf16 / GELU / residual outputs."""
+    g = torch.Generator().manual_seed(M + K + N + tile)
+    x = torch.randint(-4, 5, (M, K), generator=g).float()
+    q = torch.randint(-1, 2, (N, K), generator=g).float()
+    xb, one = x.bfloat16().cuda(), torch.ones(1).cuda()
+    for prepared in (False, True):
+        pk = orc.pack_ternary(q).cuda()
+        pk = ops.prepare_weights(pk) if prepared else pk
+        y = ops.ternary_linear(xb, pk, one, epilogue=ops.EPI_F32, token_tile=tile | ops.TILE_CTA_PAIR, prepared=prepared)
+        assert torch.equal(y.cpu(), x @ q.t())
+        for epi in (ops.EPI_BF16, ops.EPI_GELU_BF16):
+            a = torch.full((1,), 0.01).cuda()
+            y1 = ops.ternary_linear(xb, pk, a, epilogue=epi, prepared=prepared)
+            y2 = ops.ternary_linear(xb, pk, a, epilogue=epi, token_tile=tile | ops.TILE_CTA_PAIR, prepared=prepared)
+            assert torch.equal(y1, y2)
+    resid = torch.randn(M, N, generator=g)
+    o1, o2 = resid.clone().cuda(), resid.clone().cuda()
+    pk = orc.pack_ternary(q).cuda()
+    ops.ternary_linear(xb, pk, torch.full((1,), 0.3).cuda(), epilogue=ops.EPI_RESID_F32, out=o1)
+    ops.ternary_linear(xb, pk, torch.full((1,), 0.3).cuda(), epilogue=ops.EPI_RESID_F32, out=o2,
+                       token_tile=tile | ops.TILE_CTA_PAIR)
+    assert torch.equal(o1, o2)
+    assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("counts", [[100, 0, 37, 263], [0, 0, 0, 512], [1, 1, 1, 1], [300, 300, 300, 300]])
+def test_cta_pair_kernel_grouped(counts):
+    g = torch.Generator().manual_seed(sum(counts) + 1)
+    K, N, G = 256, 512, len(counts)
+    M = sum(counts)
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    x = torch.randint(-3, 4, (M, K), generator=g).float()
+    q = torch.randint(-1, 2, (G, N, K), generator=g).float()
+    alphas = torch.tensor([1.0, 0.5, 2.0, 4.0])[:G]
+    y = ops.ternary_linear_grouped(x.bfloat16().cuda(), orc.pack_ternary(q).cuda(), alphas.cuda(), offs.cuda(),
+                                   epilogue=ops.EPI_F32, token_tile=ops.TILE_CTA_PAIR)
+    ref = torch.cat([alphas[e] * (x[offs[e]:offs[e + 1]] @ q[e].t()) for e in range(G)])
+    assert torch.equal(y.cpu(), ref)
+    assert _lib.device_status() == 0
+
+
+def test_cta_pair_kernel_rejects_odd_feature_tiles():
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    packed = torch.zeros(384, 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(RuntimeError, match="256"):
+        ops.ternary_linear(x, packed, torch.ones(1, device="cuda"), token_tile=ops.TILE_CTA_PAIR)
+
+
 def test_argument_errors_are_reported():
     x = torch.zeros(4, 100, dtype=torch.bfloat16, device="cuda")
     packed = torch.zeros(128, 25, dtype=torch.uint8, device="cuda")
