@@ -105,10 +105,10 @@ inline EncodeTiledFn encode_tiled_fn() {
 
 
 // One [32 out-features (TMEM lanes)] x [32 tokens (columns)] accumulator chunk -> alpha / GELU / residual ->
-// global memory, straight from registers.  Lane = out-feature and register = token, so one store
-// instruction of a warp covers 32 consecutive features of a token row: 128 contiguous bytes for f32
-// outputs; for bf16 outputs lane pairs first swap one value per token pair, so that every lane stores a
-// bf16x2 word and an instruction covers two 64-byte row segments.  Nothing is staged in shared memory,
+// global memory, straight from registers.  Lane = out-feature and register = token, and memory wants token
+// rows, so lanes first trade values by shuffles: pairs for bf16 outputs (every lane stores a bf16x2 word, an
+// instruction covers two 64-byte row segments), quads for f32 outputs (every lane loads / stores a float4,
+// an instruction covers four 128-byte row segments).  Nothing is staged in shared memory,
 // whose bandwidth the tensor core's operand reads, the TMA writes and the decoders already use up.
 // Called by a whole epilogue warp.
 __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t taddr, float alpha, size_t row0, int f0,
@@ -132,23 +132,42 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t ta
       o += step;
     }
   } else {
-    float* o = reinterpret_cast<float*>(p.out) + row0 * p.N + f0 + lane;
-    if (p.epilogue == JB200_EPI_RESID_F32) {
+    // f32 outputs: 4x4 transposes inside lane quads (two shuffle rounds) turn "lane = feature, 4 registers =
+    // 4 tokens" into "lane = token (row0 + 4g + lane % 4), float4 = 4 features", so that loads of the old
+    // residual values and stores are 16 bytes per lane and cover four 128-byte row segments per instruction.
+    const bool resid = p.epilogue == JB200_EPI_RESID_F32;
+    const int sub = lane & 3;
+    float* o = reinterpret_cast<float*>(p.out) + (row0 + size_t(sub)) * p.N + f0 + (lane >> 2) * 4;
+    const size_t step = size_t(p.N) * 4;   // four token rows
+    float4 old[8];
+    if (resid) {
       // start the loads of the old values before waiting for the accumulator
-      float old[32];
 #pragma unroll
-      for (int j = 0; j < 32; ++j) old[j] = j < ntok ? __ldcs(o + size_t(j) * p.N) : 0.f;
-      tmem_ld_32x32(taddr, v);
-      tmem_ld_wait();
+      for (int g = 0; g < 8; ++g)
+        old[g] = 4 * g + sub < ntok ? __ldcs(reinterpret_cast<const float4*>(o + size_t(g) * step))
+                                    : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    const bool up = (lane & 2) != 0, odd = (lane & 1) != 0;
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ntok) o[size_t(j) * p.N] = __fadd_rn(__fmul_rn(alpha, __uint_as_float(v[j])), old[j]);
-    } else {
-      tmem_ld_32x32(taddr, v);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < ntok) o[size_t(j) * p.N] = alpha * __uint_as_float(v[j]);
+    for (int g = 0; g < 8; ++g) {
+      float v0 = alpha * __uint_as_float(v[4 * g + 0]), v1 = alpha * __uint_as_float(v[4 * g + 1]);
+      float v2 = alpha * __uint_as_float(v[4 * g + 2]), v3 = alpha * __uint_as_float(v[4 * g + 3]);
+      // swap the off-diagonal 2x2 blocks between lanes l and l ^ 2 ...
+      float r0 = __shfl_xor_sync(0xffffffffu, up ? v0 : v2, 2);
+      float r1 = __shfl_xor_sync(0xffffffffu, up ? v1 : v3, 2);
+      if (up) { v0 = r0; v1 = r1; } else { v2 = r0; v3 = r1; }
+      // ... then transpose inside every 2x2 block between lanes l and l ^ 1
+      r0 = __shfl_xor_sync(0xffffffffu, odd ? v0 : v1, 1);
+      r1 = __shfl_xor_sync(0xffffffffu, odd ? v2 : v3, 1);
+      if (odd) { v0 = r0; v2 = r1; } else { v1 = r0; v3 = r1; }
+      float4 w4 = make_float4(v0, v1, v2, v3);
+      if (resid) {
+        w4.x = __fadd_rn(w4.x, old[g].x); w4.y = __fadd_rn(w4.y, old[g].y);
+        w4.z = __fadd_rn(w4.z, old[g].z); w4.w = __fadd_rn(w4.w, old[g].w);
+      }
+      if (4 * g + sub < ntok) *reinterpret_cast<float4*>(o + size_t(g) * step) = w4;
     }
   }
 }
