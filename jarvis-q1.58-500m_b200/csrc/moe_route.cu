@@ -21,7 +21,7 @@ namespace {
 
 constexpr int MAX_E = 16;
 constexpr int ROUTER_THREADS = 256;                 // 8 warps, one token per warp at a time
-constexpr int ROUTER_TOKENS_PER_CTA = 64;
+constexpr int ROUTER_TOKENS_PER_CTA = 8;
 constexpr int META_CHUNK = 256;                     // assignments per CTA of the metadata kernels
 
 // ---------------------------------------------------------------------------------------------
