@@ -238,6 +238,20 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
                    float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
                    void* stream);
 
+/* ---- decode driver: next-token sampling ------------------------------------------------------- */
+
+/* One draw per row of logits, replacing sample_next_token (jarvis_engine/evaluate_jarvis.py:158-185):
+ * temperature <= 0 -> argmax (lowest id among equals); else x = logits / max(temperature, 1e-5), keep
+ * x >= the top_k-th largest x (ties kept), sort descending, softmax, drop position i >= 1 once the
+ * cumulative probability before it exceeds top_p (0 < top_p < 1; other values: no nucleus cut), and draw
+ * from the softmax over what is left.  The reference draws with torch.multinomial; here u[row] in [0, 1)
+ * comes from the caller and the draw is the inverse CDF over the kept tokens in descending order of x
+ * (equal x: lower id first).  logits: f32 (logits_dtype 0) or bf16 (1), row stride ld >= V elements.
+ * top_k in 1..1024 (the reference's top_k=None, a nucleus cut over the full vocabulary, is not offered).
+ * out_prob (optional, f32 [n_rows]): probability of the drawn token under the filtered distribution. */
+int jb200_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,
+                 float top_p, const float* u, int64_t* out_token, float* out_prob, void* stream);
+
 /* Host-side copy of the bit manipulation the GEMM's decoder warps run: 16 two-bit codes
  * (one little-endian u32 of the packed layout) -> 16 bf16 values in out8[8] (two per u32,
  * lower in-feature in the low half).  Runs on the CPU; used by the unit tests. */

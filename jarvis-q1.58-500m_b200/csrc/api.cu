@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 5; }
+int jb200_abi_version(void) { return 6; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -152,6 +152,12 @@ int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* pac
                                  int w_layout, void* stream) {
   return launch_ternary_gemm(x, M, K, packed, alpha, N, N, G, seg_offsets, epilogue, out, token_tile, w_layout,
                              static_cast<cudaStream_t>(stream));
+}
+
+int jb200_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,
+                 float top_p, const float* u, int64_t* out_token, float* out_prob, void* stream) {
+  return launch_sample(logits, logits_dtype, ld, n_rows, V, temperature, top_k, top_p, u, out_token, out_prob,
+                       static_cast<cudaStream_t>(stream));
 }
 
 int jb200_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* y, int y_dtype, int n_rows, int C,

@@ -104,6 +104,18 @@ inline EncodeTiledFn encode_tiled_fn() {
 }
 
 
+// Residual epilogue: the old values of a tile (128 KiB) are what its epilogue waits for longest.  Called by
+// an epilogue warp BEFORE it waits for the tile's accumulator, i.e. while the tile's MMAs still run: every
+// lane asks L2 for the 128-byte line (32 f32 features) of one token row of each chunk the warp will handle.
+__device__ __forceinline__ void prefetch_residual_rows(const GemmParams& p, int tok0, int tok_end, int f0, int half,
+                                                       int bn, int lane) {
+  const float* o = reinterpret_cast<const float*>(p.out);
+  for (int c0 = half * 32; c0 < bn; c0 += 64) {
+    const int row = tok0 + c0 + lane;
+    if (row < tok_end) prefetch_l2(o + size_t(row) * p.N + f0);
+  }
+}
+
 // One [32 out-features (TMEM lanes)] x [32 tokens (columns)] accumulator chunk -> alpha / GELU / residual ->
 // global memory, straight from registers.  Lane = out-feature and register = token, and memory wants token
 // rows, so lanes first trade values by shuffles: pairs for bf16 outputs (every lane stores a bf16x2 word, an

@@ -56,4 +56,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
                      int head_dim, cudaStream_t stream);
 size_t attn_scan_scratch_bytes(int B, int T, int H);
 
+int launch_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,
+                  float top_p, const float* u, int64_t* out_token, float* out_prob, cudaStream_t stream);
+
 }  // namespace jb

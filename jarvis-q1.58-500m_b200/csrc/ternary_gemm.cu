@@ -235,6 +235,8 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
       if (!tile_coord(ctl, t, n_ft, p.G, bn, &tc)) break;
       const uint32_t acc = tile_n & 1u;
       const uint32_t acc_ph = (tile_n >> 1) & 1u;
+      if (p.epilogue == JB200_EPI_RESID_F32)
+        prefetch_residual_rows(p, tc.tok0, tc.tok_end, tc.ft * BM + q * 32, half, bn, lane);
       if (!mbar_wait(smem_u32(&ctl->tmem_full[acc]), acc_ph, abort_flag, p.status, JB200_STATUS_GEMM_EPILOGUE))
         goto done;
       tc_fence_after_sync();

@@ -374,3 +374,33 @@ def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=N
         "jb200_lsf_scan",
     )
     return out, h_last
+
+
+def sample(logits: torch.Tensor, u: torch.Tensor | None = None, *, temperature: float = 0.7, top_k: int = 50,
+           top_p: float = 0.9, want_prob: bool = False):
+    """One token per row of `logits` ((B, V) f32 or bf16, rows may be strided): temperature / top-k / top-p
+    filtering of sample_next_token (jarvis_engine/evaluate_jarvis.py:158-185) and an inverse-CDF draw with
+    the caller's uniform numbers u (B,) f32.  temperature <= 0: argmax.  -> int64 (B, 1) [, f32 (B,) prob]."""
+    lib = _lib.load()
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise RuntimeError("sample: logits must be (B, V) with contiguous rows")
+    if logits.dtype not in (torch.float32, torch.bfloat16) or not logits.is_cuda:
+        raise RuntimeError("sample: logits must be a CUDA f32 or bf16 tensor")
+    B, V = logits.shape
+    greedy = temperature is None or temperature <= 0.0
+    if u is None:
+        if not greedy and top_k != 1:
+            raise RuntimeError("sample: a uniform number per row (u) is needed to draw")
+    else:
+        _need(u, torch.float32, "sample.u")
+        if u.numel() != B:
+            raise RuntimeError("sample: u must hold one number per row")
+    out = torch.empty((B, 1), dtype=torch.int64, device=logits.device)
+    prob = torch.empty((B,), dtype=torch.float32, device=logits.device) if want_prob else None
+    _lib.check(
+        lib.jb200_sample(_ptr(logits), 0 if logits.dtype == torch.float32 else 1, logits.stride(0), B, V,
+                         0.0 if greedy else float(temperature), int(top_k or 0), float(top_p if top_p is not None else 0.0),
+                         _ptr(u) if u is not None else None, _ptr(out), _ptr(prob) if prob is not None else None, _stream()),
+        "jb200_sample",
+    )
+    return (out, prob) if want_prob else out

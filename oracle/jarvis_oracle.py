@@ -336,3 +336,55 @@ def model_step(idx, sd: dict, n_layers: int, n_heads: int, h_prevs=None, attn_st
         h_last.append(r["h_last"])
         states.append(r["attn_state"])
     return F.linear(rmsnorm(x, sd["final_norm.weight"]), sd["lm_head.weight"]), h_last, states
+
+
+# ---- decode driver: sampling filter ----------------------------------------------------------------
+def sample_filtered_probs(logits: torch.Tensor, temperature: float = 0.7, top_k: int = 50, top_p: float = 0.9):
+    """The distribution sample_next_token draws from (jarvis_engine/evaluate_jarvis.py:158-185), for
+    temperature > 0: logits / max(T, 1e-5); everything below the top_k-th value -> -inf (ties with it
+    stay); sort descending, softmax, cumulative sum, drop sorted position i >= 1 when the cumulative
+    probability before it exceeds top_p (only for 0 < top_p < 1); softmax of what is left.  (B, V) -> (B, V)."""
+    x = logits.float() / max(temperature, 1e-5)
+    if top_k is not None and top_k > 0:
+        kth = torch.topk(x, min(top_k, x.size(-1))).values[:, [-1]]
+        x = x.masked_fill(x < kth, float("-inf"))
+    if top_p is not None and 0.0 < top_p < 1.0:
+        sx, si = torch.sort(x, descending=True, stable=True)
+        cum = torch.cumsum(F.softmax(sx, dim=-1), dim=-1)
+        remove = cum > top_p
+        remove[..., 1:] = remove[..., :-1].clone()
+        remove[..., 0] = False
+        x = x.masked_fill(remove.scatter(1, si, remove), float("-inf"))
+    return F.softmax(x, dim=-1)
+
+
+def sample_inverse_cdf(logits: torch.Tensor, u: torch.Tensor, temperature: float = 0.7, top_k: int = 50,
+                       top_p: float = 0.9):
+    """One draw per row from sample_filtered_probs with the caller's uniform numbers: the kept tokens are
+    walked in descending order of probability (equal probability: lower id first) and the first one whose
+    running sum exceeds u is taken.  temperature <= 0: argmax with the lowest id among equals (the
+    reference's torch.argmax branch).  The reference itself draws with torch.multinomial, whose random
+    stream cannot be reproduced elsewhere; the filtered distribution is what is pinned to it.
+    -> (tokens int64 (B, 1), probability of each drawn token (B,))."""
+    B, V = logits.shape
+    if temperature is None or temperature <= 0.0:
+        x = logits.float()
+        best = x.max(dim=-1, keepdim=True).values
+        tok = torch.where(x == best, torch.arange(V).expand(B, V), torch.full((B, V), V)).min(dim=-1, keepdim=True).values
+        return tok, torch.ones(B)
+    p = sample_filtered_probs(logits, temperature, top_k, top_p)
+    sp, si = torch.sort(p, descending=True, stable=True)      # stable: equal values keep ascending ids
+    toks, probs = [], []
+    for b in range(B):
+        c, pick = 0.0, None
+        n_kept = int((sp[b] > 0).sum())
+        for i in range(n_kept):
+            c += float(sp[b, i])
+            if c > float(u[b]):
+                pick = i
+                break
+        if pick is None:
+            pick = n_kept - 1
+        toks.append(int(si[b, pick]))
+        probs.append(float(sp[b, pick]))
+    return torch.tensor(toks).view(B, 1), torch.tensor(probs)

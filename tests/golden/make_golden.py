@@ -254,10 +254,78 @@ def golden_tbin():
                                        "blocks.0.moe.router.weight", "blocks.0.attn.gamma_raw")})
 
 
+# ---- 7. decode driver: the reference's sampling filter and its continuous-batching slot policy -----------
+def _reference_defs(path, names):
+    """exec only the named top-level classes / functions of a reference script (its module level parses
+    arguments and imports tokenisers, which the fixtures do not need)."""
+    import ast
+    import collections
+    import time
+    import typing
+    src = open(path).read()
+    tree = ast.parse(src)
+    body = [n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef)) and n.name in names]
+    ns = {"torch": torch, "F": torch.nn.functional, "collections": collections, "time": time,
+          "List": typing.List, "Dict": typing.Dict, "Optional": typing.Optional}
+    exec(compile(ast.Module(body=body, type_ignores=[]), path, "exec"), ns)
+    return ns
+
+
+def golden_sampling():
+    ns = _reference_defs(os.path.join(REF, "jarvis_engine", "evaluate_jarvis.py"), {"sample_next_token"})
+    gen = torch.Generator().manual_seed(2024)
+    B, V = 6, 512
+    logits = torch.randn(B, V, generator=gen) * 3.0
+    logits[1, 100:140] = logits[1, 100]          # a plateau of equal logits around the top-k boundary
+    logits[2] = torch.round(logits[2])            # many exact ties
+    captured = {}
+    real_multinomial = torch.multinomial
+
+    def fake_multinomial(probs, num_samples=1):
+        captured["probs"] = probs.clone()
+        return probs.argmax(dim=-1, keepdim=True)
+
+    out = {"logits": logits}
+    settings = [(0.7, 50, 0.9), (1.0, 5, 0.5), (1.3, 200, 0.95), (0.7, 50, 1.0), (0.25, 1024, 0.3)]
+    torch.multinomial = fake_multinomial
+    try:
+        for i, (t, k, p) in enumerate(settings):
+            ns["sample_next_token"](logits.clone(), temperature=t, top_k=k, top_p=p)
+            out[f"probs_{i}"] = captured["probs"]
+    finally:
+        torch.multinomial = real_multinomial
+    out["settings"] = torch.tensor(settings, dtype=torch.float64)
+    out["greedy"] = ns["sample_next_token"](logits.clone(), temperature=0.0)
+    save("sampling", **out)
+
+
+def golden_scheduler():
+    ns = _reference_defs(os.path.join(REF, "experiments", "exp_batching_continuous.py"),
+                         {"Request", "ContinuousBatchingScheduler"})
+    sched = ns["ContinuousBatchingScheduler"](max_batch_size=4, device="cpu")
+    reqs = [ns["Request"](req_id=i, prompt_tokens=[10, 20, 30], max_new_tokens=(i % 4 + 2)) for i in range(10)]
+    for r in reqs:
+        sched.add_request(r)
+    trace, finish_iter = [], [-1] * len(reqs)
+    it = 0
+    while sched.active_slots or sched.waiting_queue:
+        stepped = sched.step()
+        it += 1
+        slots = [sched.active_slots[s].req_id if s in sched.active_slots else -1 for s in range(4)]
+        for r in reqs:
+            if r.is_finished and finish_iter[r.req_id] < 0:
+                finish_iter[r.req_id] = it
+        trace.append([stepped, len(sched.waiting_queue)] + slots)
+    save("scheduler", trace=torch.tensor(trace), finish_iter=torch.tensor(finish_iter),
+         n_generated=torch.tensor([len(r.generated_tokens) for r in reqs]))
+
+
 if __name__ == "__main__":
     golden_pack()
     golden_attention()
     golden_moe()
     golden_lsf()
     golden_block_model()
+    golden_sampling()
+    golden_scheduler()
     golden_tbin()   # last: building its models draws from the global RNG that later fixtures would see
