@@ -13,10 +13,11 @@
 // carry-in, publishes (product of decays, end value) in shared memory, the carries are combined in
 // warp order (the recurrence is an associative affine map), and every thread fixes its values up
 // with  h_t = local_t + P_t * carry_in.  A CTA owns 64 channels of one sequence and walks T tile by
-// tile.  When B*D/64 CTAs cannot fill the GPU, T is also cut into segments: a first launch (ENDS_ONLY)
-// computes each non-final segment's end value (and decay product) from a zero carry, reading m once
-// more (it was just written by the MoE combine and is normally still in L2); the main launch folds
-// the earlier segments' ends into its carry-in, which is exact because the recurrence is affine.
+// tile.  When B*D/64 CTAs cannot fill the GPU, T is also cut into segments.  A first launch (ENDS_ONLY)
+// then computes, with ONE CTA PER TILE of the non-final segments (all tiles in parallel, nothing
+// sequential), each tile's end value (and decay product) from a zero carry, reading m once more (it was
+// just written by the MoE combine and is normally still in L2); the main launch folds the ends of all
+// earlier tiles into its carry-in, which is exact because the recurrence is an affine map.
 #include "common.cuh"
 #include "launchers.h"
 
@@ -41,8 +42,9 @@ struct LsfParams {
   float* h_last;           // [B][D] f32 or null
   int B, T, D;
   int seg_len, nseg;       // tokens per segment (multiple of the tile), number of segments (grid.z)
-  float* seg_end;          // [B][nseg-1][D] end value of each non-final segment from a zero carry
-  float* seg_prod;         // [B][nseg-1][D] product of its decays (tensor mode)
+  int n_pre_tiles;         // tiles in the non-final segments = (nseg - 1) * seg_len / tile
+  float* seg_end;          // [B][n_pre_tiles][D] end value of each of those tiles from a zero carry
+  float* seg_prod;         // [B][n_pre_tiles][D] product of its decays (tensor mode)
 };
 
 template <typename T>
@@ -88,17 +90,19 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
 #pragma unroll
     for (int i = 0; i < TPW; ++i) { pw[i] = a; a *= alpha; }
   }
-  const int seg = blockIdx.z;
-  const int t_begin = seg * p.seg_len;
-  const int t_end = min(p.T, t_begin + p.seg_len);
+  constexpr int TILE = LSF_WARPS * TPW;
+  const int seg = blockIdx.z;                                    // ENDS_ONLY: the tile's index instead
+  const int t_begin = ENDS_ONLY ? seg * TILE : seg * p.seg_len;
+  const int t_end = ENDS_ONLY ? t_begin + TILE : min(p.T, t_begin + p.seg_len);
   float2 carry = make_float2(0.f, 0.f);
   float2 pcarry = make_float2(1.f, 1.f);   // running decay product of the segment (ENDS_ONLY, tensor mode)
   if (!ENDS_ONLY) {
     if (p.h0 && ch_ok) carry = __ldg(reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch));
     if (seg > 0 && ch_ok) {
-      const float a_seg = TENSOR_ALPHA ? 0.f : expf(float(p.seg_len) * logf(alpha));
-      const size_t e0 = (size_t(b) * (p.nseg - 1)) * p.D + ch;
-      for (int s2 = 0; s2 < seg; ++s2) {
+      const float a_seg = TENSOR_ALPHA ? 0.f : expf(float(TILE) * logf(alpha));   // decay over one tile
+      const size_t e0 = (size_t(b) * p.n_pre_tiles) * p.D + ch;
+      const int n_before = seg * (p.seg_len / TILE);
+      for (int s2 = 0; s2 < n_before; ++s2) {
         const float2 e = __ldg(reinterpret_cast<const float2*>(p.seg_end + e0 + size_t(s2) * p.D));
         if (TENSOR_ALPHA) {
           const float2 q = __ldg(reinterpret_cast<const float2*>(p.seg_prod + e0 + size_t(s2) * p.D));
@@ -190,7 +194,7 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
     }
   }
   if (ENDS_ONLY && ch_ok && warp == 0) {
-    const size_t e = (size_t(b) * (p.nseg - 1) + seg) * p.D + ch;
+    const size_t e = (size_t(b) * p.n_pre_tiles + seg) * p.D + ch;
     *reinterpret_cast<float2*>(p.seg_end + e) = carry;
     if (TENSOR_ALPHA) *reinterpret_cast<float2*>(p.seg_prod + e) = pcarry;
   }
@@ -241,7 +245,7 @@ int launch_t(const LsfParams& p, cudaStream_t stream) {
     return JB200_OK;
   }
   if (p.nseg > 1) {
-    dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg - 1);
+    dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.n_pre_tiles);
     lsf_scan_kernel<TA, TM, TOut, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);
     JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
   }
@@ -271,7 +275,7 @@ size_t lsf_scan_scratch_bytes(int B, int T, int D) {
   const int sms = sm_count();
   int len, ns;
   pick_lsf_segments(B, T, D, sms > 0 ? sms : 148, &len, &ns);
-  return size_t(2) * B * size_t(ns - 1) * D * sizeof(float);
+  return size_t(2) * B * size_t(ns - 1) * size_t(len / LSF_TILE) * D * sizeof(float);
 }
 
 int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const float* alpha_scalar,
@@ -299,16 +303,18 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
   p.B = B; p.T = T; p.D = D;
   p.seg_len = (T + LSF_TILE - 1) / LSF_TILE * LSF_TILE;
   p.nseg = 1;
+  p.n_pre_tiles = 0;
   p.seg_end = p.seg_prod = nullptr;
   if (scratch) {
     JB_REQUIRE((reinterpret_cast<uintptr_t>(scratch) & a8) == 0, "lsf_scan: scratch pointer misaligned");
     const int sms = sm_count();
     if (sms <= 0) return JB200_ERR_CUDA;
     pick_lsf_segments(B, T, D, sms, &p.seg_len, &p.nseg);
+    p.n_pre_tiles = (p.nseg - 1) * (p.seg_len / LSF_TILE);
     p.seg_end = reinterpret_cast<float*>(scratch);
-    p.seg_prod = p.seg_end + size_t(B) * (p.nseg - 1) * D;
+    p.seg_prod = p.seg_end + size_t(B) * p.n_pre_tiles * D;
   }
-  JB_REQUIRE(p.nseg <= 65535, "lsf_scan: too many segments");
+  JB_REQUIRE(p.nseg <= 65535 && p.n_pre_tiles <= 65535, "lsf_scan: too many segments");
   const bool ta = alpha_tensor != nullptr;
   using bf = __nv_bfloat16;
   if (!ta) {
