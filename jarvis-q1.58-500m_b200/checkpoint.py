@@ -70,7 +70,9 @@ def load_packed_state_dict(model: torch.nn.Module, packed_sd: dict) -> torch.nn.
         for k, v in plain.items():
             if k not in own:
                 raise KeyError(f"load_packed_state_dict: unexpected key {k}")
-            own[k].copy_(v.to(own[k].dtype))
+            if v.numel() != own[k].numel():
+                raise ValueError(f"load_packed_state_dict: {k} has {v.numel()} elements, the model expects {own[k].numel()}")
+            own[k].copy_(v.to(own[k].dtype).reshape(own[k].shape))   # containers store 0-dim scalars as [1]
         entries = {}
         for k, d in tern.items():
             if k not in own:

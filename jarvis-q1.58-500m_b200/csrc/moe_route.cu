@@ -21,7 +21,7 @@ namespace {
 
 constexpr int MAX_E = 16;
 constexpr int ROUTER_THREADS = 256;                 // 8 warps, one token per warp at a time
-constexpr int ROUTER_TOKENS_PER_CTA = 8;
+constexpr int ROUTER_TOKENS_PER_CTA = 32;             // 512 CTAs at 16k tokens: four resident per SM (64 registers)
 constexpr int META_CHUNK = 256;                     // assignments per CTA of the metadata kernels
 
 // ---------------------------------------------------------------------------------------------
@@ -63,13 +63,22 @@ __device__ __forceinline__ void router_finish(const float (&acc)[E], int lane, i
   }
 }
 
+// Router weights in shared memory: [E][C] with the 4-float groups of every row swizzled (group g of a row
+// sits at g ^ ((g >> 3) & 1)).  A lane reads the two groups of its 8 consecutive channels, so lanes are
+// 32 bytes apart and, unswizzled, lanes l and l + 4 of each 8-lane phase would hit the same banks.
+__device__ __forceinline__ int router_w_index(int c) {   // c: channel, any value; returns the swizzled column
+  const int g = c >> 2;
+  return ((g ^ ((g >> 3) & 1)) << 2) | (c & 3);
+}
+
 // 8 consecutive activations times the matching router weights of every expert
 template <int E>
 __device__ __forceinline__ void router_dot8(const float (&xv)[8], const float* w_s, int C, int c, float (&acc)[E]) {
+  const int ca = router_w_index(c), cb = router_w_index(c + 4);
 #pragma unroll
   for (int e = 0; e < E; ++e) {
-    const float4 wa = *reinterpret_cast<const float4*>(w_s + e * C + c);
-    const float4 wb = *reinterpret_cast<const float4*>(w_s + e * C + c + 4);
+    const float4 wa = *reinterpret_cast<const float4*>(w_s + e * C + ca);
+    const float4 wb = *reinterpret_cast<const float4*>(w_s + e * C + cb);
     acc[e] += xv[0] * wa.x + xv[1] * wa.y + xv[2] * wa.z + xv[3] * wa.w + xv[4] * wb.x + xv[5] * wb.y +
               xv[6] * wb.z + xv[7] * wb.w;
   }
@@ -84,7 +93,7 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   extern __shared__ float w_s[];  // [E][C]
   __shared__ float p_acc[ROUTER_THREADS / 32][E];
   __shared__ int h_acc[E];
-  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[i] = __ldg(w_router + i);
+  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[(i / C) * C + router_w_index(i % C)] = __ldg(w_router + i);
   if (threadIdx.x < E) h_acc[threadIdx.x] = 0;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -127,7 +136,7 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 // logits in the same summation order as router_top2_kernel, so routing is bit-identical to running
 // the two kernels separately while the row is read from HBM once.
 template <int E>
-__global__ void __launch_bounds__(ROUTER_THREADS)
+__global__ void __launch_bounds__(ROUTER_THREADS, 4)
 rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_norm, float eps,
                       __nv_bfloat16* __restrict__ xn, const float* __restrict__ w_router, int n_tokens, int C,
                       int tokens_per_cta, int64_t* __restrict__ topk_idx, float* __restrict__ gates,
@@ -135,7 +144,7 @@ rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_n
   extern __shared__ float w_s[];  // [E][C]
   __shared__ float p_acc[ROUTER_THREADS / 32][E];
   __shared__ int h_acc[E];
-  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[i] = __ldg(w_router + i);
+  for (int i = threadIdx.x; i < E * C; i += ROUTER_THREADS) w_s[(i / C) * C + router_w_index(i % C)] = __ldg(w_router + i);
   if (threadIdx.x < E) h_acc[threadIdx.x] = 0;
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

@@ -136,3 +136,43 @@ def test_sampled_generation_is_reproducible_by_seed():
         outs.append([r.generated_tokens for r in sorted(sched.completed, key=lambda r: r.req_id)])
     assert outs[0] == outs[1]
     assert all(len(t) == 6 for t in outs[0])
+
+
+def test_evaluate_cli_pieces_on_a_tiny_model(tmp_path):
+    """Corpus loss through evaluate_corpus equals calling the model window by window, and sits on the oracle's
+    cross-entropy; greedy generation by re-running the window equals stateful decode for a prompt that fits
+    one window... up to the LSF decay, which is per call: so only the first generated token is compared."""
+    from jarvis_b200 import checkpoint, evaluate
+    model, sd = _tiny_model()
+    path = tmp_path / "tiny.pt"
+    torch.save({"model_state_dict": {"_orig_mod." + k: v for k, v in sd.items()}, "step": 7}, path)
+    loaded, step = evaluate.load_model(str(path), vocab=256, d_model=128, n_layers=2, n_heads=2)
+    assert step == 7
+    gen = torch.Generator().manual_seed(8)
+    toks = torch.randint(0, 256, (400,), generator=gen)
+    rep = evaluate.evaluate_corpus(loaded, toks, num_windows=4, seq_len=64, seed=1)
+    starts = evaluate.window_starts(400, 4, 64, 1)
+    losses, ce_ref = [], []
+    for s in starts:
+        x, y = toks[s:s + 64][None].cuda(), toks[s + 1:s + 65][None].cuda()
+        losses.append(float(model(x, targets=y)[1]))
+        ref_logits, _ = orc.model_forward(x.cpu(), sd, 2, 2)
+        ce_ref.append(float(torch.nn.functional.cross_entropy(ref_logits.view(-1, 256), y.cpu().view(-1))))
+    assert abs(rep["mean_loss"] - sum(losses) / 4) < 1e-5
+    assert abs(rep["mean_loss"] - sum(ce_ref) / 4) < 0.05 * abs(sum(ce_ref) / 4) + 0.05   # loss = CE + small aux terms
+    # packed container round trip through the loader
+    tb = tmp_path / "tiny.jarvis-tbin"
+    checkpoint.write_tbin(sd, str(tb))
+    from_tbin, _ = evaluate.load_model(str(tb), vocab=256, d_model=128, n_layers=2, n_heads=2)
+    x = toks[:48][None].cuda()
+    assert rel_l2(from_tbin(x)[0].float(), model(x)[0].float()) < 2e-2
+    # generation
+    prompt = toks[:20].tolist()
+    a = evaluate.generate(model, prompt, max_new_tokens=5, temperature=0.0)
+    b = evaluate.generate(model, prompt, max_new_tokens=5, temperature=0.0, stateful=True)
+    assert len(a) == 5 and len(b) == 5 and a[0] == b[0]
+    first = int(model(torch.tensor([prompt]).cuda())[0][0, -1].float().argmax())
+    assert a[0] == first
+    c = evaluate.generate(model, prompt, max_new_tokens=5, temperature=0.8, top_k=10, top_p=0.9, seed=5)
+    d = evaluate.generate(model, prompt, max_new_tokens=5, temperature=0.8, top_k=10, top_p=0.9, seed=5)
+    assert c == d

@@ -95,3 +95,55 @@ def test_eos_token_retires_early():
     sched.add_request(serving.Request(0, [1], max_new_tokens=10))
     assert sched.run() == 1
     assert sched.completed[0].generated_tokens == [42] and sched.completed[0].is_finished
+
+
+def test_evaluate_window_selection_follows_the_reference_rule():
+    from jarvis_b200 import evaluate
+    # long corpus: back-to-back windows
+    assert evaluate.window_starts(10 * 9, num_windows=10, seq_len=8, seed=1) == [i * 8 for i in range(10)]
+    # short corpus: seeded random starts, the same numbers torch draws for the reference (evaluate_jarvis.py:343-345)
+    g = torch.Generator(device="cpu").manual_seed(42)
+    want = torch.randint(0, 50 - 8 - 1, (10,), generator=g).tolist()
+    assert evaluate.window_starts(50, num_windows=10, seq_len=8, seed=42) == want
+    import pytest
+    with pytest.raises(ValueError):
+        evaluate.window_starts(8, 1, 8, 0)
+
+
+def test_evaluate_corpus_statistics_with_a_stub_model():
+    from jarvis_b200 import evaluate
+
+    class Stub(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.tok_emb = torch.nn.Embedding(16, 4)
+
+        def forward(self, x, targets=None, persist_state=False):
+            assert not persist_state and x.shape == targets.shape
+            assert torch.equal(x[0, 1:], targets[0, :-1])          # y is x shifted by one token
+            return None, x.float().mean() / 10.0
+
+    toks = torch.arange(0, 200) % 16
+    r = evaluate.evaluate_corpus(Stub(), toks, num_windows=5, seq_len=8, seed=3)
+    want = [float((toks[i * 8:i * 8 + 8].float().mean()) / 10.0) for i in range(5)]
+    assert abs(r["mean_loss"] - sum(want) / 5) < 1e-6
+    import math
+    import statistics
+    assert abs(r["std_loss"] - statistics.stdev(want)) < 1e-6
+    assert abs(r["perplexity"] - math.exp(r["mean_loss"])) < 1e-9
+    assert r["windows_evaluated"] == 5 and r["tokens_evaluated"] == 40 and not r["has_nan_inf"]
+
+
+def test_evaluate_token_files(tmp_path):
+    from jarvis_b200 import evaluate
+    import numpy as np
+    np.save(tmp_path / "c.npy", np.arange(7))
+    (tmp_path / "c.ids").write_text("3 1 4 1 5")
+    enc = evaluate.IdTokenizer()
+    assert evaluate.load_token_file(str(tmp_path / "c.npy"), enc).tolist() == list(range(7))
+    assert evaluate.load_token_file(str(tmp_path / "c.ids"), enc).tolist() == [3, 1, 4, 1, 5]
+    import pytest
+    with pytest.raises(FileNotFoundError):
+        evaluate.load_token_file(str(tmp_path / "missing.txt"), enc)
+    a = evaluate.parse_args(["--prompt", "1 2 3", "--temperature", "0", "--stateful"])
+    assert a.prompt == "1 2 3" and a.temperature == 0 and a.stateful and a.top_k == 50 and a.num_windows == 200
