@@ -91,8 +91,8 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
 }
 
 // ELU(x)+1 = x+1 for x > 0, exp(x) otherwise; branch-free, exp through ex2.approx (rel. error 2^-22,
-// far below the bf16 rounding of the result).
-__device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(fminf(x, 0.f)); }
+// far below the bf16 rounding of the result).  For large positive x the unused exp is +inf, never NaN.
+__device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(x); }
 
 template <bool STATE_ONLY>
 __global__ void __launch_bounds__(ATTN_THREADS, 4)
@@ -127,7 +127,9 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   for (int e = tid; e < 8 * 32; e += ATTN_THREADS) {
     const int d = e >> 5, ln = e & 31;
     const int diff0 = 8 * (d - 1) + (ln >> 2) - 2 * (ln & 3);   // query row - key column of c0
-    auto fac = [&](int x) { return x >= 0 ? expf(log_g * float(x)) : 0.f; };
+    // gamma^(i-j) / sqrt(D): the 1/8 of the query feature map is a power of two, so applying it to the scores
+    // (here and in the cross-chunk factor below) instead of to every element of q gives the same bits
+    auto fac = [&](int x) { return x >= 0 ? 0.125f * expf(log_g * float(x)) : 0.f; };
     sm->mf[d][ln] = make_float4(fac(diff0), fac(diff0 - 1), fac(diff0 + 8), fac(diff0 + 7));
   }
 
@@ -222,11 +224,10 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         const uint4 lo = *lo_p, hi = *hi_p;
         const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
         uint32_t ol[4], oh[4];
-        const float scale = which == 0 ? 0.125f : 1.0f;  // 1/sqrt(64)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float a0 = elu1(bf16_lo(lw[j])) * scale, a1 = elu1(bf16_hi(lw[j])) * scale;   // d
-          const float b0 = elu1(bf16_lo(hw[j])) * scale, b1 = elu1(bf16_hi(hw[j])) * scale;   // d + 32
+          const float a0 = elu1(bf16_lo(lw[j])), a1 = elu1(bf16_hi(lw[j]));   // d
+          const float b0 = elu1(bf16_lo(hw[j])), b1 = elu1(bf16_hi(hw[j]));   // d + 32
           // x*cos + rotate_half(x)*sin:  out[d] = x[d]cos - x[d+32]sin,  out[d+32] = x[d+32]cos + x[d]sin
           ol[j] = pack_bf16x2(a0 * cs[2 * j] - b0 * sn[2 * j], a1 * cs[2 * j + 1] - b1 * sn[2 * j + 1]);
           oh[j] = pack_bf16x2(b0 * cs[2 * j] + a0 * sn[2 * j], b1 * cs[2 * j + 1] + a1 * sn[2 * j + 1]);
@@ -272,7 +273,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int ks = 0; ks < 4; ++ks) mma16816(O[nt], qf[ks], bfr[2 * ks], bfr[2 * ks + 1]);
     }
     {
-      const float g_lo = sm->pw[min(i_lo + 1, CH)], g_hi = sm->pw[min(i_hi + 1, CH)];
+      const float g_lo = 0.125f * sm->pw[min(i_lo + 1, CH)], g_hi = 0.125f * sm->pw[min(i_hi + 1, CH)];
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) { O[nt][0] *= g_lo; O[nt][1] *= g_lo; O[nt][2] *= g_hi; O[nt][3] *= g_hi; }
     }
