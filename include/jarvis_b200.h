@@ -35,6 +35,8 @@ extern "C" {
 #define JB200_EPI_GELU_BF16 1 /* out bf16 [M][N]  = gelu_erf(alpha * acc)             */
 #define JB200_EPI_RESID_F32 2 /* out f32  [M][N] += alpha * acc   (residual stream)   */
 #define JB200_EPI_F32 3       /* out f32  [M][N]  = alpha * acc                       */
+#define JB200_EPI_QK_ROPE_BF16 4 /* jb200_qkv_linear_rope only: bf16 out, attention prologue on the q/k heads */
+#define JB200_ATTN_QK_PREPARED 1 /* jb200_attn_scan flag: q, k come from jb200_qkv_linear_rope */
 #define JB200_TILE_CTA_PAIR 0x1000 /* flag added to token_tile: run on CTA pairs (tcgen05 cta_group::2) */
 
 /* device status codes (0 = no bounded wait ever ran out) */
@@ -108,6 +110,21 @@ int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, v
 int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
                          int N, int epilogue, void* out, int token_tile, int w_layout, void* stream);
 
+/* The q/k/v projection fused with the prologue of the attention scan: as jb200_ternary_linear with a bf16
+ * output, but out-features [0, rope_feats) (the q and k heads, 64 features each) come out as
+ *   phi(x) = ELU(x) + 1, then half-split RoPE at position pos0[row / T] + row % T
+ * (AssociativeLinearAttention.forward, jarvis_engine/jarvis_model.py:124-128; apply_rotary_emb :29-71; fused kernel
+ * A1, associative_attention_cuda/associative_attention_cuda.cu:28-112), computed in f32 on the accumulator and
+ * rounded to bf16 once.  The caller must have INTERLEAVED the weight rows of every q/k head: row 2i of a head
+ * holds the head's feature i, row 2i+1 its feature i + 32 (i < 32); the output keeps that order, which
+ * jb200_attn_scan reads with JB200_ATTN_QK_PREPARED.  The queries' 1/sqrt(64) is applied by the scan.
+ * cos_tab / sin_tab: f32 [n_pos][32]; pos0: int32 [M / T] or NULL (then pos0_scalar); positions are clamped
+ * to the table.  M % T == 0. */
+int jb200_qkv_linear_rope(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
+                          int N, int rope_feats, const float* cos_tab, const float* sin_tab, int n_pos,
+                          const int32_t* pos0, int pos0_scalar, int T, void* out, int token_tile, int w_layout,
+                          void* stream);
+
 /* One-time re-encoding of canonical packed weights for the GEMM's fast decode: still 2 bits per
  * weight and the same byte count; inside each aligned group of 16 in-features (one 32-bit word) the
  * even in-features move to the low half-word and the odd ones to the high half-word, each stored as
@@ -150,12 +167,16 @@ int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* ou
  * o: bf16 rows [B*T] with stride ld_o.  head_dim must be 64.
  * scratch: jb200_attn_scan_scratch_bytes(B, T, H) bytes (8-byte aligned) or NULL.  With scratch, long
  *   sequences are cut into segments that run in parallel (a first launch computes each segment's state
- *   contribution from k and v); with NULL every (sequence, head) is walked by one CTA. */
+ *   contribution from k and v); with NULL every (sequence, head) is walked by one CTA.
+ * flags: 0, or JB200_ATTN_QK_PREPARED when q and k were produced by jb200_qkv_linear_rope (feature map and
+ * RoPE already applied, head dim interleaved): the scan then skips its own prologue; s_in / s_out keep the
+ * natural (B, H, D_v, D_k) order either way.  T == 1 (decode step) takes raw q, k only.
+ */
 size_t jb200_attn_scan_scratch_bytes(int B, int T, int H);
 int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                     const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
                     const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
-                    int head_dim, void* stream);
+                    int head_dim, int flags, void* stream);
 
 /* ---- MoE routing ---------------------------------------------------------------------- */
 

@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 6; }
+int jb200_abi_version(void) { return 7; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -154,6 +154,15 @@ int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* pac
                              static_cast<cudaStream_t>(stream));
 }
 
+int jb200_qkv_linear_rope(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
+                          int N, int rope_feats, const float* cos_tab, const float* sin_tab, int n_pos,
+                          const int32_t* pos0, int pos0_scalar, int T, void* out, int token_tile, int w_layout,
+                          void* stream) {
+  GemmRope r{cos_tab, sin_tab, pos0, pos0_scalar, n_pos, T, rope_feats};
+  return launch_ternary_gemm(x, M, K, packed, alpha, alpha_rows, N, 1, nullptr, JB200_EPI_QK_ROPE_BF16, out, token_tile,
+                             w_layout, static_cast<cudaStream_t>(stream), &r);
+}
+
 int jb200_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,
                  float top_p, const float* u, int64_t* out_token, float* out_prob, void* stream) {
   return launch_sample(logits, logits_dtype, ld, n_rows, V, temperature, top_k, top_p, u, out_token, out_prob,
@@ -172,9 +181,9 @@ int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* ou
 int jb200_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                     const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
                     const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
-                    int head_dim, void* stream) {
+                    int head_dim, int flags, void* stream) {
   return launch_attn_scan(q, k, v, ld_qkv, gamma, cos_tab, sin_tab, n_pos, pos0, pos0_scalar, s_in, o, ld_o, s_out,
-                          scratch, B, T, H, head_dim, static_cast<cudaStream_t>(stream));
+                          scratch, B, T, H, head_dim, flags, static_cast<cudaStream_t>(stream));
 }
 
 size_t jb200_attn_scan_scratch_bytes(int B, int T, int H) { return attn_scan_scratch_bytes(B, T, H); }

@@ -55,6 +55,7 @@ struct AttnParams {
   int seg_chunks;          // chunks per sequence segment (grid.z walks the segments)
   int nseg;
   float* seg_state;        // [B][H][nseg-1][64][64]: state contribution of each non-final segment
+  int qk_prepared;         // q, k already hold phi(.) + RoPE with the head dim interleaved (d, d+32 adjacent)
   unsigned int* status;
 };
 
@@ -142,7 +143,13 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       const int c = nt * 8 + cb;
-      if (sin_p) {
+      if (sin_p && p.qk_prepared) {
+        // the kernel's dk axis is the interleaved one (column 2i = feature i, 2i + 1 = feature i + 32);
+        // states cross the API in the natural order
+        const int d = c >> 1;
+        S[nt][0] = __ldg(sin_p + r * D + d);        S[nt][1] = __ldg(sin_p + r * D + d + 32);
+        S[nt][2] = __ldg(sin_p + (r + 8) * D + d);  S[nt][3] = __ldg(sin_p + (r + 8) * D + d + 32);
+      } else if (sin_p) {
         const float2 lo = __ldg(reinterpret_cast<const float2*>(sin_p + r * D + c));
         const float2 hi = __ldg(reinterpret_cast<const float2*>(sin_p + (r + 8) * D + c));
         S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
@@ -203,7 +210,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     // ---- prologue: feature map + RoPE on q and k (pairs d, d+32), Vw = v * gamma^(c-1-j) ----------
     // 64 rows x 4 column groups of 8; 2 items per thread
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
+    for (int it = 0; it < (p.qk_prepared ? 0 : 2); ++it) {
       const int item = tid + it * ATTN_THREADS;
       const int r = item >> 2, cg = item & 3;   // token row, 16-byte chunk in the first half
       int pos = pos_base + ck * CH + r;
@@ -382,11 +389,18 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   if (ok && so) {
     const int r = 16 * warp + (lane >> 2);
     const int cb = 2 * (lane & 3);
+    const bool natural = !STATE_ONLY && p.qk_prepared;   // segment contributions stay in the kernel's own order
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
       const int c = nt * 8 + cb;
-      *reinterpret_cast<float2*>(so + r * D + c) = make_float2(S[nt][0], S[nt][1]);
-      *reinterpret_cast<float2*>(so + (r + 8) * D + c) = make_float2(S[nt][2], S[nt][3]);
+      if (natural) {
+        const int d = c >> 1;
+        so[r * D + d] = S[nt][0];        so[r * D + d + 32] = S[nt][1];
+        so[(r + 8) * D + d] = S[nt][2];  so[(r + 8) * D + d + 32] = S[nt][3];
+      } else {
+        *reinterpret_cast<float2*>(so + r * D + c) = make_float2(S[nt][0], S[nt][1]);
+        *reinterpret_cast<float2*>(so + (r + 8) * D + c) = make_float2(S[nt][2], S[nt][3]);
+      }
     }
   }
 }
@@ -492,7 +506,9 @@ size_t attn_scan_scratch_bytes(int B, int T, int H) {
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
                      const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
-                     int head_dim, cudaStream_t stream) {
+                     int head_dim, int flags, cudaStream_t stream) {
+  JB_REQUIRE((flags & ~JB200_ATTN_QK_PREPARED) == 0, "attn_scan: unknown flags %d", flags);
+  JB_REQUIRE(!(flags & JB200_ATTN_QK_PREPARED) || T > 1, "attn_scan: prepared q/k is for T > 1 (single-token steps take raw q, k)");
   JB_REQUIRE(head_dim == D, "attn_scan: head_dim (%d) must be %d", head_dim, D);
   JB_REQUIRE(B >= 0 && T >= 0 && H > 0, "attn_scan: bad shape (B=%d, T=%d, H=%d)", B, T, H);
   JB_REQUIRE(B <= 65535, "attn_scan: batch (%d) exceeds 65535", B);
@@ -513,7 +529,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
     AttnParams dp;
     dp.gamma = gamma; dp.cos_tab = cos_tab; dp.sin_tab = sin_tab; dp.pos0 = pos0; dp.pos0_scalar = pos0_scalar;
     dp.n_pos = n_pos; dp.s_in = s_in; dp.s_out = s_out; dp.o = reinterpret_cast<__nv_bfloat16*>(o); dp.ld_o = ld_o;
-    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.status = nullptr;
+    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.qk_prepared = 0; dp.status = nullptr;
     attn_decode_kernel<<<dim3(H, B), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q),
                                                         reinterpret_cast<const __nv_bfloat16*>(k),
                                                         reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
@@ -529,6 +545,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.gamma = gamma; p.cos_tab = cos_tab; p.sin_tab = sin_tab; p.pos0 = pos0; p.pos0_scalar = pos0_scalar;
   p.n_pos = n_pos; p.s_in = s_in; p.s_out = s_out; p.o = reinterpret_cast<__nv_bfloat16*>(o); p.ld_o = ld_o;
   p.B = B; p.T = T; p.H = H;
+  p.qk_prepared = (flags & JB200_ATTN_QK_PREPARED) ? 1 : 0;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
   const int sms = sm_count();

@@ -85,6 +85,12 @@ struct GemmParams {
   int epilogue;
   int w_layout;              // 0 canonical weight_packing.py layout, 1 prepared layout
   unsigned int* status;
+  // JB200_EPI_QK_ROPE_BF16 only: attention feature map + rotary embedding applied to out-features < rope_feats
+  const float* cos_tab;      // [n_pos][32]
+  const float* sin_tab;      // [n_pos][32]
+  const int32_t* pos0;       // [rows / T] first position of every sequence, or null (pos0_scalar)
+  int pos0_scalar, n_pos, T;
+  int rope_feats;            // out-features [0, rope_feats) are q and k heads (64 features each), the rest plain
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -126,7 +132,43 @@ __device__ __forceinline__ void prefetch_residual_rows(const GemmParams& p, int 
 __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t taddr, float alpha, size_t row0, int f0,
                                                 int ntok, int lane) {
   uint32_t v[32];
-  if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16) {
+  if (p.epilogue == JB200_EPI_QK_ROPE_BF16 && f0 < p.rope_feats) {
+    // q / k heads whose weight rows were interleaved so that features d and d + 32 of a head are neighbouring
+    // out-features (2i, 2i + 1): the lane pair that already swaps values for the bf16x2 store holds exactly
+    // the two RoPE partners.  phi(x) = ELU(x) + 1 in f32 on the accumulator, then
+    //   out[d] = phi(x[d]) cos - phi(x[d+32]) sin,   out[d+32] = phi(x[d+32]) cos + phi(x[d]) sin
+    // (jarvis_model.py:124-128, :29-71), rounded to bf16 once.  The 1/sqrt(D) of the queries is left to the
+    // attention kernel's score factors (a power of two: same bits).
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    const int odd = lane & 1;
+    const int pair = ((f0 & 32) >> 1) + (lane >> 1);              // rotary pair index i of this lane pair, 0..31
+    const int row_first = int(row0) + odd;                        // this lane's tokens: row_first + 2 jj
+    const int n_seq = p.M / p.T;
+    int seq = row_first / p.T;
+    int t = row_first - seq * p.T;
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + size_t(odd)) * p.N + f0 + (lane & ~1);
+    const size_t step = size_t(p.N) * 2;
+#pragma unroll
+    for (int jj = 0; jj < 16; ++jj) {
+      int pos = (p.pos0 ? __ldg(p.pos0 + min(seq, n_seq - 1)) : p.pos0_scalar) + t;   // rows past M are not stored
+      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+      const float cs = __ldg(p.cos_tab + size_t(pos) * 32 + pair), sn = __ldg(p.sin_tab + size_t(pos) * 32 + pair);
+      float a = alpha * __uint_as_float(v[2 * jj]);       // token 2jj:     x[d] on even lanes, x[d+32] on odd lanes
+      float b = alpha * __uint_as_float(v[2 * jj + 1]);   // token 2jj + 1
+      a = a > 0.f ? a + 1.0f : __expf(a);
+      b = b > 0.f ? b + 1.0f : __expf(b);
+      // even lanes finish token 2jj (they need the partner's a), odd lanes token 2jj + 1 (the partner's b)
+      const float got = __shfl_xor_sync(0xffffffffu, odd ? a : b, 1);
+      const float lo = odd ? got : a;      // phi(x[d])
+      const float hi = odd ? b : got;      // phi(x[d+32])
+      const uint32_t w2 = pack_bf16x2(lo * cs - hi * sn, hi * cs + lo * sn);
+      if (2 * jj + odd < ntok) *reinterpret_cast<uint32_t*>(o) = w2;
+      o += step;
+      t += 2;
+      while (t >= p.T) { t -= p.T; ++seq; }   // next sequence of the batch
+    }
+  } else if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16 || p.epilogue == JB200_EPI_QK_ROPE_BF16) {
     const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;
     tmem_ld_32x32(taddr, v);
     tmem_ld_wait();

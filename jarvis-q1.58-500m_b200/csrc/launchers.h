@@ -13,9 +13,16 @@ int launch_pack_ternary(const float* w, int out_features, int in_features, const
 int launch_pack_codes(const float* w_ternary, size_t n_elems, uint8_t* packed, cudaStream_t stream);
 int launch_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, void* out, cudaStream_t stream);
 
+// Extra arguments of the JB200_EPI_QK_ROPE_BF16 epilogue (q/k/v projection fused with the attention prologue).
+struct GemmRope {
+  const float* cos_tab;   // [n_pos][32]
+  const float* sin_tab;
+  const int32_t* pos0;    // [M / T] or null
+  int pos0_scalar, n_pos, T, rope_feats;
+};
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
-                        int bn_override, int w_layout, cudaStream_t stream);
+                        int bn_override, int w_layout, cudaStream_t stream, const GemmRope* rope = nullptr);
 int launch_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, cudaStream_t stream);
 void decode16_host(uint32_t w, uint32_t* out8);
 void decode16_prepared_host(uint32_t w_canonical, uint32_t* out8);
@@ -53,7 +60,7 @@ size_t lsf_scan_scratch_bytes(int B, int T, int D);
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,
                      const float* s_in, void* o, int ld_o, float* s_out, void* scratch, int B, int T, int H,
-                     int head_dim, cudaStream_t stream);
+                     int head_dim, int flags, cudaStream_t stream);
 size_t attn_scan_scratch_bytes(int B, int T, int H);
 
 int launch_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,

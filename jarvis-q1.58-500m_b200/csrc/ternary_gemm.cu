@@ -38,6 +38,7 @@
 // instruction count of the decode is what sets the tensor-pipe utilisation.
 #include "common.cuh"
 #include "gemm_shared.cuh"
+#include "launchers.h"
 
 namespace jb {
 
@@ -284,7 +285,7 @@ int launch_ternary_gemm_pair(const void* x_bf16, const GemmParams& p, cudaStream
 
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
-                        int bn_override, int w_layout, cudaStream_t stream) {
+                        int bn_override, int w_layout, cudaStream_t stream, const GemmRope* rope) {
   JB_REQUIRE(M >= 0 && N > 0 && K > 0, "ternary_linear: bad sizes M=%d N=%d K=%d", M, N, K);
   JB_REQUIRE(N % BM == 0, "ternary_linear: out_features (%d) must be a multiple of %d", N, BM);
   JB_REQUIRE(K % BK == 0, "ternary_linear: in_features (%d) must be a multiple of %d", K, BK);
@@ -292,7 +293,15 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   JB_REQUIRE(G == 1 || seg_offsets != nullptr, "ternary_linear: grouped call needs segment offsets");
   JB_REQUIRE(alpha_rows > 0 && alpha_rows % BM == 0 && N % alpha_rows == 0,
              "ternary_linear: alpha_rows (%d) must be a multiple of %d dividing out_features", alpha_rows, BM);
-  JB_REQUIRE(epilogue >= JB200_EPI_BF16 && epilogue <= JB200_EPI_F32, "ternary_linear: unknown epilogue %d", epilogue);
+  JB_REQUIRE(epilogue >= JB200_EPI_BF16 && epilogue <= JB200_EPI_QK_ROPE_BF16, "ternary_linear: unknown epilogue %d", epilogue);
+  JB_REQUIRE((epilogue == JB200_EPI_QK_ROPE_BF16) == (rope != nullptr), "ternary_linear: the q/k RoPE epilogue needs its tables (use jb200_qkv_linear_rope)");
+  if (rope) {
+    JB_REQUIRE(G == 1, "qkv_linear_rope: no grouped form");
+    JB_REQUIRE(rope->cos_tab && rope->sin_tab && rope->n_pos >= 1, "qkv_linear_rope: RoPE tables missing");
+    JB_REQUIRE(rope->T >= 1 && M % rope->T == 0, "qkv_linear_rope: rows (%d) must be a multiple of the sequence length (%d)", M, rope->T);
+    JB_REQUIRE(rope->rope_feats >= 0 && rope->rope_feats <= N && rope->rope_feats % 64 == 0,
+               "qkv_linear_rope: rotated features (%d) must be whole 64-wide heads within out_features", rope->rope_feats);
+  }
   JB_REQUIRE(w_layout == 0 || w_layout == 1, "ternary_linear: weight layout must be 0 (canonical) or 1 (prepared)");
   JB_REQUIRE(x_bf16 && w_packed && alpha && out, "ternary_linear: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_packed) && aligned16(out), "ternary_linear: pointers must be 16-byte aligned");
@@ -319,6 +328,13 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   p.bn = bn;
   p.epilogue = epilogue;
   p.w_layout = w_layout;
+  p.cos_tab = rope ? rope->cos_tab : nullptr;
+  p.sin_tab = rope ? rope->sin_tab : nullptr;
+  p.pos0 = rope ? rope->pos0 : nullptr;
+  p.pos0_scalar = rope ? rope->pos0_scalar : 0;
+  p.n_pos = rope ? rope->n_pos : 0;
+  p.T = rope ? rope->T : 1;
+  p.rope_feats = rope ? rope->rope_feats : 0;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
   if (pair_bn) return launch_ternary_gemm_pair(x_bf16, p, stream);

@@ -149,23 +149,42 @@ class AssociativeLinearAttention(nn.Module):
         self.register_buffer("_i_idx_p1", i + 1)
         self.register_buffer("_c_m1_m_i", (cs - 1) - i)
         self._qkv = _PackCache()
+        self._qkv_rope = None      # (key, prepared packed q|k|v with the q/k head rows interleaved) for the fused prologue
+        self.fuse_prologue = True  # T > 1: feature map + RoPE in the q/k/v GEMM's epilogue instead of the scan
         self._gamma = None
         self.max_position = None   # optional upper bound of per-sequence start positions (avoids a sync)
 
     def qkv_packed(self):
         return self._qkv.get([self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], stack=False)
 
+    def qkv_packed_interleaved(self):
+        """q|k|v in the prepared layout with the rows of every q and k head interleaved (feature i next to
+        feature i + 32), the order ops.qkv_linear_rope works on."""
+        self.qkv_packed()
+        if self._qkv_rope is None or self._qkv_rope[0] is not self._qkv.canonical:
+            canon, C = self._qkv.canonical, self.q_proj.weight.shape[0]
+            rows = torch.cat([ops.interleave_head_rows(canon[:C], self.n_heads),
+                              ops.interleave_head_rows(canon[C:2 * C], self.n_heads), canon[2 * C:]])
+            self._qkv_rope = (canon, ops.prepare_weights(rows))
+        return self._qkv_rope[1], self._qkv.alpha
+
     def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False, inplace_state=False):
         """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None)."""
         C = xn_rows.shape[1]
-        packed, alpha = self.qkv_packed()
-        qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C, prepared=True)
+        fused = self.fuse_prologue and T > 1
+        if not fused:
+            packed, alpha = self.qkv_packed()
+            qkv = ops.ternary_linear(xn_rows, packed, alpha, alpha_rows=C, prepared=True)
         if torch.is_tensor(start_pos):
             # per-sequence positions: size the table from the caller's bound when given (no host sync)
             end = (self.max_position if self.max_position is not None else int(start_pos.max())) + T
         else:
             end = int(start_pos) + T
         cos, sin = self.rotary.half_tables(end, xn_rows.device)
+        if fused:
+            packed, alpha = self.qkv_packed_interleaved()
+            qkv = ops.qkv_linear_rope(xn_rows, packed, alpha, cos, sin, T, 2 * C, start_pos=start_pos, alpha_rows=C,
+                                      prepared=True)
         gkey = (self.gamma_raw.data_ptr(), self.gamma_raw._version)
         if self._gamma is None or self._gamma[0] != gkey:
             self._gamma = (gkey, torch.sigmoid(self.gamma_raw.detach().float()))
@@ -174,7 +193,7 @@ class AssociativeLinearAttention(nn.Module):
             h_prev = h_prev.to(torch.float32).contiguous()
         return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
                              start_pos=start_pos, state_in=h_prev, want_state=want_state,
-                             state_out=h_prev if (inplace_state and h_prev is not None) else None)
+                             state_out=h_prev if (inplace_state and h_prev is not None) else None, qk_prepared=fused)
 
     def forward_with_state(self, x, start_pos=0, h_prev=None):
         B, T, C = x.shape

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32, TILE_CTA_PAIR  # noqa: F401
+from ._lib import ATTN_QK_PREPARED, EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32, TILE_CTA_PAIR  # noqa: F401
 
 
 def _stream() -> int:
@@ -152,6 +152,56 @@ def ternary_linear_grouped(x: torch.Tensor, packed: torch.Tensor, alpha: torch.T
     return out
 
 
+def interleave_head_rows(packed_rows: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """Row permutation qkv_linear_rope expects for a q or k projection: inside every 64-row head, new row 2i is
+    old row i and new row 2i + 1 is old row i + 32 (RoPE partners become neighbouring out-features).
+    packed_rows: (n_heads * 64, ...) any dtype (applied to the PACKED rows, before prepare_weights)."""
+    idx = torch.arange(64, device=packed_rows.device)
+    src = (idx >> 1) + 32 * (idx & 1)
+    full = (torch.arange(n_heads, device=packed_rows.device).view(-1, 1) * 64 + src.view(1, -1)).reshape(-1)
+    return packed_rows.index_select(0, full).contiguous()
+
+
+def qkv_linear_rope(x: torch.Tensor, packed: torch.Tensor, alpha: torch.Tensor, cos_tab: torch.Tensor,
+                    sin_tab: torch.Tensor, T: int, rope_feats: int, *, start_pos=0, alpha_rows: int | None = None,
+                    out: torch.Tensor | None = None, token_tile: int = 0, prepared: bool = False):
+    """The fused q|k|v projection with the attention prologue in its epilogue: out-features [0, rope_feats)
+    (q and k heads, rows interleaved with interleave_head_rows) get ELU+1 and RoPE at position
+    start_pos[row // T] + row % T; the rest (v) is the plain bf16 output.  -> bf16 (M, N)."""
+    lib = _lib.load()
+    _need(x, torch.bfloat16, "qkv_linear_rope.x")
+    _need(packed, torch.uint8, "qkv_linear_rope.packed")
+    _need(alpha, torch.float32, "qkv_linear_rope.alpha")
+    _need(cos_tab, torch.float32, "qkv_linear_rope.cos_tab")
+    _need(sin_tab, torch.float32, "qkv_linear_rope.sin_tab")
+    M, K = x.shape
+    N = packed.shape[0]
+    if packed.shape[1] * 4 != K:
+        raise RuntimeError(f"qkv_linear_rope: packed weight has K={packed.shape[1] * 4}, x has K={K}")
+    if cos_tab.shape[1] != 32 or sin_tab.shape != cos_tab.shape:
+        raise RuntimeError("qkv_linear_rope: RoPE tables must be (n_pos, 32)")
+    if alpha_rows is None:
+        alpha_rows = N // alpha.numel()
+    pos_t, pos_s = None, 0
+    if torch.is_tensor(start_pos):
+        pos_t = _need(start_pos, torch.int32, "qkv_linear_rope.start_pos")
+        if pos_t.numel() * T != M:
+            raise RuntimeError("qkv_linear_rope: one start position per sequence is needed")
+    else:
+        pos_s = int(start_pos)
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+    else:
+        _need(out, torch.bfloat16, "qkv_linear_rope.out")
+    _lib.check(
+        lib.jb200_qkv_linear_rope(_ptr(x), M, K, _ptr(packed), _ptr(alpha), alpha_rows, N, rope_feats, _ptr(cos_tab),
+                                  _ptr(sin_tab), cos_tab.shape[0], _ptr(pos_t), pos_s, T, _ptr(out), token_tile,
+                                  1 if prepared else 0, _stream()),
+        "jb200_qkv_linear_rope",
+    )
+    return out
+
+
 def selftest_bounded_wait(limit_ms: int = 50) -> int:
     """Runs the wait-that-must-give-up kernel and returns the device status it left."""
     lib = _lib.load()
@@ -197,8 +247,9 @@ def embedding(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, cos_tab: torch.Tensor,
               sin_tab: torch.Tensor, B: int, T: int, H: int, *, start_pos=0, state_in: torch.Tensor | None = None,
               want_state: bool = False, out: torch.Tensor | None = None, segmented: bool = True,
-              state_out: torch.Tensor | None = None):
-    """Feature map + RoPE + decayed causal scan.  q, k, v: bf16 2-D views (B*T, H*64) sharing one
+              state_out: torch.Tensor | None = None, qk_prepared: bool = False):
+    """Feature map + RoPE + decayed causal scan (qk_prepared=True: q and k come from qkv_linear_rope, the
+    scan skips its prologue).  q, k, v: bf16 2-D views (B*T, H*64) sharing one
     row stride (e.g. column slices of a fused q|k|v matrix).  start_pos: int, or int32 (B,) tensor of
     per-sequence first positions.  Returns (o bf16 (B*T, H*64), final state f32 (B,H,64,64) or None)."""
     lib = _lib.load()
@@ -240,7 +291,7 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
     _lib.check(
         lib.jb200_attn_scan(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(gamma), _ptr(cos_tab), _ptr(sin_tab), cos_tab.shape[0],
                             _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0), _ptr(s_out), _ptr(scratch),
-                            B, T, H, 64, _stream()),
+                            B, T, H, 64, ATTN_QK_PREPARED if qk_prepared else 0, _stream()),
         "jb200_attn_scan",
     )
     return out, s_out

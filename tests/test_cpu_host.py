@@ -21,7 +21,7 @@ def test_library_exports_every_declared_symbol():
     assert set(declared) == set(_lib.PROTOTYPES)
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.jb200_abi_version() >= 4
+    assert lib.jb200_abi_version() >= 7
     assert lib.jb200_moe_metadata_static_max_assignments() == 262144
 
 
@@ -32,7 +32,7 @@ def test_argument_errors_need_no_gpu():
     rc = lib.jb200_pack_ternary(None, 4, 6, None, None, None, None, None)
     assert rc == _lib.ERR_ARG and "divisible by 4" in _lib.last_error()
     rc = lib.jb200_attn_scan(None, None, None, 64, None, None, None, 1, None, 0, None, None, 64, None, None, 1, 1, 1,
-                             32, None)
+                             32, 0, None)
     assert rc == _lib.ERR_ARG and "head_dim" in _lib.last_error()
     rc = lib.jb200_lsf_scan(None, 0, None, None, None, None, 0.1, 0.99, None, None, None, 0, None, None, 1, 1, 3, None)
     assert rc == _lib.ERR_ARG and "even" in _lib.last_error()

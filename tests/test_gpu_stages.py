@@ -408,3 +408,86 @@ def test_dispatch_round_trip_at_moe_bench_size():
     gates = torch.tensor([[1.0, 0.0]], device="cuda").repeat(N, 1)
     back = ops.scatter_combine(disp, gates, scatter)
     assert torch.equal(back, x)
+
+
+# ------------------------------------------------------------------ fused prologue (q/k/v GEMM epilogue + prepared scan)
+def _fused_case(B, H, T, seed, start_pos=0, with_state=False):
+    """x -> q|k|v projection with the attention prologue in its epilogue -> scan with prepared q/k, against the
+    oracle's projection + feature map + RoPE + recurrent scan."""
+    g = torch.Generator().manual_seed(seed)
+    C = H * 64
+    x = (torch.randn(B * T, C, generator=g) * 0.5).bfloat16()
+    qs = [torch.randint(-1, 2, (C, C), generator=g).float() for _ in range(3)]
+    alphas = torch.tensor([0.05, 0.04, 0.06])
+    gamma = torch.rand(H, generator=g) * 0.099 + 0.9
+    S0 = torch.randn(B, H, 64, 64, generator=g) if with_state else None
+    per_seq = torch.is_tensor(start_pos)
+    proj = [a * (x.float() @ w.t()) for a, w in zip(alphas, qs)]
+
+    def heads(t):
+        return t.view(B, T, H, 64).transpose(1, 2)
+
+    o_ref = torch.empty(B, H, T, 64, dtype=torch.float64)
+    S_ref = torch.empty(B, H, 64, 64, dtype=torch.float64)
+    qk_ref = []
+    for b in range(B):
+        sp = int(start_pos[b]) if per_seq else start_pos
+        qf, kf = orc.feature_map_rope(heads(proj[0])[b:b + 1], heads(proj[1])[b:b + 1], sp)
+        qk_ref.append((qf, kf))
+        o_ref[b:b + 1], S_ref[b:b + 1] = orc.attn_scan_recurrent(qf, kf, heads(proj[2])[b:b + 1], gamma,
+                                                                 None if S0 is None else S0[b:b + 1])
+    n_pos = (int(start_pos.max()) if per_seq else start_pos) + T
+    cos, sin = rope_tabs(n_pos)
+    canon = [orc.pack_ternary(w).cuda() for w in qs]
+    rows = torch.cat([ops.interleave_head_rows(canon[0], H), ops.interleave_head_rows(canon[1], H), canon[2]])
+    sp_dev = start_pos.cuda() if per_seq else start_pos
+    outs = []
+    for prepared in (False, True):
+        pk = ops.prepare_weights(rows) if prepared else rows
+        qkv = ops.qkv_linear_rope(x.cuda(), pk, alphas.cuda(), cos, sin, T, 2 * C, start_pos=sp_dev, alpha_rows=C,
+                                  prepared=prepared)
+        outs.append(qkv)
+    assert torch.equal(outs[0], outs[1])
+    qkv = outs[1]
+    # the epilogue's q', k' (undo the head-dim interleave; q' is stored without the 1/8)
+    un = torch.empty(64, dtype=torch.long)
+    un[torch.arange(32)] = 2 * torch.arange(32)
+    un[32 + torch.arange(32)] = 2 * torch.arange(32) + 1
+    qp = qkv[:, :C].float().cpu().view(B, T, H, 64)[..., un].transpose(1, 2) * 0.125
+    kp = qkv[:, C:2 * C].float().cpu().view(B, T, H, 64)[..., un].transpose(1, 2)
+    q_want = torch.cat([a for a, _ in qk_ref]); k_want = torch.cat([b for _, b in qk_ref])
+    assert rel_l2(qp, q_want) <= 4e-3 and rel_l2(kp, k_want) <= 4e-3          # one bf16 rounding
+    assert rel_l2(qkv[:, 2 * C:].float().cpu(), proj[2]) <= 4e-3
+    o, S = ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma.cuda(), cos, sin, B, T, H, start_pos=sp_dev,
+                         state_in=None if S0 is None else S0.cuda(), want_state=True, qk_prepared=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    o = o.float().cpu().view(B, T, H, 64).transpose(1, 2)
+    return rel_l2(o, o_ref), rel_l2(S, S_ref)
+
+
+@pytest.mark.parametrize("T", [2, 17, 64, 65, 289, 1000])
+def test_fused_prologue_lengths(T):
+    eo, es = _fused_case(2, 2, T, seed=T)
+    assert eo <= 1e-2 and es <= 1e-2
+
+
+def test_fused_prologue_state_positions_and_segments():
+    eo, es = _fused_case(2, 4, 130, seed=5, start_pos=torch.tensor([7, 300], dtype=torch.int32), with_state=True)
+    assert eo <= 1e-2 and es <= 1e-2
+    eo, es = _fused_case(1, 2, 2048, seed=6, start_pos=11, with_state=True)      # cut into segments
+    assert eo <= 1e-2 and es <= 1e-2
+    eo, es = _fused_case(3, 2, 48, seed=7)      # 32-token epilogue chunks straddle sequence boundaries (T % 32 != 0)
+    assert eo <= 1e-2 and es <= 1e-2
+
+
+def test_fused_prologue_argument_errors():
+    x = torch.zeros(64, 128, dtype=torch.bfloat16, device="cuda")
+    pk = torch.zeros(384, 32, dtype=torch.uint8, device="cuda")
+    cos, sin = rope_tabs(64)
+    with pytest.raises(RuntimeError, match="multiple of the sequence length"):
+        ops.qkv_linear_rope(x, pk, torch.ones(3, device="cuda"), cos, sin, 48, 256, alpha_rows=128)
+    with pytest.raises(RuntimeError, match="whole 64-wide heads"):
+        ops.qkv_linear_rope(x, pk, torch.ones(3, device="cuda"), cos, sin, 32, 200, alpha_rows=128)
+    with pytest.raises(RuntimeError, match="needs its tables"):
+        ops.ternary_linear(x, pk, torch.ones(3, device="cuda"), epilogue=4, alpha_rows=128)
