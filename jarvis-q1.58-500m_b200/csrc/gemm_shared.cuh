@@ -139,21 +139,40 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t ta
     //   out[d] = phi(x[d]) cos - phi(x[d+32]) sin,   out[d+32] = phi(x[d+32]) cos + phi(x[d]) sin
     // (jarvis_model.py:124-128, :29-71), rounded to bf16 once.  The 1/sqrt(D) of the queries is left to the
     // attention kernel's score factors (a power of two: same bits).
-    tmem_ld_32x32(taddr, v);
-    tmem_ld_wait();
     const int odd = lane & 1;
     const int pair = ((f0 & 32) >> 1) + (lane >> 1);              // rotary pair index i of this lane pair, 0..31
-    const int row_first = int(row0) + odd;                        // this lane's tokens: row_first + 2 jj
     const int n_seq = p.M / p.T;
-    int seq = row_first / p.T;
-    int t = row_first - seq * p.T;
+    const int seq0 = int(row0) / p.T;                             // sequence and offset of the chunk's first row
+    const int t0 = int(row0) - seq0 * p.T;
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (row0 + size_t(odd)) * p.N + f0 + (lane & ~1);
     const size_t step = size_t(p.N) * 2;
+    const int base_pos = (p.pos0 ? __ldg(p.pos0 + min(seq0, n_seq - 1)) : p.pos0_scalar) + t0;
+    // Fast path (warp-uniform): the 32 rows lie in one sequence and inside the table.  The angle of pair i grows
+    // by the same amount from one position to the next, so only the lane's first (cos, sin) and the rotation by
+    // two positions (table row 2) are loaded, before the accumulator wait; the other 15 come from the angle
+    // addition formulas (error ~1e-6 after 15 steps, three orders below the bf16 rounding of the result).
+    const bool fast = t0 + 32 <= p.T && base_pos >= 0 && base_pos + 32 <= p.n_pos && p.n_pos > 2;
+    float cs = 1.f, sn = 0.f, c2 = 1.f, s2 = 0.f;
+    if (fast) {
+      cs = __ldg(p.cos_tab + size_t(base_pos + odd) * 32 + pair);
+      sn = __ldg(p.sin_tab + size_t(base_pos + odd) * 32 + pair);
+      c2 = __ldg(p.cos_tab + 2 * 32 + pair);
+      s2 = __ldg(p.sin_tab + 2 * 32 + pair);
+    }
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    int seq = seq0, t = t0 + odd;                                 // this lane's tokens: row0 + odd + 2 jj
+    while (t >= p.T) { t -= p.T; ++seq; }
 #pragma unroll
     for (int jj = 0; jj < 16; ++jj) {
-      int pos = (p.pos0 ? __ldg(p.pos0 + min(seq, n_seq - 1)) : p.pos0_scalar) + t;   // rows past M are not stored
-      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
-      const float cs = __ldg(p.cos_tab + size_t(pos) * 32 + pair), sn = __ldg(p.sin_tab + size_t(pos) * 32 + pair);
+      if (!fast) {
+        int pos = (p.pos0 ? __ldg(p.pos0 + min(seq, n_seq - 1)) : p.pos0_scalar) + t;   // rows past M are not stored
+        pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+        cs = __ldg(p.cos_tab + size_t(pos) * 32 + pair);
+        sn = __ldg(p.sin_tab + size_t(pos) * 32 + pair);
+        t += 2;
+        while (t >= p.T) { t -= p.T; ++seq; }   // next sequence of the batch
+      }
       float a = alpha * __uint_as_float(v[2 * jj]);       // token 2jj:     x[d] on even lanes, x[d+32] on odd lanes
       float b = alpha * __uint_as_float(v[2 * jj + 1]);   // token 2jj + 1
       a = a > 0.f ? a + 1.0f : __expf(a);
@@ -165,8 +184,11 @@ __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t ta
       const uint32_t w2 = pack_bf16x2(lo * cs - hi * sn, hi * cs + lo * sn);
       if (2 * jj + odd < ntok) *reinterpret_cast<uint32_t*>(o) = w2;
       o += step;
-      t += 2;
-      while (t >= p.T) { t -= p.T; ++seq; }   // next sequence of the batch
+      if (fast) {                           // advance the angle by two positions
+        const float cn = cs * c2 - sn * s2;
+        sn = sn * c2 + cs * s2;
+        cs = cn;
+      }
     }
   } else if (p.epilogue == JB200_EPI_BF16 || p.epilogue == JB200_EPI_GELU_BF16 || p.epilogue == JB200_EPI_QK_ROPE_BF16) {
     const bool gelu = p.epilogue == JB200_EPI_GELU_BF16;

@@ -150,7 +150,11 @@ class AssociativeLinearAttention(nn.Module):
         self.register_buffer("_c_m1_m_i", (cs - 1) - i)
         self._qkv = _PackCache()
         self._qkv_rope = None      # (key, prepared packed q|k|v with the q/k head rows interleaved) for the fused prologue
-        self.fuse_prologue = True  # T > 1: feature map + RoPE in the q/k/v GEMM's epilogue instead of the scan
+        # T > 1: run the feature map + RoPE in the q/k/v GEMM's epilogue instead of the scan.  Off by default: at
+        # B=8 x T=2048 the scan gets 32 us faster but the GEMM 43 us slower (its 8 epilogue warps have fewer
+        # issue slots for that arithmetic than the scan's 16 warps per SM); the fused form rounds q', k' once
+        # instead of twice, so it is the more accurate of the two.
+        self.fuse_prologue = False
         self._gamma = None
         self.max_position = None   # optional upper bound of per-sequence start positions (avoids a sync)
 

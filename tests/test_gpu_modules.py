@@ -60,6 +60,36 @@ def test_model_fixture_and_persistence():
     assert torch.isfinite(loss)
 
 
+def test_model_fixture_with_the_prologue_fused_into_the_projection():
+    """Same fixtures with the attention feature map + RoPE done by the q/k/v GEMM's epilogue (off by default)."""
+    g = load("model")
+    sd = {k[3:]: v for k, v in g.items() if k.startswith("sd_")}
+    model = jm.Jarvis(vocab_size=256, d_model=128, n_layers=2, n_heads=2, max_seq_len=256).eval()
+    model.load_state_dict(sd)
+    model = model.cuda()
+    for blk in model.blocks:
+        blk.attn.fuse_prologue = True
+    idx = g["idx"].cuda()
+    logits, _ = model(idx)
+    assert rel_l2(logits.float(), g["logits"]) <= 1.5e-2
+    model.reset_state()
+    la, _ = model(idx[:, :32], persist_state=True)
+    lb, _ = model(idx[:, 32:64], persist_state=True)          # start_pos = 32 goes through the epilogue's positions
+    assert rel_l2(la.float(), g["persist_logits_a"]) <= 1.5e-2
+    assert rel_l2(lb.float(), g["persist_logits_b"]) <= 1.5e-2
+    # state-carrying chunked prefill: the state leaves and re-enters the scan in the natural (D_v, D_k) order
+    a, st = model.step(idx[:, :64])
+    b, _ = model.step(idx[:, 64:], positions=64, state=st)
+    for blk in model.blocks:
+        blk.attn.fuse_prologue = False
+    a2, st2 = model.step(idx[:, :64])
+    b2, _ = model.step(idx[:, 64:], positions=64, state=st2)
+    assert rel_l2(a.float(), a2.float()) <= 1e-2 and rel_l2(b.float(), b2.float()) <= 1e-2
+    for x, y in zip(st["S"], st2["S"]):
+        assert rel_l2(x, y) <= 1e-2
+    assert _lib.device_status() == 0
+
+
 def test_ragged_state_carrying_decode_matches_oracle():
     """Prefill of ragged lengths is emulated by random carried states and per-sequence positions; then
     T=1 steps with the state handed from step to step, against the oracle stepped the same way."""
