@@ -172,9 +172,14 @@ class AssociativeLinearAttention(nn.Module):
             self._qkv_rope = (canon, ops.prepare_weights(rows))
         return self._qkv_rope[1], self._qkv.alpha
 
-    def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False, inplace_state=False):
-        """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None)."""
+    def scan_rows(self, xn_rows, B, T, start_pos=0, h_prev=None, want_state=False, inplace_state=False, cp=None):
+        """xn_rows: bf16 (B*T, C) normalised input -> (o bf16 (B*T, C), state or None).
+        cp: a parallel.ContextParallel when this rank holds one T-token slice of longer sequences
+        (start_pos is then the position of the SEQUENCE's first token; the returned state is the one after
+        the whole sequence)."""
         C = xn_rows.shape[1]
+        if cp is not None:
+            start_pos = start_pos + cp.rank * T
         fused = self.fuse_prologue and T > 1
         if not fused:
             packed, alpha = self.qkv_packed()
@@ -195,6 +200,11 @@ class AssociativeLinearAttention(nn.Module):
         gamma = self._gamma[1]
         if h_prev is not None:
             h_prev = h_prev.to(torch.float32).contiguous()
+        if cp is not None:
+            def scan(state_in):
+                return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
+                                     start_pos=start_pos, state_in=state_in, want_state=True, qk_prepared=fused)
+            return cp.attention(scan, gamma, T, h_prev)
         return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
                              start_pos=start_pos, state_in=h_prev, want_state=want_state,
                              state_out=h_prev if (inplace_state and h_prev is not None) else None, qk_prepared=fused)
@@ -386,12 +396,13 @@ class JarvisBlock(nn.Module):
         self.reflect = ReflectivePenalty()
 
     def forward_rows(self, x, B, T, h_prev=None, start_pos=0, attn_state=None, want_attn_state=False,
-                     inplace_state=False, scratch=None):
+                     inplace_state=False, scratch=None, cp=None):
         """x: f32 (B*T, C) residual stream, UPDATED IN PLACE.  Returns (h_last f32 (B, C), scalars f32
-        [l_balance, act_mean, act_var], attention state or None)."""
+        [l_balance, act_mean, act_var], attention state or None).  cp (parallel.ContextParallel): this rank
+        holds one T-token slice of every sequence; states returned are those after the whole sequence."""
         C = x.shape[1]
         xn = ops.rmsnorm(x, self.norm1.weight.detach().float(), self.norm1.eps)
-        o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state, inplace_state)
+        o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state, inplace_state, cp=cp)
         po, ao = self.attn.out_proj.packed()
         ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)          # x += attn(norm1(x))
         norm2 = (self.norm2.weight.detach().float(), self.norm2.eps)
@@ -399,6 +410,18 @@ class JarvisBlock(nn.Module):
             moe_out, scalars = self.moe.run_rows(x, norm=norm2)
         else:
             moe_out, scalars = self.moe.run_rows(x, acc=scratch[0], hist=scratch[1], scalars=scratch[2], norm=norm2)
+        if cp is not None:
+            # the decay of the call (one scalar, from the statistics of the WHOLE batch: moe.stats_group) in
+            # torch, for the weights of the slice-end sum; the scan kernel derives the same value itself
+            lq = self.liquid
+            alpha = lq.alpha_min + (lq.alpha_max - lq.alpha_min) * torch.sigmoid(-lq.var_scale.detach().float() * scalars[2])
+
+            def scan(h_in):
+                ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=lq.var_scale.detach().float().reshape(1),
+                             alpha_min=lq.alpha_min, alpha_max=lq.alpha_max, h0=h_in.contiguous(),
+                             resid=x.view(B, T, C), want_out=False)
+            _, h_last = cp.lsf(scan, moe_out.view(B, T, C), alpha, None if h_prev is None else h_prev.float())
+            return h_last, scalars, state
         _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],
                                  var_scale=self.liquid.var_scale.detach().float().reshape(1),
                                  alpha_min=self.liquid.alpha_min, alpha_max=self.liquid.alpha_max,
@@ -439,6 +462,7 @@ class Jarvis(nn.Module):
         self._attn_states: list = [None] * n_layers
         self._token_pos: int = 0
         self.carry_attention_state = False
+        self._cp = None
         self.logits_dtype = torch.bfloat16
         self._lm_head_bf16 = None
         self.last_aux = None
@@ -487,7 +511,7 @@ class Jarvis(nn.Module):
         x = ops.embedding(idx.contiguous(), self.tok_emb.weight.detach().float()).view(B * T, self.d_model)
         start_pos = self._token_pos if persist_state else 0
         if persist_state:
-            self._token_pos += T
+            self._token_pos += T * (self._cp.world if self._cp is not None else 1)
         h_prevs = self._h_states if persist_state else [None] * len(self.blocks)
         s_prevs = self._attn_states if (persist_state and self.carry_attention_state) else [None] * len(self.blocks)
         new_h, new_s, aux = [], [], []
@@ -500,7 +524,8 @@ class Jarvis(nn.Module):
             if s_prev is not None and s_prev.shape[0] != B:
                 s_prev = None
             h_last, sc, state = block.forward_rows(x, B, T, h_prev, start_pos, s_prev,
-                                                   want_attn_state=self.carry_attention_state, scratch=scratch[i])
+                                                   want_attn_state=self.carry_attention_state, scratch=scratch[i],
+                                                   cp=self._cp)
             new_h.append(h_last)
             new_s.append(state)
             aux.append(sc)
@@ -562,6 +587,15 @@ class Jarvis(nn.Module):
         for blk in self.blocks:
             blk.moe.stats_group = group
             blk.moe._n_total_hint = global_tokens
+
+    def set_context_parallel(self, group):
+        """Sequence parallelism of `forward` / `hidden_rows`: the ranks of `group` hold consecutive T-token slices
+        of the same sequences (rank r: tokens [r*T, (r+1)*T)).  Every layer all-gathers the slices' attention
+        and LSF end states (parallel.ContextParallel) and all-reduces its MoE statistics, so each rank's logits
+        are those of its slice in a single-GPU run over the whole sequence.  group=None switches it off."""
+        from . import parallel
+        self._cp = None if group is None else parallel.ContextParallel(group)
+        self.set_batch_split(group)
 
     def param_count(self):
         n = sum(p.numel() for p in self.parameters())

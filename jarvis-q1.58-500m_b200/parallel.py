@@ -1,4 +1,7 @@
-"""Expert-parallel execution of the top-2 MoE layer over the ranks of one node.
+"""Multi-GPU forms of the path: expert parallelism of the top-2 MoE layer and context (sequence) parallelism of
+the two scans, over the ranks of one node.
+
+Expert parallelism:
 
 The reference has no distributed code; this adds the one exchange the path has when the 4 experts
 live on different GPUs: an all-to-all of dispatched token rows before the expert FFN and its inverse
@@ -140,3 +143,81 @@ class ExpertParallelMoE:
                 y_disp[lo:hi] = back[pos:pos + hi - lo]
                 pos += hi - lo
         return self._combine(y_disp, gates, scatter_map, out_dtype), (idx, gates)
+
+
+class ContextParallel:
+    """Sequence (context) parallelism for the two recurrences of the block: rank r of the group holds tokens
+    [r * T_local, (r + 1) * T_local) of EVERY sequence of the batch.
+
+    Both scans are linear in their carried state, so a rank's slice can be scanned from a zero state, the
+    slices' end states combined across ranks, and the true incoming state fed to a second, final pass:
+
+      attention  S_out = gamma^T_local * S_in + D_r      (D_r: end state of slice r scanned from zero)
+      LSF        h_out = alpha^T_local * h_in + e_r      (e_r: end value of slice r scanned from zero)
+
+    One all-gather of D_r (B, H, 64, 64 f32) and one of e_r (B, C f32) per layer; every rank folds the
+    contributions of the ranks before it (the reference has no multi-GPU code; the combine is the one its
+    chunk-parallel attention path applies between chunks, jarvis_engine/jarvis_model.py:131-190).
+    The scans themselves are passed in, so the class runs with the CUDA kernels or with the CPU oracle."""
+
+    def __init__(self, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+
+    def _gather(self, t: torch.Tensor):
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return parts
+
+    def attention_states(self, delta: torch.Tensor, gamma: torch.Tensor, t_local: int, state0=None):
+        """delta: this rank's D_r (B, H, Dv, Dk); gamma: (H,) decays.  -> (state entering this rank's slice,
+        state after the last rank's slice); `state0` is the state before the first token of the sequence."""
+        parts = self._gather(delta.float())
+        g = gamma.float().to(delta.device).pow(float(t_local)).view(1, -1, 1, 1)
+        s = torch.zeros_like(parts[0]) if state0 is None else state0.float().clone()
+        s_in = None
+        for r, d in enumerate(parts):
+            if r == self.rank:
+                s_in = s.clone()
+            s = g * s + d
+        return s_in, s
+
+    def lsf_states(self, end: torch.Tensor, alpha, t_local: int, h0=None):
+        """end: this rank's e_r (B, C); alpha: scalar decay of the call.  -> (carry into this rank's slice,
+        membrane after the last rank's slice)."""
+        parts = self._gather(end.float())
+        a = torch.as_tensor(alpha, dtype=torch.float32, device=end.device).reshape(()).pow(float(t_local))
+        h = torch.zeros_like(parts[0]) if h0 is None else h0.float().clone()
+        h_in = None
+        for r, e in enumerate(parts):
+            if r == self.rank:
+                h_in = h.clone()
+            h = a * h + e
+        return h_in, h
+
+    @staticmethod
+    def lsf_slice_end(m: torch.Tensor, alpha) -> torch.Tensor:
+        """End value of h_t = alpha h_{t-1} + (1 - alpha) m_t over a slice (B, T, C) started from zero: a
+        weighted sum over t, so it needs no scan: sum_t (1 - alpha) alpha^(T-1-t) m_t  ->  (B, C) f32."""
+        T = m.shape[1]
+        a = torch.as_tensor(alpha, dtype=torch.float32, device=m.device).reshape(())
+        w = (1.0 - a) * a.pow(torch.arange(T - 1, -1, -1, device=m.device, dtype=torch.float32))
+        return torch.einsum("btc,t->bc", m.float(), w)
+
+    # ---- the two scans of one layer ----------------------------------------------------------------
+    def attention(self, scan, gamma, t_local: int, state0=None):
+        """scan(state_in) -> (o, state_out) runs this rank's slice.  Rank 0 without an initial state needs one
+        pass; the others scan once from zero for D_r and once from the true incoming state.
+        -> (o of this rank's slice, state after the whole sequence)."""
+        o, delta = scan(None)
+        s_in, s_last = self.attention_states(delta, gamma, t_local, state0)
+        if self.rank > 0 or state0 is not None:
+            o, _ = scan(s_in)
+        return o, s_last
+
+    def lsf(self, scan, m, alpha, h0=None):
+        """scan(h_in) applies the LSF scan to this rank's slice m (B, T_local, C) from the carry h_in and returns
+        its result.  -> (that result, membrane after the whole sequence)."""
+        h_in, h_last = self.lsf_states(self.lsf_slice_end(m, alpha), alpha, m.shape[1], h0)
+        return scan(h_in), h_last

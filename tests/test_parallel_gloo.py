@@ -114,3 +114,58 @@ def test_expert_parallel_matches_oracle(world):
     assert len(results) == world
     for rank in range(world):
         assert results[rank] == (True, True, True), (rank, results[rank])
+
+
+# ---- context (sequence) parallelism of the two scans ------------------------------------------------
+def _cp_worker(rank, world, port, results):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(1)
+        g = torch.Generator().manual_seed(9)
+        B, H, T, D, Cc = 2, 3, 24 * world, 64, 10
+        q, k, v = (torch.randn(B, H, T, D, generator=g) for _ in range(3))
+        gamma = torch.rand(H, generator=g) * 0.1 + 0.88
+        S0 = torch.randn(B, H, D, D, generator=g)
+        m = torch.randn(B, T, Cc, generator=g)
+        h0 = torch.randn(B, Cc, generator=g)
+        alpha = 0.83
+        cp = par.ContextParallel()
+        tl = T // world
+        sl = slice(rank * tl, (rank + 1) * tl)
+        ok = []
+        for s_init, h_init in ((None, None), (S0, h0)):
+            # attention: positions enter through the feature map, which sees the slice's true start
+            qf, kf = orc.feature_map_rope(q, k, 5)
+            o_ref, S_ref = orc.attn_scan_recurrent(qf, kf, v, gamma, s_init)
+            calls = []
+
+            def scan(state_in):
+                calls.append(state_in is not None)
+                o, S = orc.attn_scan_recurrent(qf[:, :, sl], kf[:, :, sl], v[:, :, sl], gamma, state_in)
+                return o.float(), S.float()
+
+            o, s_last = cp.attention(scan, gamma, tl, s_init)
+            ok.append(torch.allclose(o.double(), o_ref[:, :, sl], rtol=1e-4, atol=1e-4))
+            ok.append(torch.allclose(s_last.double(), S_ref, rtol=1e-4, atol=1e-4))
+            ok.append(len(calls) == (1 if (rank == 0 and s_init is None) else 2))
+            # LSF
+            h_ref = orc.lsf_scan(m, alpha, h_init)
+            ok.append(torch.allclose(cp.lsf_slice_end(m[:, sl], alpha), orc.lsf_scan(m[:, sl], alpha)[:, -1], atol=1e-5))
+            h, h_last = cp.lsf(lambda h_in: orc.lsf_scan(m[:, sl], alpha, h_in), m[:, sl], alpha, h_init)
+            ok.append(torch.allclose(h, h_ref[:, sl], atol=1e-5))
+            ok.append(torch.allclose(h_last, h_ref[:, -1], atol=1e-5))
+        results[rank] = tuple(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_scans_match_the_whole_sequence(world):
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_cp_worker, args=(world, _free_port(), results), nprocs=world, join=True)
+    assert len(results) == world
+    for rank in range(world):
+        assert all(results[rank]), (rank, results[rank])
