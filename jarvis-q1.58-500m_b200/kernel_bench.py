@@ -213,6 +213,52 @@ def case_decode(a):
                   "cuda_graph": not a.eager})
 
 
+def case_context(a):
+    """Long-sequence prefill of the 606M model with the sequences cut across the ranks (context parallelism):
+    B sequences of T tokens, rank r holding tokens [r*T/W, (r+1)*T/W) of each; hidden states only (no lm_head).
+    Under torchrun; with one process it times the whole sequence on one GPU (the figure to compare with)."""
+    import torch.distributed as dist
+    from jarvis_b200 import modules as jm
+    dev = torch.device("cuda")
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    with torch.device(dev):
+        model = jm.Jarvis(max_seq_len=a.T)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for mod in model.modules():
+            if isinstance(mod, jm.TernaryLinear):
+                mod.weight.copy_(torch.randn(mod.weight.shape, generator=gen, device=dev) * 0.02)
+    model.eval()
+    idx = torch.randint(0, 50257, (a.B, a.T), generator=torch.Generator().manual_seed(1)).to(dev)
+    tl = a.T // world
+    if world > 1:
+        model.set_context_parallel(dist.group.WORLD)
+    mine = idx[:, rank * tl:(rank + 1) * tl].contiguous()
+    for _ in range(3):
+        model.hidden_rows(mine)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        model.hidden_rows(mine)
+    e1.record()
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    t = torch.tensor([e0.elapsed_time(e1) / a.iters], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+    if rank == 0:
+        report("context-parallel prefill (606M, 24 layers, hidden states)", ms, flops=a.B * a.T * 603.98e6 / world,
+               extra={"B": a.B, "T": a.T, "n_gpus": world, "tokens_per_s": a.B * a.T / ms * 1e3,
+                      "note": "achieved = per-GPU ternary-GEMM rate; tokens_per_s = whole job"})
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="case", required=True)
@@ -232,6 +278,8 @@ def main():
     s = sub.add_parser("decode")
     s.add_argument("--B", type=int, default=256); s.add_argument("--steps", type=int, default=64)
     s.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    s = sub.add_parser("context")
+    s.add_argument("--B", type=int, default=2); s.add_argument("--T", type=int, default=16384)
     for p in sub.choices.values():
         p.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
@@ -240,7 +288,8 @@ def main():
         lr = int(os.environ.get("LOCAL_RANK", "0"))
         torch.cuda.set_device(lr)
         dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
-    {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode}[a.case](a)
+    {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode,
+     "context": case_context}[a.case](a)
 
 
 if __name__ == "__main__":

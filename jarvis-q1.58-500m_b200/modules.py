@@ -292,11 +292,13 @@ class SparseMoELayer(nn.Module):
         n_total = N
         if self.stats_group is not None:
             import torch.distributed as dist
-            dist.all_reduce(acc, group=self.stats_group)
-            dist.all_reduce(hist, group=self.stats_group)
-            cnt = torch.tensor([N], dtype=torch.int64, device=dev)
-            dist.all_reduce(cnt, group=self.stats_group)
-            n_total = int(cnt.item()) if self._n_total_hint is None else self._n_total_hint
+            # one all-reduce for everything: sums, P_e, the top-1 histogram and the token count travel as f64
+            # (integers up to 2^53 are exact)
+            both = torch.cat([acc, hist.to(torch.float64), torch.full((1,), float(N), dtype=torch.float64, device=dev)])
+            dist.all_reduce(both, group=self.stats_group)
+            acc.copy_(both[:2 + E])
+            hist.copy_(both[2 + E:2 + 2 * E].to(torch.int32))
+            n_total = int(both[-1].item()) if self._n_total_hint is None else self._n_total_hint
         scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, n_total, n_total * C, self.balance_alpha, scalars=scalars)
         self.last_routing = (idx, gates, meta)
         return out, scalars
@@ -420,7 +422,10 @@ class JarvisBlock(nn.Module):
                 ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=lq.var_scale.detach().float().reshape(1),
                              alpha_min=lq.alpha_min, alpha_max=lq.alpha_max, h0=h_in.contiguous(),
                              resid=x.view(B, T, C), want_out=False)
-            _, h_last = cp.lsf(scan, moe_out.view(B, T, C), alpha, None if h_prev is None else h_prev.float())
+            # the slice's end value from a zero carry: the scan kernel asked for its last value only (reads m once)
+            _, end = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=lq.var_scale.detach().float().reshape(1),
+                                  alpha_min=lq.alpha_min, alpha_max=lq.alpha_max, want_out=False)
+            _, h_last = cp.lsf(scan, end, alpha, T, None if h_prev is None else h_prev.float())
             return h_last, scalars, state
         _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],
                                  var_scale=self.liquid.var_scale.detach().float().reshape(1),
@@ -516,6 +521,9 @@ class Jarvis(nn.Module):
         s_prevs = self._attn_states if (persist_state and self.carry_attention_state) else [None] * len(self.blocks)
         new_h, new_s, aux = [], [], []
         scratch = self._layer_scratch(x.device)
+        if self._cp is not None:
+            for block in self.blocks:       # every rank holds B*T tokens: no host read of the all-reduced count
+                block.moe._n_total_hint = B * T * self._cp.world
         for i, block in enumerate(self.blocks):
             h_prev = h_prevs[i]
             if h_prev is not None and h_prev.shape[0] != B:

@@ -166,6 +166,10 @@ class ContextParallel:
         self.rank = dist.get_rank(group)
 
     def _gather(self, t: torch.Tensor):
+        if t.is_cuda:   # NCCL: one output tensor, no per-rank copies
+            out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+            dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
+            return list(out.unbind(0))
         parts = [torch.empty_like(t) for _ in range(self.world)]
         dist.all_gather(parts, t.contiguous(), group=self.group)
         return parts
@@ -216,8 +220,9 @@ class ContextParallel:
             o, _ = scan(s_in)
         return o, s_last
 
-    def lsf(self, scan, m, alpha, h0=None):
-        """scan(h_in) applies the LSF scan to this rank's slice m (B, T_local, C) from the carry h_in and returns
-        its result.  -> (that result, membrane after the whole sequence)."""
-        h_in, h_last = self.lsf_states(self.lsf_slice_end(m, alpha), alpha, m.shape[1], h0)
+    def lsf(self, scan, slice_end: torch.Tensor, alpha, t_local: int, h0=None):
+        """scan(h_in) applies the LSF scan to this rank's slice from the carry h_in and returns its result;
+        slice_end is the slice's end value from a zero carry (B, C) (lsf_slice_end, or the scan kernel asked
+        for its last value only).  -> (scan's result, membrane after the whole sequence)."""
+        h_in, h_last = self.lsf_states(slice_end, alpha, t_local, h0)
         return scan(h_in), h_last

@@ -153,7 +153,7 @@ def _cp_worker(rank, world, port, results):
             # LSF
             h_ref = orc.lsf_scan(m, alpha, h_init)
             ok.append(torch.allclose(cp.lsf_slice_end(m[:, sl], alpha), orc.lsf_scan(m[:, sl], alpha)[:, -1], atol=1e-5))
-            h, h_last = cp.lsf(lambda h_in: orc.lsf_scan(m[:, sl], alpha, h_in), m[:, sl], alpha, h_init)
+            h, h_last = cp.lsf(lambda h_in: orc.lsf_scan(m[:, sl], alpha, h_in), cp.lsf_slice_end(m[:, sl], alpha), alpha, tl, h_init)
             ok.append(torch.allclose(h, h_ref[:, sl], atol=1e-5))
             ok.append(torch.allclose(h_last, h_ref[:, -1], atol=1e-5))
         results[rank] = tuple(ok)
