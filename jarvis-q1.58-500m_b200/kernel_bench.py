@@ -290,6 +290,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode,
      "context": case_context}[a.case](a)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":
