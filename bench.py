@@ -34,6 +34,13 @@ sys.path.insert(0, ROOT)
 CFG = dict(vocab=50257, d_model=1024, n_layers=24, n_heads=16, n_experts=4, top_k=2, B=8, T=2048)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each of the four GEMM shapes of a layer, from ncu
+# captures of the same kernel (profiles/ternary_gemm_kernel_qkv_and_w2.md): q/k/v 80.9 MB, out-proj + residual
+# 111.5 MB, expert w1 + GELU 152.5 MB, expert w2 174.8 MB.  Below the algorithmic bytes (135 / 168 / 203 / 203 MB)
+# because part of every output is still in L2 when the kernel ends.
+GEMM_DRAM_BYTES_PER_LAUNCH = (80.9e6 + 111.5e6 + 152.5e6 + 174.8e6) / 4
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -249,7 +256,8 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "ternary_gemm_kernel (tcgen05)", "achieved": achieved,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_source": f"bf16_tflops_sustained of {peaks['source']}", "traffic": None,
+                     "peak_source": f"bf16_tflops_sustained of {peaks['source']}",
+                     "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch (mean of the 4 shapes, ncu)",
                      "launches": n_gemm, "flops_per_step": gemm_flops / args.steps,
                      "avg_launch_ms": gemm_ms / max(n_gemm, 1), "gemm_share_of_step": gemm_ms / ms},
         "device_status": status,
