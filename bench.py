@@ -290,9 +290,9 @@ def cpu_state_dict(seed=0):
     return sd
 
 
-def time_cpu_oracle(steps, warmup, budget_s):
+def time_cpu_oracle(steps, warmup, limit_s):
     """Times oracle.model_forward on (1, T_s) token ids; T_s is the largest of 2048/1024/512/256 whose
-    projected total stays within budget_s.  Returns (tok/s, seconds per step, T_s, cores)."""
+    projected total stays within limit_s.  Returns (tok/s, seconds per step, T_s, cores)."""
     from oracle import jarvis_oracle as orc
 
     cores = os.cpu_count() or 1
@@ -310,7 +310,7 @@ def time_cpu_oracle(steps, warmup, budget_s):
     probe = run(256)
     T_s = 256
     for cand in (2048, 1024, 512):
-        if probe * (cand / 256) * 1.3 * (steps + warmup) <= budget_s:   # ~linear in T with a T^2 LSF term
+        if probe * (cand / 256) * 1.3 * (steps + warmup) <= limit_s:   # ~linear in T with a T^2 LSF term
             T_s = cand
             break
     for _ in range(warmup):
@@ -323,7 +323,7 @@ def time_cpu_oracle(steps, warmup, budget_s):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
-    tps, sec, T_s, cores = time_cpu_oracle(args.steps, args.warmup, budget_s=200.0)
+    tps, sec, T_s, cores = time_cpu_oracle(args.steps, args.warmup, limit_s=200.0)
     sample = f"1 of the 8 sequences, first {T_s} of 2048 positions, all 24 layers + lm_head, fp32, per step"
     return {
         "impl": "reference", "metric": "prefill tok/s (606M, B=8xT=2048)", "value": tps, "unit": "tok/s",
@@ -364,7 +364,7 @@ def main():
     out = run_ours(args, rank, world, local_rank)
     if out is not None:
         if world == 1 and not args.no_cpu_baseline:
-            tps, sec, T_s, cores = time_cpu_oracle(steps=1, warmup=0, budget_s=40.0)
+            tps, sec, T_s, cores = time_cpu_oracle(steps=1, warmup=0, limit_s=40.0)
             out["cpu_baseline"] = {
                 "value": tps, "unit": "tok/s", "cores": cores, "kind": "port",
                 "sample": f"1 of the 8 sequences, first {T_s} of 2048 positions, all 24 layers + lm_head, fp32, "

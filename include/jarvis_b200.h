@@ -210,7 +210,7 @@ int jb200_moe_metadata(const int64_t* topk_idx, int N, int K, int E, int32_t* ex
  * (No counterpart in the reference: its extension allocates its outputs and work buffers through
  * torch on every call.)  It is meant for hosts that cannot hand this library device memory on
  * demand -- for example an inference server that gives all device memory to its own arena at
- * start-up and runs plugins with a fixed budget, or a latency-critical loop that must not reach
+ * start-up and gives plugins a fixed share of it, or a latency-critical loop that must not reach
  * cudaMalloc because that call stalls the whole device.  The work arrays live in a 128 KiB array
  * built into the library (every GPU that loads the library carries it until the process exits),
  * which limits N*K to jb200_moe_metadata_static_max_assignments() = 262144; larger inputs are

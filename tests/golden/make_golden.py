@@ -1,7 +1,7 @@
 """Generates tests/golden/*.npz by running the REFERENCE's own modules on CPU (fp32).
 
 Run where the reference tree is mounted:
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/reference]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference   (or JARVIS_REFERENCE=...)
 The fixtures are committed; the tests never need the reference tree.  Inputs are seeded
 synthetic tensors; every stored output was produced by reference code, never by this repo.
 """
@@ -12,7 +12,8 @@ import numpy as np
 import torch
 
 sys.dont_write_bytecode = True
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+_REPO = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+REF = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("JARVIS_REFERENCE") or os.path.join(os.path.dirname(_REPO), "reference"))
 for sub in ("jarvis_engine", "runtime", "associative_attention_cuda", "sparse_model_cuda", "liquid_fusion_cuda"):
     sys.path.insert(0, os.path.join(REF, sub))
 

@@ -82,7 +82,9 @@ def test_no_cpu_fallback():
         jm.LiquidStateFusion(8)(torch.randn(1, 4, 8), torch.tensor(0.5))
 
 
-REF = "/root/reference/jarvis_engine"
+# the reference checkout, when one is at hand: $JARVIS_REFERENCE, else a `reference` directory beside this repo
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(os.environ.get("JARVIS_REFERENCE") or os.path.join(os.path.dirname(_REPO), "reference"), "jarvis_engine")
 
 
 @pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
