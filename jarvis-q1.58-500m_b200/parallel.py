@@ -165,40 +165,45 @@ class ContextParallel:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
 
-    def _gather(self, t: torch.Tensor):
+    def _gather(self, t: torch.Tensor) -> torch.Tensor:
+        """-> (world, *t.shape): every rank's tensor, in rank order."""
         if t.is_cuda:   # NCCL: one output tensor, no per-rank copies
             out = torch.empty((self.world,) + tuple(t.shape), dtype=t.dtype, device=t.device)
             dist.all_gather_into_tensor(out, t.contiguous(), group=self.group)
-            return list(out.unbind(0))
+            return out
         parts = [torch.empty_like(t) for _ in range(self.world)]
         dist.all_gather(parts, t.contiguous(), group=self.group)
-        return parts
+        return torch.stack(parts)
+
+    def _fold(self, parts: torch.Tensor, decay: torch.Tensor, init):
+        """parts: (W, ...) end states of the slices from zero; decay: per-slice decay, broadcastable to parts[0]
+        (gamma^T_local per head, or alpha^T_local).  State entering slice r: sum_{r' < r} decay^(r-1-r') parts[r']
+        + decay^r init; state after the last slice: the same with r = W.  Two weighted sums instead of a loop
+        of W small updates."""
+        W = self.world
+        out = []
+        for upto in (self.rank, W):
+            acc = torch.zeros_like(parts[0]) if init is None else decay.pow(float(upto)) * init
+            if upto > 0:
+                expo = torch.arange(upto - 1, -1, -1, device=parts.device, dtype=torch.float32)
+                w = decay.unsqueeze(0).pow(expo.view((-1,) + (1,) * decay.dim()))       # (upto, *decay.shape)
+                acc = acc + (w * parts[:upto]).sum(dim=0)
+            out.append(acc)
+        return out[0], out[1]
 
     def attention_states(self, delta: torch.Tensor, gamma: torch.Tensor, t_local: int, state0=None):
         """delta: this rank's D_r (B, H, Dv, Dk); gamma: (H,) decays.  -> (state entering this rank's slice,
         state after the last rank's slice); `state0` is the state before the first token of the sequence."""
         parts = self._gather(delta.float())
         g = gamma.float().to(delta.device).pow(float(t_local)).view(1, -1, 1, 1)
-        s = torch.zeros_like(parts[0]) if state0 is None else state0.float().clone()
-        s_in = None
-        for r, d in enumerate(parts):
-            if r == self.rank:
-                s_in = s.clone()
-            s = g * s + d
-        return s_in, s
+        return self._fold(parts, g, None if state0 is None else state0.float())
 
     def lsf_states(self, end: torch.Tensor, alpha, t_local: int, h0=None):
         """end: this rank's e_r (B, C); alpha: scalar decay of the call.  -> (carry into this rank's slice,
         membrane after the last rank's slice)."""
         parts = self._gather(end.float())
-        a = torch.as_tensor(alpha, dtype=torch.float32, device=end.device).reshape(()).pow(float(t_local))
-        h = torch.zeros_like(parts[0]) if h0 is None else h0.float().clone()
-        h_in = None
-        for r, e in enumerate(parts):
-            if r == self.rank:
-                h_in = h.clone()
-            h = a * h + e
-        return h_in, h
+        a = torch.as_tensor(alpha, dtype=torch.float32, device=end.device).reshape(1, 1).pow(float(t_local))
+        return self._fold(parts, a, None if h0 is None else h0.float())
 
     @staticmethod
     def lsf_slice_end(m: torch.Tensor, alpha) -> torch.Tensor:
