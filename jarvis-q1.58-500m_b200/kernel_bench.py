@@ -213,6 +213,42 @@ def case_decode(a):
                   "cuda_graph": not a.eager})
 
 
+def case_serve(a):
+    """Continuous batching on the 606M model: `--requests` requests with prompts ~ U[16, 256] tokens and
+    16..64 new tokens each through `--slots` slots (serving.build_scheduler: admission by prefill, one
+    CUDA-graphed batched step + sampling kernel per iteration).  Wall-clock, host work included."""
+    import time
+    from jarvis_b200 import modules as jm, serving
+    dev = torch.device("cuda")
+    with torch.device(dev):
+        model = jm.Jarvis(max_seq_len=1024)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for mod in model.modules():
+            if isinstance(mod, jm.TernaryLinear):
+                mod.weight.copy_(torch.randn(mod.weight.shape, generator=gen, device=dev) * 0.02)
+    model.eval()
+    sched = serving.build_scheduler(model, max_batch_size=a.slots, max_position=1024, temperature=0.7, top_k=50,
+                                    top_p=0.9, seed=0)
+    g = torch.Generator().manual_seed(1)
+    n_prompt = 0
+    for i in range(a.requests):
+        plen = int(torch.randint(16, 257, (1,), generator=g))
+        n_prompt += plen
+        sched.add_request(serving.Request(i, torch.randint(0, 50257, (plen,), generator=g).tolist(),
+                                          int(torch.randint(16, 65, (1,), generator=g))))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    iters = sched.run()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    assert _lib.device_status() == 0
+    n_new = sum(len(r.generated_tokens) for r in sched.completed)
+    print(json.dumps({"kernel": "continuous batching (606M)", "requests": a.requests, "slots": a.slots, "iterations": iters,
+                      "prompt_tokens": n_prompt, "generated_tokens": n_new, "seconds": dt,
+                      "generated_tok_per_s": n_new / dt, "ms_per_iteration": dt / iters * 1e3}), flush=True)
+
+
 def case_context(a):
     """Long-sequence prefill of the 606M model with the sequences cut across the ranks (context parallelism):
     B sequences of T tokens, rank r holding tokens [r*T/W, (r+1)*T/W) of each; hidden states only (no lm_head).
@@ -278,6 +314,8 @@ def main():
     s = sub.add_parser("decode")
     s.add_argument("--B", type=int, default=256); s.add_argument("--steps", type=int, default=64)
     s.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    s = sub.add_parser("serve")
+    s.add_argument("--slots", type=int, default=64); s.add_argument("--requests", type=int, default=256)
     s = sub.add_parser("context")
     s.add_argument("--B", type=int, default=2); s.add_argument("--T", type=int, default=16384)
     for p in sub.choices.values():
@@ -289,7 +327,7 @@ def main():
         torch.cuda.set_device(lr)
         dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode,
-     "context": case_context}[a.case](a)
+     "context": case_context, "serve": case_serve}[a.case](a)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         import torch.distributed as dist
         if dist.is_initialized():

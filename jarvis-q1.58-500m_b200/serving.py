@@ -139,7 +139,8 @@ class CudaDecodeEngine:
         """Prefill prompt[:-1] into the slot's state; the step of this iteration consumes prompt[-1]."""
         if len(prompt_tokens) > self.max_position:
             raise ValueError(f"prompt of {len(prompt_tokens)} tokens exceeds max_position={self.max_position}")
-        self._zero_slot(slot)
+        if len(prompt_tokens) == 1:
+            self._zero_slot(slot)           # longer prompts overwrite every tensor of the slot below
         if len(prompt_tokens) > 1:
             ctx = torch.tensor([prompt_tokens[:-1]], dtype=torch.int64, device=self.device)
             for blk in self.model.blocks:
