@@ -259,6 +259,43 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
                    float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
                    void* stream);
 
+/* ---- expert parallelism over peer memory (no counterpart: the reference is single-GPU) ------------------- */
+
+/* Device buffers that other processes on the node can map (CUDA IPC).  alloc: cudaMalloc on the current device and
+ * the 64-byte handle to send to the peers (by any host channel); open: maps a peer's buffer for kernels of the
+ * CURRENT device (peer access over NVLink is switched on by the mapping); close / free undo them.  These are the
+ * only entry points that allocate; call them at set-up time, never between kernels. */
+int jb200_peer_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int jb200_peer_buffer_open(const unsigned char* handle64, void** ptr);
+int jb200_peer_buffer_close(void* ptr);
+int jb200_peer_buffer_free(void* ptr);
+
+/* The dispatch exchange of the MoE layer done by the gather itself: rank `rank` of `world` owns experts
+ * [rank*E/world, (rank+1)*E/world) and builds their input rows by reading every rank's routing result and rows
+ * directly from that rank's memory (plain loads over NVLink; all pointers in the three device arrays must be
+ * mapped in this process, e.g. CUDA IPC handles of the peers' buffers):
+ *   peer_offs[s]: i32 [E + 2] = rank s's expert_offsets (jb200_moe_metadata) followed by its n_tokens
+ *   peer_gmap[s]: i32 [n_max * K] = its gather_map;   peer_xn[s]: bf16 [n_max][C] = its rows
+ * Output: dispatched bf16 [max_rows][C], rows of owned expert 0 first, inside an expert ordered by (source rank,
+ * local stable order) = the dispatch order of sparse_model_cuda/sparse_model.cu:23-90 when ranks hold contiguous
+ * token ranges; seg_offsets i32 [E/world + 1] on the device for jb200_ternary_linear_grouped; meta i32
+ * [(E/world) * (world + 1) + E/world + 1] (start of every source's rows inside each owned expert, then a copy of
+ * seg_offsets), which the peers' jb200_ep_pull_combine reads.  Nothing is read back to the host; the caller
+ * places a stream-ordered barrier over the ranks before this call (peers' buffers written), between the expert
+ * GEMMs and jb200_ep_pull_combine (owners' outputs written), and before any of the buffers is reused. */
+int jb200_ep_pull_gather(const void* const* peer_offs, const void* const* peer_gmap, const void* const* peer_xn,
+                         int world, int rank, int E, int C, int K, int n_max, int max_rows, void* dispatched,
+                         int32_t* seg_offsets, int32_t* meta, void* stream);
+
+/* The return exchange fused with scatter_combine (sparse_model.cu:104-124): out[t] = sum_k gates[t][k] *
+ * y_owner[row], the row read from the owner rank's output buffer peer_y[owner] (bf16 [max_rows][C]) at the
+ * position its meta (peer_meta[owner]) gives for this rank's rows.  offs_local / topk_idx / gates / scatter_map are
+ * this rank's own routing results; out f32 or bf16 [n_tokens][C]; stats as jb200_moe_scatter_combine. */
+int jb200_ep_pull_combine(const void* const* peer_y, const void* const* peer_meta, const int32_t* offs_local,
+                          const int64_t* topk_idx, const float* gates, const int32_t* scatter_map, int world, int rank,
+                          int E, int C, int K, int n_tokens, int max_rows, void* out, int out_dtype, double* stats,
+                          void* stream);
+
 /* ---- decode driver: next-token sampling ------------------------------------------------------- */
 
 /* One draw per row of logits, replacing sample_next_token (jarvis_engine/evaluate_jarvis.py:158-185):

@@ -54,6 +54,12 @@ PROTOTYPES = {
     "jb200_moe_finalize": (_I, [_P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P]),
     "jb200_lsf_scan": (_I, [_P, _I, _P, _P, _P, _P, _F, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P]),
     "jb200_lsf_scan_scratch_bytes": (_Z, [_I, _I, _I]),
+    "jb200_peer_buffer_alloc": (_I, [_Z, _P, _P]),
+    "jb200_peer_buffer_open": (_I, [_P, _P]),
+    "jb200_peer_buffer_close": (_I, [_P]),
+    "jb200_peer_buffer_free": (_I, [_P]),
+    "jb200_ep_pull_gather": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "jb200_ep_pull_combine": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
     "jb200_sample": (_I, [_P, _I, _I, _I, _I, _F, _I, _F, _P, _P, _P, _P]),
     "jb200_host_decode16": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
     "jb200_ternary_linear_grouped": (_I, [_P, _I, _I, _P, _P, _I, _I, _P, _I, _P, _I, _I, _P]),

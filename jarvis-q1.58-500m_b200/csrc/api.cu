@@ -98,7 +98,7 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 7; }
+int jb200_abi_version(void) { return 10; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
@@ -161,6 +161,58 @@ int jb200_qkv_linear_rope(const void* x, int M, int K, const uint8_t* packed, co
   GemmRope r{cos_tab, sin_tab, pos0, pos0_scalar, n_pos, T, rope_feats};
   return launch_ternary_gemm(x, M, K, packed, alpha, alpha_rows, N, 1, nullptr, JB200_EPI_QK_ROPE_BF16, out, token_tile,
                              w_layout, static_cast<cudaStream_t>(stream), &r);
+}
+
+int jb200_peer_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  JB_REQUIRE(bytes > 0 && ptr && handle64, "peer_buffer_alloc: bad arguments");
+  void* d = nullptr;
+  JB_CUDA(cudaMalloc(&d, bytes));
+  cudaIpcMemHandle_t h;
+  const cudaError_t e = cudaIpcGetMemHandle(&h, d);
+  if (e != cudaSuccess) {
+    (void)cudaFree(d);
+    JB_CUDA(e);
+  }
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  *ptr = d;
+  return JB200_OK;
+}
+
+int jb200_peer_buffer_open(const unsigned char* handle64, void** ptr) {
+  JB_REQUIRE(handle64 && ptr, "peer_buffer_open: bad arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  void* d = nullptr;
+  // opened with the accessing device current: the mapping is made for this device, peer access included
+  JB_CUDA(cudaIpcOpenMemHandle(&d, h, cudaIpcMemLazyEnablePeerAccess));
+  *ptr = d;
+  return JB200_OK;
+}
+
+int jb200_peer_buffer_close(void* ptr) {
+  if (ptr) JB_CUDA(cudaIpcCloseMemHandle(ptr));
+  return JB200_OK;
+}
+
+int jb200_peer_buffer_free(void* ptr) {
+  if (ptr) JB_CUDA(cudaFree(ptr));
+  return JB200_OK;
+}
+
+int jb200_ep_pull_gather(const void* const* peer_offs, const void* const* peer_gmap, const void* const* peer_xn,
+                         int world, int rank, int E, int C, int K, int n_max, int max_rows, void* dispatched,
+                         int32_t* seg_offsets, int32_t* meta, void* stream) {
+  return launch_ep_pull_gather(peer_offs, peer_gmap, peer_xn, world, rank, E, C, K, n_max, max_rows, dispatched,
+                               seg_offsets, meta, static_cast<cudaStream_t>(stream));
+}
+
+int jb200_ep_pull_combine(const void* const* peer_y, const void* const* peer_meta, const int32_t* offs_local,
+                          const int64_t* topk_idx, const float* gates, const int32_t* scatter_map, int world, int rank,
+                          int E, int C, int K, int n_tokens, int max_rows, void* out, int out_dtype, double* stats,
+                          void* stream) {
+  return launch_ep_pull_combine(peer_y, peer_meta, offs_local, topk_idx, gates, scatter_map, world, rank, E, C, K,
+                                n_tokens, max_rows, out, out_dtype, stats, static_cast<cudaStream_t>(stream));
 }
 
 int jb200_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,

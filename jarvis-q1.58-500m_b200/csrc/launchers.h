@@ -63,6 +63,13 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
                      int head_dim, int flags, cudaStream_t stream);
 size_t attn_scan_scratch_bytes(int B, int T, int H);
 
+int launch_ep_pull_gather(const void* const* peer_offs, const void* const* peer_gmap, const void* const* peer_xn,
+                          int world, int rank, int E, int C, int K, int n_max, int max_rows, void* dispatched,
+                          int32_t* seg_offsets, int32_t* meta, cudaStream_t stream);
+int launch_ep_pull_combine(const void* const* peer_y, const void* const* peer_meta, const int32_t* offs_local,
+                           const int64_t* topk_idx, const float* gates, const int32_t* scatter_map, int world, int rank,
+                           int E, int C, int K, int n_tokens, int max_rows, void* out, int out_dtype, double* stats,
+                           cudaStream_t stream);
 int launch_sample(const void* logits, int logits_dtype, int ld, int n_rows, int V, float temperature, int top_k,
                   float top_p, const float* u, int64_t* out_token, float* out_prob, cudaStream_t stream);
 

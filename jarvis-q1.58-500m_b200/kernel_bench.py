@@ -154,7 +154,7 @@ def case_moe(a):
     rank = dist.get_rank()
     n_loc = a.N // world
     x_loc = xb[rank * n_loc:(rank + 1) * n_loc].contiguous()
-    ep = par.ExpertParallelMoE(moe)
+    ep = par.PeerExpertParallelMoE(moe, max_tokens=n_loc) if a.peer else par.ExpertParallelMoE(moe)
     out, _ = ep.run_rows(x_loc)
     ref, _ = moe.run_rows(x_loc)
     err = float((out.float() - ref.float()).norm() / ref.float().norm())
@@ -163,15 +163,22 @@ def case_moe(a):
     ms = timeit(lambda: ep.run_rows(x_loc), a.iters)
     t = torch.tensor([ms], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    recv = torch.tensor([sum(r) for r in ep.last_recv_counts], device="cuda").sum().reshape(1)
+    if a.peer:
+        recv = ep.seg[-1:].to(torch.int64)          # rows this rank's experts received (device count)
+    else:
+        recv = torch.tensor([sum(r) for r in ep.last_recv_counts], device="cuda").sum().reshape(1)
     allrecv = [torch.zeros_like(recv) for _ in range(world)]
     dist.all_gather(allrecv, recv)
     if rank == 0:
         ms = float(t[0])
-        report("moe_layer expert-parallel (router, all-to-all, experts, all-to-all, combine)", ms,
+        name = ("moe_layer expert-parallel over peer memory (router, pull-gather, experts, pull-combine)" if a.peer
+                else "moe_layer expert-parallel (router, all-to-all, experts, all-to-all, combine)")
+        report(name, ms,
                flops=2.0 * 2 * a.N * (2 * C * C) * 2,
                extra={"N": a.N, "n_gpus": world, "tokens_per_s": a.N / ms * 1e3, "rel_l2_vs_single_gpu": err,
                       "rows_received_per_rank": [int(v) for v in allrecv]})
+    if a.peer:
+        ep.close()
 
 
 def case_decode(a):
@@ -311,6 +318,7 @@ def main():
     s.add_argument("--C", type=int, default=1024); s.add_argument("--resid", action="store_true")
     s = sub.add_parser("moe")
     s.add_argument("--N", type=int, default=65536); s.add_argument("--zipf", type=float, default=1.2)
+    s.add_argument("--peer", action="store_true", help="expert parallel: exchange rows by peer-memory loads, not NCCL all-to-all")
     s = sub.add_parser("decode")
     s.add_argument("--B", type=int, default=256); s.add_argument("--steps", type=int, default=64)
     s.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")

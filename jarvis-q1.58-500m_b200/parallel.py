@@ -231,3 +231,141 @@ class ContextParallel:
         for its last value only).  -> (scan's result, membrane after the whole sequence)."""
         h_in, h_last = self.lsf_states(slice_end, alpha, t_local, h0)
         return scan(h_in), h_last
+
+
+class PeerExpertParallelMoE:
+    """Expert parallelism with the two exchanges done by kernels that read the other GPUs' memory directly
+    (csrc/ep_peer.cu) instead of NCCL all-to-alls: the owner of an expert pulls its input rows from every rank's
+    routing result, the home rank of a token pulls its expert outputs back.  Needs world <= num_experts,
+    num_experts % world == 0, one process per GPU on one node, and at most `max_tokens` tokens per rank and call.
+
+    Buffers that peers read (rows, gather map, offsets, expert outputs, row bookkeeping) live in one slab per rank,
+    allocated once and mapped into every other rank through its CUDA IPC handle (jb200_peer_buffer_*).  No count is ever read back to the host; the phases
+    are separated by stream-ordered barriers (a one-element all-reduce).  Results equal the single-GPU layer
+    bit for bit when ranks hold contiguous token ranges (same rows in the same order through the same GEMMs)."""
+
+    def __init__(self, moe, max_tokens: int, group=None, out_dtype=torch.bfloat16):
+        import ctypes as C_
+        from . import _lib
+        self._lib = _lib
+        lib = _lib.load()
+        self.moe = moe
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        E, K = moe.num_experts, moe.top_k
+        if self.world > E or E % self.world:
+            raise ValueError(f"peer expert parallelism needs world ({self.world}) to divide num_experts ({E})")
+        self.per = E // self.world
+        dev = moe.router.weight.device
+        C = moe.router.weight.shape[1]
+        self.C, self.E, self.K, self.n_max = C, E, K, max_tokens
+        self.max_rows = max_tokens * K * self.world          # every slot of every rank on one expert: the worst case
+        # one slab per rank holds everything its peers read; the same layout on every rank
+        layout, off = {}, 0
+        for name, nbytes in (("xn", max_tokens * C * 2), ("y", self.max_rows * C * 2), ("gmap", max_tokens * K * 4),
+                             ("offs", (E + 2) * 4), ("meta", (self.per * (self.world + 1) + self.per + 1) * 4)):
+            layout[name] = off
+            off = (off + nbytes + 255) // 256 * 256
+        self._slab_bytes = off
+        with torch.cuda.device(dev):
+            ptr, handle = C_.c_void_p(), (C_.c_ubyte * 64)()
+            _lib.check(lib.jb200_peer_buffer_alloc(off, C_.byref(ptr), handle), "jb200_peer_buffer_alloc")
+            self._slab = ptr.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self._opened, bases = [], []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    bases.append(self._slab)
+                    continue
+                p = C_.c_void_p()
+                _lib.check(lib.jb200_peer_buffer_open((C_.c_ubyte * 64).from_buffer_copy(h), C_.byref(p)), "jb200_peer_buffer_open")
+                self._opened.append(p.value)
+                bases.append(p.value)
+
+        class _Raw:      # zero-copy torch view of the slab
+            def __init__(self, address, nbytes):
+                self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
+
+        slab = torch.as_tensor(_Raw(self._slab, off), device=dev)
+        slab.zero_()
+
+        def view(name, dtype, shape):
+            n = 1
+            for d in shape:
+                n *= d
+            nbytes = n * torch.empty((), dtype=dtype).element_size()
+            return slab[layout[name]:layout[name] + nbytes].view(dtype).view(shape)
+
+        self.xn = view("xn", torch.bfloat16, (max_tokens, C))
+        self.y = view("y", torch.bfloat16, (self.max_rows, C))
+        self.gmap = view("gmap", torch.int32, (max_tokens * K,))
+        self.offs = view("offs", torch.int32, (E + 2,))
+        self.meta = view("meta", torch.int32, (self.per * (self.world + 1) + self.per + 1,))
+        self._ptrs = {name: torch.tensor([b + layout[name] for b in bases], dtype=torch.int64, device=dev) for name in layout}
+        self.disp = torch.empty((self.max_rows, C), dtype=torch.bfloat16, device=dev)
+        self.hid = None
+        self.seg = torch.zeros((self.per + 1,), dtype=torch.int32, device=dev)
+        self._flag = torch.zeros((1,), dtype=torch.float32, device=dev)
+        (p1, a1), (p2, a2) = moe.packed()
+        sel = torch.arange(self.rank * self.per, (self.rank + 1) * self.per, device=dev)
+        self._w = (p1[sel].contiguous(), a1[sel].contiguous(), p2[sel].contiguous(), a2[sel].contiguous())
+        self.out_dtype = out_dtype
+        torch.cuda.synchronize(dev)
+        self.barrier()
+
+    def barrier(self):
+        """Stream-ordered barrier over the ranks: every rank's earlier kernels have finished (and their writes are
+        in device memory) before any rank's later kernels start."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self):
+        """Unmap the peers' slabs and free this rank's (call on every rank before the process group goes away)."""
+        if self._slab is None:
+            return
+        self.barrier()
+        torch.cuda.synchronize()
+        lib = self._lib.load()
+        for p in self._opened:
+            self._lib.check(lib.jb200_peer_buffer_close(p), "jb200_peer_buffer_close")
+        self._opened = []
+        dist.barrier(group=self.group)              # nobody still maps this rank's slab
+        self.xn = self.y = self.gmap = self.offs = self.meta = None
+        self._lib.check(lib.jb200_peer_buffer_free(self._slab), "jb200_peer_buffer_free")
+        self._slab = None
+
+    def run_rows(self, x, stats=None):
+        """x: bf16 (N_local, C) rows of this rank -> ((N_local, C) MoE output, (topk_idx, gates))."""
+        from . import ops
+        lib, C, E, K = self._lib.load(), self.C, self.E, self.K
+        N = x.shape[0]
+        if N > self.n_max:
+            raise RuntimeError(f"PeerExpertParallelMoE: {N} tokens exceed max_tokens={self.n_max}")
+        stream = torch.cuda.current_stream().cuda_stream
+        idx, gates, _ = ops.router_top2(x, self.moe.router.weight.detach().float().contiguous())
+        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, E)
+        self.xn[:N].copy_(x)
+        self.gmap[:N * K].copy_(gather)
+        self.offs[:E + 1].copy_(offsets)
+        self.offs[E + 1:].fill_(N)
+        self.barrier()                                  # every rank's rows and routing are in place
+        self._lib.check(lib.jb200_ep_pull_gather(self._ptrs["offs"].data_ptr(), self._ptrs["gmap"].data_ptr(),
+                                                 self._ptrs["xn"].data_ptr(), self.world, self.rank, E, C, K, self.n_max,
+                                                 self.max_rows, self.disp.data_ptr(), self.seg.data_ptr(),
+                                                 self.meta.data_ptr(), stream), "jb200_ep_pull_gather")
+        p1, a1, p2, a2 = self._w
+        if self.hid is None:
+            self.hid = torch.empty((self.max_rows, p1.shape[1]), dtype=torch.bfloat16, device=x.device)
+        ops.ternary_linear_grouped(self.disp, p1, a1, self.seg, epilogue=ops.EPI_GELU_BF16, out=self.hid, prepared=True)
+        ops.ternary_linear_grouped(self.hid, p2, a2, self.seg, epilogue=ops.EPI_BF16, out=self.y, prepared=True)
+        self.barrier()                                  # every owner's outputs (and row bookkeeping) are in place
+        out = torch.empty((N, C), dtype=self.out_dtype, device=x.device)
+        self._lib.check(lib.jb200_ep_pull_combine(self._ptrs["y"].data_ptr(), self._ptrs["meta"].data_ptr(),
+                                                  offsets.data_ptr(), idx.data_ptr(), gates.data_ptr(), scatter.data_ptr(),
+                                                  self.world, self.rank, E, C, K, N, self.max_rows, out.data_ptr(),
+                                                  1 if self.out_dtype == torch.bfloat16 else 0,
+                                                  None if stats is None else stats.data_ptr(), stream),
+                        "jb200_ep_pull_combine")
+        self.barrier()                                  # nobody still reads buffers that the next call overwrites
+        return out, (idx, gates)

@@ -29,6 +29,16 @@ def test_expert_parallel_moe_two_gpus():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_expert_parallel_over_peer_memory_two_gpus():
+    """Same layer with the exchanges done by kernels reading the other GPU's memory (plain loads, no multimem)."""
+    res = _torchrun(2, ["jarvis-q1.58-500m_b200/kernel_bench.py", "moe", "--N", "8192", "--iters", "2", "--peer"])
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads([ln for ln in res.stdout.strip().splitlines() if ln.startswith("{")][-1])
+    assert line["n_gpus"] == 2 and line["rel_l2_vs_single_gpu"] < 1e-6
+    assert sum(line["rows_received_per_rank"]) == 2 * 8192
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_data_parallel_bench_two_gpus():
     res = _torchrun(2, ["bench.py", "--gpus", "2", "--steps", "2", "--warmup", "3"], timeout=900)
     assert res.returncode == 0, res.stderr[-2000:]
