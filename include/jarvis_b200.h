@@ -168,6 +168,9 @@ int jb200_embedding(const int64_t* idx, const float* table, int vocab, float* ou
  * scratch: jb200_attn_scan_scratch_bytes(B, T, H) bytes (8-byte aligned) or NULL.  With scratch, long
  *   sequences are cut into segments that run in parallel (a first launch computes each segment's state
  *   contribution from k and v); with NULL every (sequence, head) is walked by one CTA.
+ * o == NULL (then q may be NULL too; needs s_out, scratch, T > 1): state only - just the k/v half of the work,
+ *   every piece of the sequence in parallel, and s_out = the state after the sequence (what a rank of a
+ *   context-parallel group needs from its slice before it knows its incoming state).
  * flags: 0, or JB200_ATTN_QK_PREPARED when q and k were produced by jb200_qkv_linear_rope (feature map and
  * RoPE already applied, head dim interleaved): the scan then skips its own prologue; s_in / s_out keep the
  * natural (B, H, D_v, D_k) order either way.  T == 1 (decode step) takes raw q, k only.

@@ -55,6 +55,7 @@ struct AttnParams {
   int seg_chunks;          // chunks per sequence segment (grid.z walks the segments)
   int nseg;
   float* seg_state;        // [B][H][nseg-1][64][64]: state contribution of each non-final segment
+  int n_pieces;            // state contributions stored per (sequence, head): nseg - 1, or nseg in a state-only call
   int qk_prepared;         // q, k already hold phi(.) + RoPE with the head dim interleaved (d, d+32 adjacent)
   unsigned int* status;
 };
@@ -110,7 +111,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int n_chunks = (T + CH - 1) / CH;
   const int seg = blockIdx.z;
   const int ck_begin = seg * p.seg_chunks;
-  const int ck_end = STATE_ONLY ? ck_begin + p.seg_chunks : min(n_chunks, ck_begin + p.seg_chunks);
+  const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
   const int row0 = b * T;                       // first row of this sequence in the (B*T, ld) matrices
   const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
   const float gamma = __ldg(p.gamma + h);
@@ -159,7 +160,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       if (!STATE_ONLY && seg > 0) {
         // state entering this segment: fold the earlier segments' contributions, oldest first
         const float gL = expf(log_g * float(p.seg_chunks * CH));
-        const float* dp = p.seg_state + (size_t(b) * p.H + h) * (p.nseg - 1) * D * D;
+        const float* dp = p.seg_state + (size_t(b) * p.H + h) * p.n_pieces * D * D;
         for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
           const float2 lo = __ldg(reinterpret_cast<const float2*>(dp + r * D + c));
           const float2 hi = __ldg(reinterpret_cast<const float2*>(dp + (r + 8) * D + c));
@@ -384,7 +385,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   }
 
   float* so = nullptr;
-  if (STATE_ONLY) so = p.seg_state + ((size_t(b) * p.H + h) * (p.nseg - 1) + seg) * D * D;
+  if (STATE_ONLY) so = p.seg_state + ((size_t(b) * p.H + h) * p.n_pieces + seg) * D * D;
   else if (p.s_out && seg == p.nseg - 1) so = p.s_out + (size_t(b) * p.H + h) * D * D;
   if (ok && so) {
     const int r = 16 * warp + (lane >> 2);
@@ -402,6 +403,28 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         *reinterpret_cast<float2*>(so + (r + 8) * D + c) = make_float2(S[nt][2], S[nt][3]);
       }
     }
+  }
+}
+
+// State-only calls (no output rows wanted): every piece of the sequence has left its contribution D_s, scanned
+// from a zero state, in seg_state; the state after the whole sequence is
+//   S = gamma^T S_in + sum_s gamma^(T - end_s) D_s,      end_s = last token of piece s + 1.
+// One CTA per (head, sequence), 16 elements per thread.  The pieces are in the kernel's own column order
+// (interleaved when q/k were prepared); s_in / s_out use the natural one.
+__global__ void __launch_bounds__(256) attn_fold_states_kernel(const AttnParams p) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  const float log_g = logf(__ldg(p.gamma + h));
+  const int L = p.seg_chunks * CH;
+  const size_t bh = size_t(b) * p.H + h;
+  for (int e = threadIdx.x; e < D * D; e += 256) {
+    const int r = e >> 6, d = e & 63;
+    const int col = p.qk_prepared ? (2 * (d & 31) + (d >> 5)) : d;
+    float acc = p.s_in ? expf(log_g * float(p.T)) * __ldg(p.s_in + bh * D * D + e) : 0.f;
+    for (int s2 = 0; s2 < p.n_pieces; ++s2) {
+      const int end = min((s2 + 1) * L, p.T);
+      acc += expf(log_g * float(p.T - end)) * __ldg(p.seg_state + (bh * p.n_pieces + s2) * D * D + r * D + col);
+    }
+    p.s_out[bh * D * D + e] = acc;
   }
 }
 
@@ -500,7 +523,7 @@ size_t attn_scan_scratch_bytes(int B, int T, int H) {
   const int sms = sm_count();
   int sc, ns;
   pick_segments(B, T, H, sms > 0 ? sms : 148, &sc, &ns);
-  return size_t(B) * H * size_t(ns - 1) * D * D * sizeof(float);
+  return size_t(B) * H * size_t(ns) * D * D * sizeof(float);   // ns - 1 pieces for a full call, ns for a state-only one
 }
 
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
@@ -513,10 +536,13 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   JB_REQUIRE(B >= 0 && T >= 0 && H > 0, "attn_scan: bad shape (B=%d, T=%d, H=%d)", B, T, H);
   JB_REQUIRE(B <= 65535, "attn_scan: batch (%d) exceeds 65535", B);
   if (B == 0 || T == 0) return JB200_OK;
-  JB_REQUIRE(q && k && v && gamma && cos_tab && sin_tab && o, "attn_scan: null pointer");
-  JB_REQUIRE(ld_qkv >= H * D && ld_qkv % 8 == 0 && ld_o >= H * D && ld_o % 8 == 0,
+  JB_REQUIRE(k && v && gamma && cos_tab && sin_tab, "attn_scan: null pointer");
+  JB_REQUIRE(o ? (q != nullptr) : (s_out && scratch && T > 1),
+             "attn_scan: a call without output rows (state only) needs s_out, scratch and T > 1; any other call needs q and o");
+  if (!q) q = k;     // state only: the tensor map of q is built but never used
+  JB_REQUIRE(ld_qkv >= H * D && ld_qkv % 8 == 0 && (!o || (ld_o >= H * D && ld_o % 8 == 0)),
              "attn_scan: row strides must cover H*64 columns and be multiples of 8 elements");
-  JB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(o) && aligned16(cos_tab) && aligned16(sin_tab),
+  JB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && (!o || aligned16(o)) && aligned16(cos_tab) && aligned16(sin_tab),
              "attn_scan: pointers must be 16-byte aligned");
   JB_REQUIRE(!s_in || (reinterpret_cast<uintptr_t>(s_in) & 7u) == 0, "attn_scan: state pointer misaligned");
   JB_REQUIRE(!s_out || (reinterpret_cast<uintptr_t>(s_out) & 7u) == 0, "attn_scan: state pointer misaligned");
@@ -529,7 +555,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
     AttnParams dp;
     dp.gamma = gamma; dp.cos_tab = cos_tab; dp.sin_tab = sin_tab; dp.pos0 = pos0; dp.pos0_scalar = pos0_scalar;
     dp.n_pos = n_pos; dp.s_in = s_in; dp.s_out = s_out; dp.o = reinterpret_cast<__nv_bfloat16*>(o); dp.ld_o = ld_o;
-    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.qk_prepared = 0; dp.status = nullptr;
+    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.n_pieces = 0; dp.qk_prepared = 0; dp.status = nullptr;
     attn_decode_kernel<<<dim3(H, B), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q),
                                                         reinterpret_cast<const __nv_bfloat16*>(k),
                                                         reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
@@ -546,6 +572,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.n_pos = n_pos; p.s_in = s_in; p.s_out = s_out; p.o = reinterpret_cast<__nv_bfloat16*>(o); p.ld_o = ld_o;
   p.B = B; p.T = T; p.H = H;
   p.qk_prepared = (flags & JB200_ATTN_QK_PREPARED) ? 1 : 0;
+  p.n_pieces = 0;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
   const int sms = sm_count();
@@ -556,6 +583,16 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   if (scratch) pick_segments(B, T, H, sms, &p.seg_chunks, &p.nseg);   // without scratch: one segment per sequence
   JB_REQUIRE(p.nseg <= 65535, "attn_scan: too many segments");
   JB_REQUIRE(!scratch || (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "attn_scan: scratch pointer misaligned");
+  p.n_pieces = o ? p.nseg - 1 : p.nseg;
+  if (!o) {
+    // state only: the k/v pass over every piece, then the fold
+    JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
+    attn_scan_kernel<true><<<dim3(H, B, p.nseg), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+    JB_LAUNCH_CHECK("attn_scan_kernel<state>");
+    attn_fold_states_kernel<<<dim3(H, B), 256, 0, stream>>>(p);
+    JB_LAUNCH_CHECK("attn_fold_states_kernel");
+    return JB200_OK;
+  }
   JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
   if (p.nseg > 1) {
     JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));

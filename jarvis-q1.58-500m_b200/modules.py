@@ -204,7 +204,10 @@ class AssociativeLinearAttention(nn.Module):
             def scan(state_in):
                 return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
                                      start_pos=start_pos, state_in=state_in, want_state=True, qk_prepared=fused)
-            return cp.attention(scan, gamma, T, h_prev)
+            def state_only():
+                return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
+                                     start_pos=start_pos, qk_prepared=fused, want_out=False)[1]
+            return cp.attention(scan, gamma, T, h_prev, state_only=state_only if T > 1 else None)
         return ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, self.n_heads,
                              start_pos=start_pos, state_in=h_prev, want_state=want_state,
                              state_out=h_prev if (inplace_state and h_prev is not None) else None, qk_prepared=fused)

@@ -247,9 +247,9 @@ def embedding(idx: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Tensor, cos_tab: torch.Tensor,
               sin_tab: torch.Tensor, B: int, T: int, H: int, *, start_pos=0, state_in: torch.Tensor | None = None,
               want_state: bool = False, out: torch.Tensor | None = None, segmented: bool = True,
-              state_out: torch.Tensor | None = None, qk_prepared: bool = False):
+              state_out: torch.Tensor | None = None, qk_prepared: bool = False, want_out: bool = True):
     """Feature map + RoPE + decayed causal scan (qk_prepared=True: q and k come from qkv_linear_rope, the
-    scan skips its prologue).  q, k, v: bf16 2-D views (B*T, H*64) sharing one
+    scan skips its prologue; want_out=False: state only, returns (None, state) after a k/v-only pass).  q, k, v: bf16 2-D views (B*T, H*64) sharing one
     row stride (e.g. column slices of a fused q|k|v matrix).  start_pos: int, or int32 (B,) tensor of
     per-sequence first positions.  Returns (o bf16 (B*T, H*64), final state f32 (B,H,64,64) or None)."""
     lib = _lib.load()
@@ -273,7 +273,11 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
         _need(state_in, torch.float32, "attn_scan.state_in")
         if tuple(state_in.shape) != (B, H, 64, 64):
             raise RuntimeError("attn_scan: state_in must be (B, H, 64, 64)")
-    if out is None:
+    if not want_out:
+        if T <= 1:
+            raise RuntimeError("attn_scan: a state-only call needs T > 1")
+        want_state, segmented, out = True, True, None
+    elif out is None:
         out = torch.empty((B * T, H * 64), dtype=torch.bfloat16, device=q.device)
     if state_out is not None:
         # may alias state_in when the call runs one segment per sequence (every CTA reads its own
@@ -290,7 +294,8 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
             scratch = torch.empty((nbytes // 4,), dtype=torch.float32, device=q.device)
     _lib.check(
         lib.jb200_attn_scan(_ptr(q), _ptr(k), _ptr(v), ld, _ptr(gamma), _ptr(cos_tab), _ptr(sin_tab), cos_tab.shape[0],
-                            _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0), _ptr(s_out), _ptr(scratch),
+                            _ptr(pos_t), pos_s, _ptr(state_in), _ptr(out), out.stride(0) if out is not None else 0, _ptr(s_out),
+                            _ptr(scratch),
                             B, T, H, 64, ATTN_QK_PREPARED if qk_prepared else 0, _stream()),
         "jb200_attn_scan",
     )

@@ -215,13 +215,19 @@ class ContextParallel:
         return torch.einsum("btc,t->bc", m.float(), w)
 
     # ---- the two scans of one layer ----------------------------------------------------------------
-    def attention(self, scan, gamma, t_local: int, state0=None):
-        """scan(state_in) -> (o, state_out) runs this rank's slice.  Rank 0 without an initial state needs one
-        pass; the others scan once from zero for D_r and once from the true incoming state.
-        -> (o of this rank's slice, state after the whole sequence)."""
-        o, delta = scan(None)
+    def attention(self, scan, gamma, t_local: int, state0=None, state_only=None):
+        """scan(state_in) -> (o, state_out) runs this rank's slice; state_only() -> D_r, when given, is a cheaper
+        way to get the slice's end state from a zero state (k/v only).  Rank 0 without an initial state needs one
+        full pass (its output is final and its end state is D_0); the others get D_r first and scan once more
+        from the true incoming state.  -> (o of this rank's slice, state after the whole sequence)."""
+        second = self.rank > 0 or state0 is not None
+        o = None
+        if second and state_only is not None:
+            delta = state_only()
+        else:
+            o, delta = scan(None)
         s_in, s_last = self.attention_states(delta, gamma, t_local, state0)
-        if self.rank > 0 or state0 is not None:
+        if second:
             o, _ = scan(s_in)
         return o, s_last
 

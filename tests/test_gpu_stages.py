@@ -491,3 +491,28 @@ def test_fused_prologue_argument_errors():
         ops.qkv_linear_rope(x, pk, torch.ones(3, device="cuda"), cos, sin, 32, 200, alpha_rows=128)
     with pytest.raises(RuntimeError, match="needs its tables"):
         ops.ternary_linear(x, pk, torch.ones(3, device="cuda"), epilogue=4, alpha_rows=128)
+
+
+@pytest.mark.parametrize("T", [2, 65, 1000, 2048])
+def test_attn_state_only_call_matches_the_full_scan(T):
+    """o == NULL: only the k/v half runs, every piece in parallel; the end state must be the full call's (same
+    bf16 products, another summation order), with and without an incoming state, and against the oracle."""
+    g = torch.Generator().manual_seed(T)
+    B, H = 2, 3
+    q, k, v = (torch.randn(B * T, H * 64, generator=g).bfloat16().cuda() for _ in range(3))
+    gamma = (torch.rand(H, generator=g) * 0.099 + 0.9).cuda()
+    cos, sin = rope_tabs(T + 9)
+    S0 = torch.randn(B, H, 64, 64, generator=g).cuda()
+    for s_in in (None, S0):
+        _, S_full = ops.attn_scan(q, k, v, gamma, cos, sin, B, T, H, start_pos=9, state_in=s_in, want_state=True)
+        none, S_only = ops.attn_scan(q, k, v, gamma, cos, sin, B, T, H, start_pos=9, state_in=s_in, want_out=False)
+        assert none is None
+        assert rel_l2(S_only, S_full) <= 2e-3
+    assert _lib.device_status() == 0
+
+    def heads(t):
+        return t.float().cpu().view(B, T, H, 64).transpose(1, 2)
+
+    qf, kf = orc.feature_map_rope(heads(q), heads(k), 9)
+    _, S_ref = orc.attn_scan_recurrent(qf, kf, heads(v), gamma.cpu(), S0.cpu())
+    assert rel_l2(S_only, S_ref) <= 1e-2
