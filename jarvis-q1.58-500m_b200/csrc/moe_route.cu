@@ -286,6 +286,50 @@ meta_assign_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, co
   }
 }
 
+// Small batches (single-token decode steps): the three kernels above in one CTA of up to 1024 threads, one
+// assignment per thread.  Same stable order: earlier assignments of the same expert come first.
+constexpr int META_SMALL_MAX = 1024;
+__global__ void __launch_bounds__(META_SMALL_MAX)
+meta_small_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, int* __restrict__ expert_counts,
+                  int* __restrict__ expert_offsets, int* __restrict__ scatter_map, int* __restrict__ gather_map,
+                  int* __restrict__ gate_idx_map) {
+  __shared__ int warp_cnt[META_SMALL_MAX / 32][MAX_E];
+  __shared__ int offs[MAX_E + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  const int m = threadIdx.x;
+  const int e = m < M ? clamp_expert(flat_idx[m], E) : -1;
+  int rank = 0;
+  for (int q = 0; q < E; ++q) {
+    const unsigned mask = __ballot_sync(0xffffffffu, e == q);
+    if (e == q) rank = __popc(mask & ((1u << lane) - 1u));
+    if (lane == 0) warp_cnt[warp][q] = __popc(mask);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int q = 0; q < E; ++q) {
+      int c = 0;
+      for (int w = 0; w < n_warps; ++w) c += warp_cnt[w][q];
+      offs[q] = acc;
+      expert_counts[q] = c;
+      expert_offsets[q] = acc;
+      acc += c;
+    }
+    offs[E] = acc;
+    expert_offsets[E] = acc;
+  }
+  __syncthreads();
+  if (m < M) {
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_cnt[w][e];
+    const int slot = offs[e] + before + rank;
+    scatter_map[m] = slot;
+    gather_map[slot] = m / K;
+    gate_idx_map[slot] = m % K;
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // gather / combine
 // ---------------------------------------------------------------------------------------------
@@ -437,6 +481,12 @@ int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int
   const int M = n_tokens * K;
   const int chunks = (M + META_CHUNK - 1) / META_CHUNK;
   JB_REQUIRE(M == 0 || (topk_idx && scatter_map && gather_map && gate_idx_map && scratch), "moe_metadata: null pointer");
+  if (M > 0 && M <= META_SMALL_MAX) {
+    meta_small_kernel<<<1, (M + 31) / 32 * 32, 0, stream>>>(topk_idx, M, K, E, expert_counts, expert_offsets, scatter_map,
+                                                            gather_map, gate_idx_map);
+    JB_LAUNCH_CHECK("meta_small_kernel");
+    return JB200_OK;
+  }
   int* chunk_counts = reinterpret_cast<int*>(scratch);
   int* chunk_base = chunk_counts + size_t(chunks) * E;
   if (M > 0) {
