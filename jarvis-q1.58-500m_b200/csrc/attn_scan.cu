@@ -368,14 +368,16 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           mma16816(S[2 * np + 1], af, b2, b3);
         }
       }
-      // publish the bf16 mirror for the next chunk's cross term
-      const int r = 16 * warp + (lane >> 2);
-      const int cb = 2 * (lane & 3);
+      // publish the bf16 mirror for the next chunk's cross term (a k/v-only pass has none)
+      if (!STATE_ONLY) {
+        const int r = 16 * warp + (lane >> 2);
+        const int cb = 2 * (lane & 3);
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int c = nt * 8 + cb;
-        *reinterpret_cast<uint32_t*>(sb_next + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
-        *reinterpret_cast<uint32_t*>(sb_next + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
+        for (int nt = 0; nt < 8; ++nt) {
+          const int c = nt * 8 + cb;
+          *reinterpret_cast<uint32_t*>(sb_next + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
+          *reinterpret_cast<uint32_t*>(sb_next + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
+        }
       }
     }
 
