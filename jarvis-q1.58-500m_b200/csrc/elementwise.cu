@@ -105,6 +105,7 @@ int launch_rmsnorm(const void* x, int x_dtype, const float* w, float eps, void* 
   JB_REQUIRE(n_rows >= 0 && C > 0, "rmsnorm: bad shape (%d, %d)", n_rows, C);
   JB_REQUIRE(C % 8 == 0 && C <= 4096, "rmsnorm: row length (%d) must be a multiple of 8 and at most 4096", C);
   JB_REQUIRE((x_dtype == 0 || x_dtype == 1) && (y_dtype == 0 || y_dtype == 1), "rmsnorm: dtype must be 0 (f32) or 1 (bf16)");
+  if (n_rows == 0) return JB200_OK;
   JB_REQUIRE(x && w && y, "rmsnorm: null pointer");
   JB_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y), "rmsnorm: pointers must be 16-byte aligned");
   if (n_rows == 0) return JB200_OK;
@@ -118,6 +119,7 @@ int launch_embedding(const int64_t* idx, const float* table, int vocab, float* o
                      cudaStream_t stream) {
   JB_REQUIRE(n_rows >= 0 && C > 0 && vocab > 0, "embedding: bad shape");
   JB_REQUIRE(C % 4 == 0, "embedding: row length (%d) must be a multiple of 4", C);
+  if (n_rows == 0) return JB200_OK;
   JB_REQUIRE(idx && table && out, "embedding: null pointer");
   JB_REQUIRE(aligned16(table) && aligned16(out), "embedding: pointers must be 16-byte aligned");
   if (n_rows == 0) return JB200_OK;

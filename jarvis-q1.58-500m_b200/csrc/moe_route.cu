@@ -420,6 +420,7 @@ int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, 
   JB_REQUIRE(n_tokens >= 0 && C > 0, "router_top2: bad shape");
   JB_REQUIRE(E == 4 || E == 8, "router_top2: num_experts (%d) must be 4 or 8", E);
   JB_REQUIRE(C % 8 == 0 && size_t(E) * C * 4 <= 160 * 1024, "router_top2: d_model (%d) must be a multiple of 8 and fit shared memory", C);
+  if (n_tokens == 0) return JB200_OK;
   JB_REQUIRE(x_bf16 && w_router && topk_idx && gates, "router_top2: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_router), "router_top2: pointers must be 16-byte aligned");
   if (n_tokens == 0) return JB200_OK;
@@ -448,6 +449,7 @@ int launch_rmsnorm_router(const float* x, const float* w_norm, float eps, void* 
   JB_REQUIRE(n_tokens >= 0 && C > 0, "rmsnorm_router: bad shape");
   JB_REQUIRE(E == 4 || E == 8, "rmsnorm_router: num_experts (%d) must be 4 or 8", E);
   JB_REQUIRE(C % 8 == 0 && C <= 1024, "rmsnorm_router: d_model (%d) must be a multiple of 8 and at most 1024", C);
+  if (n_tokens == 0) return JB200_OK;
   JB_REQUIRE(x && w_norm && xn_bf16 && w_router && topk_idx && gates, "rmsnorm_router: null pointer");
   JB_REQUIRE(aligned16(x) && aligned16(w_norm) && aligned16(xn_bf16) && aligned16(w_router),
              "rmsnorm_router: pointers must be 16-byte aligned");

@@ -154,6 +154,7 @@ int launch_pack_ternary(const float* w, int out_features, int in_features, const
 
 int launch_pack_codes(const float* w_ternary, size_t n_elems, uint8_t* packed, cudaStream_t stream) {
   JB_REQUIRE(n_elems % 4 == 0, "pack_codes: element count must be divisible by 4");
+  if (n_elems == 0) return JB200_OK;
   JB_REQUIRE(w_ternary && packed, "pack_codes: null pointer");
   JB_REQUIRE(aligned16(w_ternary), "pack_codes: input pointer must be 16-byte aligned");
   JB_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 3u) == 0, "pack_codes: packed pointer must be 4-byte aligned");
@@ -168,6 +169,7 @@ int launch_pack_codes(const float* w_ternary, size_t n_elems, uint8_t* packed, c
 
 int launch_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, void* out, cudaStream_t stream) {
   JB_REQUIRE(out_dtype == 0 || out_dtype == 1, "unpack_ternary: out_dtype must be 0 (f32) or 1 (bf16)");
+  if (n_bytes == 0) return JB200_OK;
   JB_REQUIRE(packed && out, "unpack_ternary: null pointer");
   if (n_bytes == 0) return JB200_OK;
   size_t blocks = (n_bytes + PACK_THREADS - 1) / PACK_THREADS;

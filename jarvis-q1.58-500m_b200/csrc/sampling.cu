@@ -180,6 +180,7 @@ int launch_sample(const void* logits, int logits_dtype, int ld, int n_rows, int 
                   float top_p, const float* u, int64_t* out_token, float* out_prob, cudaStream_t stream) {
   JB_REQUIRE(n_rows >= 0 && V > 0 && ld >= V, "sample: bad shape (rows=%d, V=%d, ld=%d)", n_rows, V, ld);
   JB_REQUIRE(logits_dtype == 0 || logits_dtype == 1, "sample: logits dtype must be 0 (f32) or 1 (bf16)");
+  if (n_rows == 0) return JB200_OK;
   JB_REQUIRE(logits && out_token, "sample: null pointer");
   const bool greedy = temperature <= 0.f;
   JB_REQUIRE(greedy || (top_k >= 1 && top_k <= SAMPLE_MAX_K),

@@ -304,6 +304,7 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
                "qkv_linear_rope: rotated features (%d) must be whole 64-wide heads within out_features", rope->rope_feats);
   }
   JB_REQUIRE(w_layout == 0 || w_layout == 1, "ternary_linear: weight layout must be 0 (canonical) or 1 (prepared)");
+  if (M == 0) return JB200_OK;   // nothing to do: an empty batch may come with null row pointers
   JB_REQUIRE(x_bf16 && w_packed && alpha && out, "ternary_linear: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_packed) && aligned16(out), "ternary_linear: pointers must be 16-byte aligned");
   if (M == 0) return JB200_OK;

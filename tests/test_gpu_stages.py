@@ -516,3 +516,37 @@ def test_attn_state_only_call_matches_the_full_scan(T):
     qf, kf = orc.feature_map_rope(heads(q), heads(k), 9)
     _, S_ref = orc.attn_scan_recurrent(qf, kf, heads(v), gamma.cpu(), S0.cpu())
     assert rel_l2(S_only, S_ref) <= 1e-2
+
+
+def test_empty_inputs_are_accepted_everywhere():
+    """Zero tokens / zero sequences: every entry point returns empty results without launching on nothing."""
+    dev = "cuda"
+    C, H, E = 128, 2, 4
+    x0 = torch.empty(0, C, dtype=torch.bfloat16, device=dev)
+    q = torch.randint(-1, 2, (128, C)).float()
+    pk = orc.pack_ternary(q).cuda()
+    y = ops.ternary_linear(x0, pk, torch.ones(1, device=dev))
+    assert tuple(y.shape) == (0, 128)
+    offs = torch.zeros(E + 1, dtype=torch.int32, device=dev)
+    yg = ops.ternary_linear_grouped(x0, orc.pack_ternary(torch.zeros(E, 128, C)).cuda(), torch.ones(E, device=dev), offs)
+    assert tuple(yg.shape) == (0, 128)
+    assert tuple(ops.rmsnorm(torch.empty(0, C, device=dev), torch.ones(C, device=dev)).shape) == (0, C)
+    idx, gates, _ = ops.router_top2(x0, torch.randn(E, C, device=dev))
+    assert tuple(idx.shape) == (0, 2) and tuple(gates.shape) == (0, 2)
+    counts, offsets, scatter, gather, gate_idx = ops.moe_metadata(idx, E)
+    assert counts.tolist() == [0] * E and offsets.tolist() == [0] * (E + 1) and gather.numel() == 0
+    disp = ops.dispatch_gather(x0, gather)
+    assert tuple(disp.shape) == (0, C)
+    out = ops.scatter_combine(disp, gates, scatter)
+    assert tuple(out.shape) == (0, C)
+    cos, sin = rope_tabs(8)
+    qkv = torch.empty(0, 3 * H * 64, dtype=torch.bfloat16, device=dev)
+    o, S = ops.attn_scan(qkv[:, :H * 64], qkv[:, H * 64:2 * H * 64], qkv[:, 2 * H * 64:], torch.full((H,), 0.9, device=dev),
+                         cos, sin, 0, 4, H)
+    assert o.shape[0] == 0
+    h, last = ops.lsf_scan(torch.empty(0, 4, C, dtype=torch.bfloat16, device=dev), alpha_scalar=torch.full((1,), 0.5, device=dev))
+    assert h.shape[0] == 0
+    tok = ops.sample(torch.empty(0, 50, device=dev), torch.empty(0, device=dev), temperature=1.0, top_k=5, top_p=0.9)
+    assert tuple(tok.shape) == (0, 1)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
