@@ -181,6 +181,19 @@ def case_moe(a):
         ep.close()
 
 
+def case_router(a):
+    """norm2 + top-2 router fused (rmsnorm_router_kernel) and the plain RMSNorm on N tokens x 1024 channels."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    N, C, E = a.N, 1024, 4
+    x = torch.randn(N, C, generator=g, device="cuda")
+    wn = torch.rand(C, generator=g, device="cuda") + 0.5
+    wr = torch.randn(E, C, generator=g, device="cuda") * 0.05
+    ms = timeit(lambda: ops.rmsnorm_router(x, wn, 1e-6, wr), a.iters)
+    report("rmsnorm_router_kernel", ms, bytes_=6.0 * N * C, extra={"N": N})
+    ms = timeit(lambda: ops.rmsnorm(x, wn, 1e-6), a.iters)
+    report("rmsnorm_kernel", ms, bytes_=6.0 * N * C, extra={"N": N})
+
+
 def case_decode(a):
     """Config 5: ragged state-carrying decode on the 606M model: B sequences, one token per step,
     positions ~ U[1, 4096], carried attention state (B, H, 64, 64) f32 and LSF membrane per layer."""
@@ -322,6 +335,8 @@ def main():
     s = sub.add_parser("decode")
     s.add_argument("--B", type=int, default=256); s.add_argument("--steps", type=int, default=64)
     s.add_argument("--eager", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    s = sub.add_parser("router")
+    s.add_argument("--N", type=int, default=16384)
     s = sub.add_parser("serve")
     s.add_argument("--slots", type=int, default=64); s.add_argument("--requests", type=int, default=256)
     s = sub.add_parser("context")
@@ -335,7 +350,7 @@ def main():
         torch.cuda.set_device(lr)
         dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     {"gemm": case_gemm, "attn": case_attn, "lsf": case_lsf, "moe": case_moe, "decode": case_decode,
-     "context": case_context, "serve": case_serve}[a.case](a)
+     "context": case_context, "serve": case_serve, "router": case_router}[a.case](a)
     if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         import torch.distributed as dist
         if dist.is_initialized():
