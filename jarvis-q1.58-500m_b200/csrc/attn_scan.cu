@@ -67,6 +67,7 @@ struct Smem {
   float pw[CH + 1];                    // gamma^n
   float4 mf[8][32];                    // decay-mask factors of one 16x8 score tile, by (2*warp - key_tile + 1, lane)
   uint64_t full[STAGES];
+  uint64_t full_b;                     // k/v-only pass: barrier of its second stage (the state-mirror buffers)
   uint32_t abort_flag;
 };
 
@@ -119,6 +120,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&sm->full[s]), 1);
+    mbar_init(smem_u32(&sm->full_b), 1);
     sm->abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
@@ -168,42 +170,48 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           S[nt][2] = gL * S[nt][2] + hi.x; S[nt][3] = gL * S[nt][3] + hi.y;
         }
       }
-      *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
-      *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
+      if (!STATE_ONLY) {
+        *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
+        *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
+      }
     }
   }
   __syncthreads();
 
+  // The k/v-only pass has no use for the q tile and the state mirror, so it runs two stages: k, v of odd
+  // chunks land in the two mirror buffers (16 KiB, 1024-byte aligned like the tiles) under their own barrier.
+  constexpr int N_ST = STATE_ONLY ? 2 : STAGES;
   auto issue_chunk = [&](int ck) {  // called by thread 0 only
-    const int s = (ck - ck_begin) % STAGES;
-    const uint32_t bar = smem_u32(&sm->full[s]);
+    const int s = (ck - ck_begin) % N_ST;
+    const bool second = STATE_ONLY && s == 1;
+    const uint32_t bar = smem_u32(second ? &sm->full_b : &sm->full[STATE_ONLY ? 0 : s]);
     mbar_arrive_expect_tx(bar, STATE_ONLY ? 2 * TILE_BYTES : STAGE_BYTES);
-    const uint32_t dst = smem_u32(sm->tiles[s]);
+    const uint32_t dst = smem_u32(sm->tiles[STATE_ONLY ? 0 : s]);
     const int r = row0 + ck * CH;
     if (!STATE_ONLY) tma_load_2d(dst, &tm_q, h * D, r, bar);
-    tma_load_2d(dst + TILE_BYTES, &tm_k, h * D, r, bar);
-    tma_load_2d(dst + 2 * TILE_BYTES, &tm_v, h * D, r, bar);
+    tma_load_2d(second ? smem_u32(sm->s_bf16[0]) : dst + TILE_BYTES, &tm_k, h * D, r, bar);
+    tma_load_2d(second ? smem_u32(sm->s_bf16[1]) : dst + 2 * TILE_BYTES, &tm_v, h * D, r, bar);
   };
   if (tid == 0) {
-    for (int ck = ck_begin; ck < ck_begin + STAGES && ck < ck_end; ++ck) issue_chunk(ck);
+    for (int ck = ck_begin; ck < ck_begin + N_ST && ck < ck_end; ++ck) issue_chunk(ck);
   }
 
   const uint32_t vw_a = smem_u32(sm->vw);
   bool ok = true;
   for (int ck = ck_begin; ck < ck_end; ++ck) {
     const int lc = ck - ck_begin;
-    const int s = lc % STAGES;
+    const int s = lc % N_ST;
+    const bool second = STATE_ONLY && s == 1;
     const int c_len = min(CH, T - ck * CH);
-    const uint32_t q_a = smem_u32(sm->tiles[s]);
-    const uint32_t k_a = q_a + TILE_BYTES, v_a = q_a + 2 * TILE_BYTES;
-    uint8_t* q_p = sm->tiles[s];
-    uint8_t* k_p = q_p + TILE_BYTES;
-    uint8_t* v_p = q_p + 2 * TILE_BYTES;
+    uint8_t* q_p = sm->tiles[STATE_ONLY ? 0 : s];
+    uint8_t* k_p = second ? sm->s_bf16[0] : q_p + TILE_BYTES;
+    uint8_t* v_p = second ? sm->s_bf16[1] : q_p + 2 * TILE_BYTES;
+    const uint32_t q_a = smem_u32(q_p), k_a = smem_u32(k_p), v_a = smem_u32(v_p);
     const uint32_t sb_a = smem_u32(sm->s_bf16[lc & 1]);
     uint8_t* sb_next = sm->s_bf16[(lc + 1) & 1];
 
-    if (!mbar_wait(smem_u32(&sm->full[s]), uint32_t(lc / STAGES) & 1u, &sm->abort_flag, p.status,
-                   JB200_STATUS_ATTN_LOAD)) {
+    if (!mbar_wait(smem_u32(second ? &sm->full_b : &sm->full[STATE_ONLY ? 0 : s]), uint32_t(lc / N_ST) & 1u,
+                   &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) {
       ok = false;
     }
     if (__syncthreads_or(!ok)) break;   // leave together if any thread's wait ran out
@@ -383,7 +391,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     fence_proxy_async_smem();  // order this thread's generic accesses to stage s before the next TMA write into it
     __syncthreads();  // tiles of stage s and vw are free; the new state mirror is complete
-    if (tid == 0 && ck + STAGES < ck_end) issue_chunk(ck + STAGES);
+    if (tid == 0 && ck + N_ST < ck_end) issue_chunk(ck + N_ST);
   }
 
   float* so = nullptr;
