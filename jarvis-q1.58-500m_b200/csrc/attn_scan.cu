@@ -13,7 +13,7 @@
 // The reference's chunk-parallel path instead materialises per-chunk states (B,H,T/64,64,64) twice.
 //
 // Per chunk (c <= 64 tokens, decay tables for the actual c):
-//   TMA (128B-swizzled boxes, 3-stage mbarrier ring)  ->  q, k, v tiles in shared memory
+//   TMA (128B-swizzled boxes; one stage, four CTAs per SM cover each other's latency)  ->  q, k, v tiles in smem
 //   all threads: feature map + RoPE in place on q, k;  Vw = v * gamma^(c-1-j)
 //   warp w (query rows 16w..16w+15), tensor cores via mma.sync m16n8k16 bf16 -> fp32:
 //     O  = (Q S^T) * gamma^(i+1)                 cross-chunk
