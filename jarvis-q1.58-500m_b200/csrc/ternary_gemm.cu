@@ -34,8 +34,10 @@
 //      every 32-bit word the even in-features sit in the low half and the odd ones in the high half,
 //      each as (sign << 1 | nonzero), so (w << (14 - 2j)) & 0xC000C000 IS the bf16 pair
 //      {0, +2.0, -2.0} for in-features (2j, 2j+1): 2 ops / 2 weights; the factor 2 is folded into alpha.
-// The decoders share the SM's issue slots with the epilogue, and the kernel is issue-bound, so the
-// instruction count of the decode is what sets the tensor-pipe utilisation.
+// The decoders, the TMA writes, the tensor core's operand reads and the epilogue all go through the same
+// shared memory and issue slots; per-role cycle counters put the MMA issue interval at 126 cycles (of 128) for
+// K = 4096 and 154 for K = 1024, so the cheap decode and an epilogue that never touches shared memory are what
+// keep the tensor pipe fed.
 #include "common.cuh"
 #include "gemm_shared.cuh"
 #include "launchers.h"
