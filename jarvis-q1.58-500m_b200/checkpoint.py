@@ -57,11 +57,12 @@ def load_packed_state_dict(model: torch.nn.Module, packed_sd: dict) -> torch.nn.
     if dev.type != "cuda":
         raise RuntimeError("load_packed_state_dict: move the model to a CUDA device first")
     plain, tern = {}, {}
+    cleaned = {_clean(key) for key in packed_sd}     # pair `.alpha` with `.packed_weight` on the cleaned names
     for key, value in packed_sd.items():
         k = _clean(key)
         if k.endswith(".packed_weight"):
             tern.setdefault(k[: -len(".packed_weight")], {})["packed"] = value
-        elif k.endswith(".alpha") and k[: -len(".alpha")] + ".packed_weight" in packed_sd:
+        elif k.endswith(".alpha") and k[: -len(".alpha")] + ".packed_weight" in cleaned:
             tern.setdefault(k[: -len(".alpha")], {})["alpha"] = value
         else:
             plain[k] = value
@@ -85,6 +86,11 @@ def load_packed_state_dict(model: torch.nn.Module, packed_sd: dict) -> torch.nn.
         missing = [k for k, v in own.items() if is_ternary_key(k, v) and k not in entries]
         if missing:
             raise KeyError(f"load_packed_state_dict: missing packed weights for {missing[:3]} ...")
+        # everything else the model owns (norms, router, embedding, lm_head, decay, buffers of the state dict)
+        # must come from the file too: a silently kept constructor value would run, and be wrong
+        absent = [k for k in own if k not in plain and k not in entries]
+        if absent:
+            raise KeyError(f"load_packed_state_dict: the file lacks {absent[:3]}{' ...' if len(absent) > 3 else ''}")
     mods = dict(model.named_modules())
     for name, mod in mods.items():
         pre = name + "." if name else ""

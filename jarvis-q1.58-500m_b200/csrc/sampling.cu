@@ -47,6 +47,7 @@ struct SampleSmem {
   unsigned int prefix;       // key bits fixed so far
   unsigned int remaining;    // rank still to find inside the current bucket
   unsigned int count;        // candidates gathered
+  unsigned int ties;         // elements whose key equals the k-th key
   float red_val[SAMPLE_THREADS / 32];
   int red_idx[SAMPLE_THREADS / 32];
 };
@@ -109,20 +110,50 @@ sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, in
       }
       sm.prefix = prefix | (unsigned(b) << shift);
       sm.remaining = rem;
+      sm.ties = sm.hist[b];              // after the last pass: the elements equal to the k-th value
     }
     __syncthreads();
   }
   const uint32_t kth_key = sm.prefix;
 
-  // ---- gather the survivors (key >= k-th key), in index order inside each thread's stride ---------------
+  // ---- gather the survivors (key >= k-th key) -------------------------------------------------------------
+  // Strictly larger values number at most k - 1 <= 1023 and always fit.  When they and the values EQUAL to the
+  // k-th one fit the buffer together, arrival order does not matter (the sort below fixes it).  When a long run
+  // of equal values would overflow it (constant or degenerate rows), the larger values are taken first and the
+  // equal ones follow in ascending token id until the buffer is full, so the result stays a function of
+  // (logits, u) and the argmax can never be crowded out.
+  const bool overflow = (k - sm.remaining) + sm.ties > unsigned(SAMPLE_CAP);
   for (int i = tid; i < V; i += SAMPLE_THREADS) {
     const float x = load_logit<T>(row, i) * inv_t;
-    if (float_key(x) >= kth_key) {
+    const uint32_t key = float_key(x);
+    if (overflow ? key > kth_key : key >= kth_key) {
       const unsigned int slot = atomicAdd(&sm.count, 1u);
       if (slot < SAMPLE_CAP) { sm.val[slot] = (x != x) ? -INFINITY : x; sm.idx[slot] = i; }
     }
   }
   __syncthreads();
+  if (overflow) {
+    for (int i0 = 0; i0 < V; i0 += SAMPLE_THREADS) {
+      const unsigned int base = sm.count;            // stable: written only between the barriers below
+      if (base >= unsigned(SAMPLE_CAP)) break;
+      const int i = i0 + tid;
+      const float x = i < V ? load_logit<T>(row, i) * inv_t : 0.f;
+      const bool tie = i < V && float_key(x) == kth_key;
+      const unsigned int bal = __ballot_sync(0xffffffffu, tie);
+      if (lane == 0) sm.red_idx[warp] = __popc(bal);
+      __syncthreads();
+      unsigned int before = 0, total = 0;
+      for (int w = 0; w < SAMPLE_THREADS / 32; ++w) {
+        if (w < warp) before += unsigned(sm.red_idx[w]);
+        total += unsigned(sm.red_idx[w]);
+      }
+      const unsigned int slot = base + before + __popc(bal & ((1u << lane) - 1u));
+      if (tie && slot < unsigned(SAMPLE_CAP)) { sm.val[slot] = x; sm.idx[slot] = i; }
+      __syncthreads();
+      if (tid == 0) sm.count = base + total;
+      __syncthreads();
+    }
+  }
   const int n = int(min(sm.count, unsigned(SAMPLE_CAP)));
   int n2 = 1;
   while (n2 < n) n2 <<= 1;

@@ -671,9 +671,26 @@ def install(model: nn.Module) -> nn.Module:
     attribute-replacement mechanism (experiments/architecture_matrix/modular_memory.py:353-368)."""
 
     def adopt(dst: nn.Module, src: nn.Module):
-        missing = dst.load_state_dict(src.state_dict(), strict=False)
-        if missing.missing_keys:
-            raise RuntimeError(f"install: source module lacks {missing.missing_keys}")
+        # the SAME Parameter / buffer objects are attached to the new module: no second copy of the weights,
+        # and later in-place updates of the model's tensors (or `.to(device)` on the model) reach it
+        src_params, src_bufs = dict(src.named_parameters()), dict(src.named_buffers())
+        missing = [k for k in dst.state_dict() if k not in src_params and k not in src_bufs]
+        if missing:
+            raise RuntimeError(f"install: source module lacks {missing}")
+        for name in [n for n, _ in dst.named_parameters()]:
+            owner, leaf = dst, name
+            while "." in leaf:
+                head, leaf = leaf.split(".", 1)
+                owner = getattr(owner, head)
+            owner._parameters[leaf] = src_params[name]
+        for name in [n for n, _ in dst.named_buffers()]:
+            if name not in src_bufs:
+                continue                 # non-persistent caches of the new module (RoPE tables)
+            owner, leaf = dst, name
+            while "." in leaf:
+                head, leaf = leaf.split(".", 1)
+                owner = getattr(owner, head)
+            owner._buffers[leaf] = src_bufs[name]
         return dst.to(next(src.parameters()).device).eval()
 
     for blk in model.blocks:

@@ -20,6 +20,12 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+def _overlap(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when the memory of two contiguous tensors intersects (same tensor, views, slices of one buffer)."""
+    a0, b0 = a.data_ptr(), b.data_ptr()
+    return a0 < b0 + b.numel() * b.element_size() and b0 < a0 + a.numel() * a.element_size()
+
+
 def _need(t: torch.Tensor, dtype, name: str) -> torch.Tensor:
     if not t.is_cuda:
         raise RuntimeError(f"{name}: expected a CUDA tensor (this path has no CPU fallback)")
@@ -283,8 +289,8 @@ def attn_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gamma: torch.Te
         # may alias state_in when the call runs one segment per sequence (every CTA reads its own
         # (sequence, head) state before it writes it): the decode step updates states in place
         s_out = _need(state_out, torch.float32, "attn_scan.state_out")
-        if state_out is state_in:
-            segmented = False
+        if state_in is not None and _overlap(state_out, state_in):
+            segmented = False      # also for two views of one buffer: segment CTAs would read what the last one writes
     else:
         s_out = torch.empty((B, H, 64, 64), dtype=torch.float32, device=q.device) if want_state else None
     scratch = None
@@ -414,7 +420,7 @@ def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=N
     out = torch.empty((B, T, D), dtype=out_dtype or m.dtype, device=m.device) if want_out else None
     if last_out is not None:
         h_last = _need(last_out, torch.float32, "lsf_scan.last_out")   # may alias h0 in unsegmented calls
-        if last_out is h0:
+        if h0 is not None and _overlap(last_out, h0):
             segmented = False
     else:
         h_last = torch.empty((B, D), dtype=torch.float32, device=m.device) if want_last else None

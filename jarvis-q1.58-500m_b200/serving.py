@@ -40,11 +40,14 @@ class Request:
         self.is_finished = False
         self.arrival_time = time.time()
         self.finish_time: Optional[float] = None
+        self.error: Optional[str] = None
 
 
 class ContinuousBatchingScheduler:
     """Slot policy of exp_batching_continuous.py:141-177 over an engine with
-    `admit(slot, prompt_tokens)`, `release(slot)` and `step(active_slots) -> {slot: token}`."""
+    `admit(slot, prompt_tokens, max_new_tokens)`, `release(slot)` and `step(active_slots) -> {slot: token}`.
+    A request the engine refuses (ValueError from `admit`: its positions would run past the engine's limit)
+    is retired at once, unfinished, with the message in `req.error`; the slot goes to the next request."""
 
     def __init__(self, engine, max_batch_size: int = 8, eos_token: Optional[int] = None):
         self.engine = engine
@@ -61,9 +64,15 @@ class ContinuousBatchingScheduler:
         """One iteration: fill empty slots, advance every active request by one token, retire the finished.
         Returns the number of requests advanced (0 when idle)."""
         for slot in range(self.max_batch_size):
-            if slot not in self.active_slots and self.waiting_queue:
+            while slot not in self.active_slots and self.waiting_queue:
                 req = self.waiting_queue.popleft()
-                self.engine.admit(slot, req.prompt_tokens)
+                try:
+                    self.engine.admit(slot, req.prompt_tokens, req.max_new_tokens)
+                except ValueError as exc:
+                    req.error = str(exc)
+                    req.finish_time = time.time()
+                    self.completed.append(req)
+                    continue
                 self.active_slots[slot] = req
         if not self.active_slots:
             return 0
@@ -135,10 +144,13 @@ class CudaDecodeEngine:
         self.session.positions[slot] = 0
         self.next_token[slot, 0] = self.pad_token
 
-    def admit(self, slot: int, prompt_tokens: List[int]):
-        """Prefill prompt[:-1] into the slot's state; the step of this iteration consumes prompt[-1]."""
-        if len(prompt_tokens) > self.max_position:
-            raise ValueError(f"prompt of {len(prompt_tokens)} tokens exceeds max_position={self.max_position}")
+    def admit(self, slot: int, prompt_tokens: List[int], max_new_tokens: int = 0):
+        """Prefill prompt[:-1] into the slot's state; the step of this iteration consumes prompt[-1].
+        The RoPE table captured in the step's graph has `max_position` rows and the kernels clamp positions
+        to it silently, so a request whose last generated token would sit beyond the table is refused here."""
+        if len(prompt_tokens) + max(int(max_new_tokens), 0) > self.max_position:
+            raise ValueError(f"prompt of {len(prompt_tokens)} tokens + {max_new_tokens} new tokens exceeds "
+                             f"max_position={self.max_position}")
         if len(prompt_tokens) == 1:
             self._zero_slot(slot)           # longer prompts overwrite every tensor of the slot below
         if len(prompt_tokens) > 1:

@@ -4,6 +4,9 @@ Run where the reference tree is mounted:
     PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference   (or JARVIS_REFERENCE=...)
 The fixtures are committed; the tests never need the reference tree.  Inputs are seeded
 synthetic tensors; every stored output was produced by reference code, never by this repo.
+Every golden_* function seeds the global RNG itself, so each .npz regenerates bit for bit whatever
+ran before it; the one varying byte range is the `created_at` time stamp that the reference's exporter
+writes into the manifest of tiny.jarvis-tbin.
 """
 import os
 import sys
@@ -58,13 +61,17 @@ def grid_randn(shape, gen):
 
 
 def ternary_init(module, gen):
+    """Every ternary matrix (q/k/v/out projections, expert w1 / w2) gets grid weights; names are matched with a
+    leading dot so that a bare SparseMoELayer (`w1.0.weight`) is covered like a block (`moe.w1.0.weight`)."""
     for name, p in module.named_parameters():
-        if name.endswith("proj.weight") or ".w1." in name or ".w2." in name:
+        dotted = "." + name
+        if name.endswith("proj.weight") or ".w1." in dotted or ".w2." in dotted:
             p.copy_(grid_randn(p.shape, gen))
 
 
 # ---- 1. ternary quantisation + packing --------------------------------------------------
 def golden_pack():
+    torch.manual_seed(101)   # constructors below draw from the global RNG
     gen = torch.Generator().manual_seed(1)
     w = torch.randn(96, 64, generator=gen) * 0.02
     w[0, :6] = torch.tensor([0.0, 1e-9, -1.0, 1.0, 0.5, -0.5])
@@ -85,6 +92,7 @@ def golden_pack():
 
 # ---- 2. attention ---------------------------------------------------------------------
 def golden_attention():
+    torch.manual_seed(102)   # constructors below draw from the global RNG
     d_model, H = 128, 2
     out = {}
     gen = torch.Generator().manual_seed(42)
@@ -140,6 +148,7 @@ def golden_attention():
 
 # ---- 3. MoE ---------------------------------------------------------------------------
 def golden_moe():
+    torch.manual_seed(103)   # constructors below draw from the global RNG
     d_model = 128
     out = {}
     cases = [("b1t16", 1, 16, None), ("b2t64", 2, 64, None), ("all_e0", 2, 32, "all0"), ("e0_empty", 2, 32, "empty0"),
@@ -182,6 +191,7 @@ def golden_moe():
 
 # ---- 4. LSF ---------------------------------------------------------------------------
 def golden_lsf():
+    torch.manual_seed(104)   # constructors below draw from the global RNG
     out = {}
     gen = torch.Generator().manual_seed(3)
     m = jm.LiquidStateFusion(32).eval()
@@ -209,6 +219,7 @@ def golden_lsf():
 
 # ---- 5. block and a tiny model -----------------------------------------------------------
 def golden_block_model():
+    torch.manual_seed(105)   # constructors below draw from the global RNG
     gen = torch.Generator().manual_seed(0)
     blk = jm.JarvisBlock(128, 2, 4, 2, use_cuda_attn=False, use_cuda_moe=False).eval()
     ternary_init(blk, gen)
@@ -237,6 +248,7 @@ def golden_block_model():
 
 # ---- 6. the .jarvis-tbin container, written and re-read by the reference's own code ---------------
 def golden_tbin():
+    torch.manual_seed(106)   # constructors below draw from the global RNG
     sys.path.insert(0, os.path.join(REF, "experiments", "architecture_matrix", "ternary_packed"))
     import jarvis_tbin_format as tb
     gen = torch.Generator().manual_seed(77)
@@ -273,6 +285,7 @@ def _reference_defs(path, names):
 
 
 def golden_sampling():
+    torch.manual_seed(107)   # constructors below draw from the global RNG
     ns = _reference_defs(os.path.join(REF, "jarvis_engine", "evaluate_jarvis.py"), {"sample_next_token"})
     gen = torch.Generator().manual_seed(2024)
     B, V = 6, 512
@@ -301,6 +314,7 @@ def golden_sampling():
 
 
 def golden_scheduler():
+    torch.manual_seed(108)   # constructors below draw from the global RNG
     ns = _reference_defs(os.path.join(REF, "experiments", "exp_batching_continuous.py"),
                          {"Request", "ContinuousBatchingScheduler"})
     sched = ns["ContinuousBatchingScheduler"](max_batch_size=4, device="cpu")
@@ -329,4 +343,4 @@ if __name__ == "__main__":
     golden_block_model()
     golden_sampling()
     golden_scheduler()
-    golden_tbin()   # last: building its models draws from the global RNG that later fixtures would see
+    golden_tbin()

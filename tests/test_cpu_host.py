@@ -99,10 +99,14 @@ def test_install_keeps_reference_state_dict_keys():
                        use_cuda_moe=False).eval()
     keys = list(model.state_dict().keys())
     weights = {k: v.clone() for k, v in model.state_dict().items()}
+    params_before = dict(model.named_parameters())
     jarvis_b200.install(model)
     assert list(model.state_dict().keys()) == keys
     for k, v in model.state_dict().items():
         assert torch.equal(v, weights[k]), k
+    # shared, not copied: the installed modules hold the very Parameter objects the model had
+    for k, p in model.named_parameters():
+        assert p is params_before[k], k
     assert isinstance(model.blocks[0].attn, jm.AssociativeLinearAttention)
     assert isinstance(model.blocks[1].moe, jm.SparseMoELayer)
 

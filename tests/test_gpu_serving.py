@@ -64,6 +64,32 @@ def test_sampling_kernel_frequencies_follow_the_filtered_distribution():
     assert (freq - want).abs().max() < 0.02
 
 
+def test_sampling_long_runs_of_equal_logits_keep_the_largest_and_stay_deterministic():
+    """More equal values at the k-th rank than the kernel's candidate buffer holds (a constant row with one
+    larger entry): the larger entry must survive, the equal ones are taken in ascending token id, and the same
+    (logits, u) always gives the same token."""
+    V = 6000
+    row = torch.zeros(4, V)
+    row[0, 4321] = 5.0          # argmax hidden behind thousands of ties
+    row[1, 17] = 1.0
+    row[2, V - 1] = 2.0
+    # row 3: all equal
+    u = torch.tensor([0.0, 0.999, 0.5, 0.25])
+    dev = row.cuda()
+    first = ops.sample(dev, u.cuda(), temperature=1.0, top_k=50, top_p=1.0)
+    for _ in range(5):
+        assert torch.equal(ops.sample(dev, u.cuda(), temperature=1.0, top_k=50, top_p=1.0), first)
+    assert int(first[0]) == 4321                                   # u = 0 picks the most probable token
+    tok, prob = ops.sample(dev, torch.zeros(4).cuda(), temperature=1.0, top_k=50, top_p=1.0, want_prob=True)
+    assert tok.view(-1).tolist()[:3] == [4321, 17, V - 1] and int(tok[3]) == 0
+    # kept set = the larger value + the first 2047 equal tokens by id: u close to 1 lands on the last kept id
+    last = ops.sample(dev, torch.full((4,), 0.999999).cuda(), temperature=1.0, top_k=50, top_p=1.0).view(-1).tolist()
+    assert last[3] == 2047 and last[1] in (2046, 2047) and last[0] == 2046
+    # greedy path for comparison
+    assert ops.sample(dev, None, temperature=0.0).view(-1).tolist() == [4321, 17, V - 1, 0]
+    assert _lib.device_status() == 0
+
+
 def test_sampling_argument_errors():
     x = torch.zeros(2, 100, device="cuda")
     with pytest.raises(RuntimeError, match="top_k"):

@@ -1,6 +1,7 @@
 """CPU tests of the decode driver's host logic: the oracle's sampling filter against the distribution the
 reference's sample_next_token builds (golden fixture), and the slot policy against the trace of the
 reference's ContinuousBatchingScheduler."""
+import pytest
 import torch
 
 import jarvis_b200  # noqa: F401  (alias of the package directory)
@@ -52,10 +53,13 @@ def test_oracle_inverse_cdf_draw():
 class _FakeEngine:
     """Stands in for the CUDA engine: every active slot gets token 42, like the reference's simulation."""
 
-    def __init__(self):
+    def __init__(self, limit=None):
         self.admitted, self.released = [], []
+        self.limit = limit
 
-    def admit(self, slot, prompt_tokens):
+    def admit(self, slot, prompt_tokens, max_new_tokens=0):
+        if self.limit is not None and len(prompt_tokens) + max_new_tokens > self.limit:
+            raise ValueError("too long")
         self.admitted.append((slot, tuple(prompt_tokens)))
 
     def release(self, slot):
@@ -87,6 +91,29 @@ def test_slot_policy_matches_reference_scheduler_trace():
     assert all(r.generated_tokens == [42] * len(r.generated_tokens) for r in reqs)
     assert len(eng.admitted) == 10 and sorted(eng.released) == sorted(s for s, _ in eng.admitted)
     assert sched.step() == 0      # idle
+
+
+def test_requests_that_would_outrun_the_position_table_are_refused():
+    """prompt + max_new_tokens beyond the engine's limit: retired unfinished with an error, the slot is reused."""
+    eng = _FakeEngine(limit=8)
+    sched = serving.ContinuousBatchingScheduler(eng, max_batch_size=1)
+    sched.add_request(serving.Request(0, [1, 2, 3], max_new_tokens=6))      # 9 > 8: refused
+    sched.add_request(serving.Request(1, [1, 2, 3], max_new_tokens=5))      # 8: fits
+    sched.run()
+    by_id = {r.req_id: r for r in sched.completed}
+    assert by_id[0].error is not None and not by_id[0].is_finished and by_id[0].generated_tokens == []
+    assert by_id[1].error is None and by_id[1].is_finished and len(by_id[1].generated_tokens) == 5
+    assert eng.admitted == [(0, (1, 2, 3))]
+
+
+def test_cuda_engine_admit_checks_prompt_plus_new_tokens():
+    """CudaDecodeEngine.admit refuses before touching the device (no GPU needed to check the rule)."""
+    eng = serving.CudaDecodeEngine.__new__(serving.CudaDecodeEngine)
+    eng.max_position = 16
+    with pytest.raises(ValueError, match="exceeds max_position"):
+        eng.admit(0, list(range(10)), max_new_tokens=7)
+    with pytest.raises(ValueError, match="exceeds max_position"):
+        eng.admit(0, list(range(17)))
 
 
 def test_eos_token_retires_early():
