@@ -1,4 +1,4 @@
-// Scalar-decay associative linear-attention causal scan, fused with its prologue.
+// Scalar-decay associative linear-attention causal scan on the 5th-generation tensor cores, fused with its prologue.
 //
 //   q <- (ELU(q)+1)/sqrt(D),  k <- ELU(k)+1,  half-split RoPE on both   (jarvis_model.py:124-128, :29-71;
 //                                                                      fused kernel A1, associative_attention_cuda.cu:28-112)
@@ -6,26 +6,33 @@
 //   optional initial state S_in and final state S_out (B, H, D_v, D_k)  (associative_attention.py:126-152, :273-308;
 //                                                                      kernel A3, associative_attention_cuda.cu:218-265)
 //
-// One CTA per (sequence, head, segment) walks its part of the sequence in 64-token chunks.  The state S never leaves
-// the SM: it is carried in fp32 accumulator registers (one 16-row band per warp) and mirrored
-// as bf16 in shared memory for the cross-chunk product, so HBM traffic is the algorithmic
-// q, k, v in / o out (512 B per token-head) plus one optional state load/store per sequence-head.
-// The reference's chunk-parallel path instead materialises per-chunk states (B,H,T/64,64,64) twice.
+// The reference's chunk-parallel path does the four chunk products as batched library GEMMs over materialised
+// per-chunk states (associative_attention.py:242-266).  Here one CTA per (sequence, head, segment) walks its part
+// of the sequence in 128-token chunks and issues the same four products as tcgen05.mma (bf16 operands from shared
+// memory, fp32 accumulators in tensor memory); the state S never leaves the SM (fp32 master copy in registers,
+// bf16 copy in shared memory as an MMA operand), so HBM traffic is q, k, v in / o out (512 B per token-head)
+// plus one optional state load / store per (sequence, head).  Chunk length is free: the chunked form equals
+// the recurrence for any length, only rounding differs.
 //
-// Per chunk (c <= 64 tokens, decay tables for the actual c):
-//   TMA (128B-swizzled boxes; one stage, four CTAs per SM cover each other's latency)  ->  q, k, v tiles in smem
-//   all threads: feature map + RoPE in place on q, k;  Vw = v * gamma^(c-1-j)
-//   warp w (query rows 16w..16w+15), tensor cores via mma.sync m16n8k16 bf16 -> fp32:
-//     O  = (Q S^T) * gamma^(i+1)                 cross-chunk
-//     A  = (Q K^T) o gamma^(i-j) [j <= i]         only the causal n-tiles are computed
-//     O += A V                                    intra-chunk
-//   warp w (state rows dv 16w..16w+15):  S = gamma^c S + Vw^T K
+// Per chunk of c <= 128 tokens (i, j: query / key token inside the chunk; g = gamma):
+//   TMA (128B-swizzled [128 tokens][64] boxes)                        ->  q, k, v tiles in shared memory
+//   all threads: feature map + RoPE in place on q and k;  kw[j] = k'[j] * g^(c-1-j)
+//   MMA  A:  scores = Q' K'^T       (M=128 i, N=128 j, K=64; both operands K-major)             -> TMEM [0,128)
+//            O2     = Q' S^T        (M=128 i, N=64 dv, K=64; S bf16 [dv][dk] is K-major)        -> TMEM [128,192)
+//   MMA  S:  dS     = V^T Kw        (M=dv, N=dk, K=128 j; both operands are the [token][64] tiles read
+//                                    MN-major; M is padded to 128 by reading the 64 dv twice)    -> TMEM [192,256)
+//   all threads: P[i][j] = scores * g^(i-j) / 8 for j <= i, else 0      (TMEM -> registers -> bf16 tile in smem)
+//   MMA  B:  O1     = P V           (M=128 i, N=64 dv, K=128 j; V read MN-major from its raw tile) -> TMEM [0,64)
+//   all threads: S = g^c S + dS (registers; bf16 copy to smem);   o[i] = O1 + g^(i+1)/8 * O2  -> global
+// One thread issues the TMA loads and the MMAs; every wait (TMA arrival, MMA completion) is an mbarrier wait
+// bounded in time.  256 TMEM columns, 105 KiB of shared memory and <= 128 registers per thread let two CTAs
+// share an SM and cover each other's latencies.
 //
-// Sequence segments: when B*H alone cannot fill the GPU (prefill of a few long sequences), T is cut
-// into segments.  A first launch (STATE_ONLY) runs only the k/v half of the work for every non-final
-// segment from a zero state and stores its contribution D_s; the main launch starts segment s from
+// Sequence segments: when B*H alone cannot fill the GPU (prefill of a few long sequences), T is cut into
+// segments.  A first launch (STATE_ONLY) runs only the k/v half of the work for every non-final segment from a
+// zero state and stores its contribution D_s; the main launch starts segment s from
 // S = fold_{s' < s}(gamma^L S + D_s'), which is exact because the recurrence is linear in S.
-// Extra HBM traffic: k and v are read twice (the second time mostly from L2).
+// Extra HBM traffic: k and v of the non-final segments are read twice (the second time mostly from L2).
 #include "common.cuh"
 #include "launchers.h"
 
@@ -34,11 +41,12 @@ namespace jb {
 namespace {
 
 constexpr int D = 64;             // head dim (fixed by the path: 16 heads x 64)
-constexpr int CH = 64;            // chunk length, AssociativeLinearAttention.CHUNK_SIZE
-constexpr int STAGES = 1;             // 49 KiB of shared memory and 128 registers per CTA -> four CTAs per SM, which cover each other's load latency
-constexpr int TILE_BYTES = CH * D * 2;          // 8 KiB
-constexpr int STAGE_BYTES = 3 * TILE_BYTES;     // q, k, v
-constexpr int ATTN_THREADS = 128;
+constexpr int CH = 128;           // tokens per chunk = rows of one MMA tile
+constexpr int TILE_BYTES = CH * D * 2;          // 16 KiB: [128 tokens][64 bf16], 128B-swizzled
+constexpr int S_BYTES = D * D * 2;              // 8 KiB: bf16 state [dv][dk]
+constexpr int ATTN_THREADS = 256;
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TM_SCORES = 0, TM_O1 = 0, TM_O2 = 128, TM_DS = 192;
 
 struct AttnParams {
   const float* gamma;      // [H] decay in (0,1)
@@ -54,51 +62,73 @@ struct AttnParams {
   int B, T, H;
   int seg_chunks;          // chunks per sequence segment (grid.z walks the segments)
   int nseg;
-  float* seg_state;        // [B][H][nseg-1][64][64]: state contribution of each non-final segment
-  int n_pieces;            // state contributions stored per (sequence, head): nseg - 1, or nseg in a state-only call
+  float* seg_state;        // [B][H][n_pieces][64][64]: state contribution of each piece
+  int n_pieces;            // pieces stored per (sequence, head): nseg - 1, or nseg in a state-only call
   int qk_prepared;         // q, k already hold phi(.) + RoPE with the head dim interleaved (d, d+32 adjacent)
+  int wide_store;          // output rows are 32-byte aligned: 256-bit stores
   unsigned int* status;
 };
 
 struct Smem {
-  uint8_t tiles[STAGES][STAGE_BYTES];  // [stage][q|k|v][64 rows x 128 B, 128B-swizzled]
-  uint8_t vw[TILE_BYTES];              // v * gamma^(c-1-j)
-  uint8_t s_bf16[2][TILE_BYTES];       // state mirror [dv][dk], double buffered
-  float pw[CH + 1];                    // gamma^n
-  float4 mf[8][32];                    // decay-mask factors of one 16x8 score tile, by (2*warp - key_tile + 1, lane)
-  uint64_t full[STAGES];
-  uint64_t full_b;                     // k/v-only pass: barrier of its second stage (the state-mirror buffers)
+  uint8_t q[TILE_BYTES];       // state-only pass: second stage of k
+  uint8_t k[TILE_BYTES];
+  uint8_t kw[TILE_BYTES];
+  uint8_t v[TILE_BYTES];
+  uint8_t p[2][TILE_BYTES];    // P as two K-major tiles (keys 0-63, 64-127); state-only pass: p[0] = second stage of v
+  uint8_t s[S_BYTES];
+  float pwm[2 * CH];           // pwm[x + CH] = gamma^x / 8 for x >= 0, 0 for x < 0: the decay mask by (i - j)
+  float pw[CH + 1];            // gamma^n
+  uint64_t bar_qk[2], bar_v[2], bar_a, bar_s, bar_b;
+  uint32_t tmem_base;
   uint32_t abort_flag;
 };
 
 constexpr size_t ATTN_SMEM_BYTES = sizeof(Smem) + 1024;
 
-__device__ __forceinline__ uint32_t swz(int row, int chunk16) {  // byte offset inside a swizzled 64x128B tile
+__device__ __forceinline__ uint32_t swz(int row, int chunk16) {  // byte offset inside a swizzled [rows][128 B] tile
   return uint32_t(row) * 128u + (uint32_t(chunk16 ^ (row & 7)) << 4);
 }
 
-__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+// Shared-memory matrix descriptor, 128-byte swizzle.  K-major operands (rows of 64 K-elements): lbo is unused
+// (16), sbo = 1024 is the distance between 8-row groups.  MN-major operands (a [K rows][64 MN-elements] tile):
+// sbo = 1024 is the distance between groups of 8 K rows, lbo the distance between blocks of 64 MN-elements.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
 }
-__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+// kind::f16 instruction descriptor: bf16 operands, fp32 accumulator; a_mn / b_mn = 1 reads that operand MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n, int a_mn, int b_mn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn) << 15) | (uint32_t(b_mn) << 16) |
+         (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
-// ELU(x)+1 = x+1 for x > 0, exp(x) otherwise; branch-free, exp through ex2.approx (rel. error 2^-22,
-// far below the bf16 rounding of the result).  For large positive x the unused exp is +inf, never NaN.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void st_global_256(void* p, const uint32_t* w) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7])
+               : "memory");
+}
+
+// ELU(x)+1 = x+1 for x > 0, exp(x) otherwise; exp through ex2.approx (rel. error 2^-22, far below the bf16
+// rounding of the result).  For large positive x the unused exp is +inf, never NaN.
 __device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(x); }
 
 template <bool STATE_ONLY>
-__global__ void __launch_bounds__(ATTN_THREADS, 4)
+__global__ void __launch_bounds__(ATTN_THREADS, 2)
 attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -107,6 +137,8 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   Smem* sm = reinterpret_cast<Smem*>(smem_raw + (base - raw_addr));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int qd = warp & 3;          // TMEM lane quarter this warp may access: lanes 32*qd .. 32*qd+31
+  const int hf = warp >> 2;         // which half of the columns this warp takes
   const int h = blockIdx.x, b = blockIdx.y;
   const int T = p.T;
   const int n_chunks = (T + CH - 1) / CH;
@@ -119,300 +151,334 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const float log_g = logf(gamma);
 
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(smem_u32(&sm->full[s]), 1);
-    mbar_init(smem_u32(&sm->full_b), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&sm->bar_qk[s]), 1);
+      mbar_init(smem_u32(&sm->bar_v[s]), 1);
+    }
+    mbar_init(smem_u32(&sm->bar_a), 1);
+    mbar_init(smem_u32(&sm->bar_s), 1);
+    mbar_init(smem_u32(&sm->bar_b), 1);
     sm->abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
+  if (warp == 0) {
+    __syncwarp();                 // tcgen05.alloc is warp-collective: lane 0 rejoins from the barrier set-up first
+    tmem_alloc(smem_u32(&sm->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
   for (int n = tid; n <= CH; n += ATTN_THREADS) sm->pw[n] = expf(log_g * float(n));
-  for (int e = tid; e < 8 * 32; e += ATTN_THREADS) {
-    const int d = e >> 5, ln = e & 31;
-    const int diff0 = 8 * (d - 1) + (ln >> 2) - 2 * (ln & 3);   // query row - key column of c0
+  for (int n = tid; n < 2 * CH; n += ATTN_THREADS) {
     // gamma^(i-j) / sqrt(D): the 1/8 of the query feature map is a power of two, so applying it to the scores
-    // (here and in the cross-chunk factor below) instead of to every element of q gives the same bits
-    auto fac = [&](int x) { return x >= 0 ? 0.125f * expf(log_g * float(x)) : 0.f; };
-    sm->mf[d][ln] = make_float4(fac(diff0), fac(diff0 - 1), fac(diff0 + 8), fac(diff0 + 7));
+    // (and to the cross-chunk factor) instead of to every element of q gives the same bits
+    const int x = n - CH;
+    sm->pwm[n] = x >= 0 ? 0.125f * expf(log_g * float(x)) : 0.f;
+  }
+  if (!STATE_ONLY) {
+    // blocks of P above the diagonal are never written again: zero the tile once
+    uint4* pz = reinterpret_cast<uint4*>(sm->p[0]);
+    for (int e = tid; e < 2 * TILE_BYTES / 16; e += ATTN_THREADS) pz[e] = make_uint4(0u, 0u, 0u, 0u);
   }
 
-  // state: fp32 accumulators, rows dv = 16*warp + lane/4 (+8), cols dk = 8*nt + 2*(lane%4) (+1)
-  float S[8][4];
+  // state: fp32 master copy in registers.  Thread (qd, hf, lane) owns row dv = 32*(qd&1) + lane, columns
+  // dk = 16*cg .. 16*cg+15 with cg = 2*(qd>>1) + hf: the accumulator of MMA S holds the 64 dv rows twice (lanes
+  // 0-63 and 64-127), so all eight warps read their share of it from their own lane quarter.
+  const int s_row = 32 * (qd & 1) + lane;
+  const int s_cg = 2 * (qd >> 1) + hf;
+  float S[16];
   {
-    const int r = 16 * warp + (lane >> 2);
-    const int cb = 2 * (lane & 3);
-    const float* sin_p = (!STATE_ONLY && p.s_in) ? p.s_in + (size_t(b) * p.H + h) * D * D : nullptr;
+    const size_t bh = size_t(b) * p.H + h;
+    const float* sin_p = (!STATE_ONLY && p.s_in) ? p.s_in + bh * D * D + s_row * D : nullptr;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int c = nt * 8 + cb;
-      if (sin_p && p.qk_prepared) {
-        // the kernel's dk axis is the interleaved one (column 2i = feature i, 2i + 1 = feature i + 32);
-        // states cross the API in the natural order
-        const int d = c >> 1;
-        S[nt][0] = __ldg(sin_p + r * D + d);        S[nt][1] = __ldg(sin_p + r * D + d + 32);
-        S[nt][2] = __ldg(sin_p + (r + 8) * D + d);  S[nt][3] = __ldg(sin_p + (r + 8) * D + d + 32);
-      } else if (sin_p) {
-        const float2 lo = __ldg(reinterpret_cast<const float2*>(sin_p + r * D + c));
-        const float2 hi = __ldg(reinterpret_cast<const float2*>(sin_p + (r + 8) * D + c));
-        S[nt][0] = lo.x; S[nt][1] = lo.y; S[nt][2] = hi.x; S[nt][3] = hi.y;
-      } else {
-        S[nt][0] = S[nt][1] = S[nt][2] = S[nt][3] = 0.f;
-      }
-      if (!STATE_ONLY && seg > 0) {
-        // state entering this segment: fold the earlier segments' contributions, oldest first
-        const float gL = expf(log_g * float(p.seg_chunks * CH));
-        const float* dp = p.seg_state + (size_t(b) * p.H + h) * p.n_pieces * D * D;
-        for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
-          const float2 lo = __ldg(reinterpret_cast<const float2*>(dp + r * D + c));
-          const float2 hi = __ldg(reinterpret_cast<const float2*>(dp + (r + 8) * D + c));
-          S[nt][0] = gL * S[nt][0] + lo.x; S[nt][1] = gL * S[nt][1] + lo.y;
-          S[nt][2] = gL * S[nt][2] + hi.x; S[nt][3] = gL * S[nt][3] + hi.y;
+    for (int e = 0; e < 16; ++e) {
+      const int c = 16 * s_cg + e;
+      // prepared q/k: the kernel's dk axis is the interleaved one (column 2i = feature i, 2i + 1 = feature i + 32);
+      // states cross the API in the natural order
+      const int d = p.qk_prepared ? (c >> 1) + 32 * (c & 1) : c;
+      S[e] = sin_p ? __ldg(sin_p + d) : 0.f;
+    }
+    if (!STATE_ONLY && seg > 0) {
+      // state entering this segment: fold the earlier segments' contributions, oldest first
+      const float gL = expf(log_g * float(p.seg_chunks * CH));
+      const float* dp = p.seg_state + bh * p.n_pieces * D * D + s_row * D + 16 * s_cg;
+      for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) {
+          const float4 v4 = __ldg(reinterpret_cast<const float4*>(dp) + e4);
+          S[4 * e4 + 0] = gL * S[4 * e4 + 0] + v4.x; S[4 * e4 + 1] = gL * S[4 * e4 + 1] + v4.y;
+          S[4 * e4 + 2] = gL * S[4 * e4 + 2] + v4.z; S[4 * e4 + 3] = gL * S[4 * e4 + 3] + v4.w;
         }
-      }
-      if (!STATE_ONLY) {
-        *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
-        *reinterpret_cast<uint32_t*>(sm->s_bf16[0] + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
       }
     }
   }
-  __syncthreads();
+  auto publish_state = [&]() {   // bf16 copy of this thread's 16 state values -> K-major tile [dv][dk]
+    uint32_t w[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(S[2 * e], S[2 * e + 1]);
+    *reinterpret_cast<uint4*>(sm->s + swz(s_row, 2 * s_cg)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(sm->s + swz(s_row, 2 * s_cg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+  };
+  if (!STATE_ONLY) publish_state();
 
-  // The k/v-only pass has no use for the q tile and the state mirror, so it runs two stages: k, v of odd
-  // chunks land in the two mirror buffers (16 KiB, 1024-byte aligned like the tiles) under their own barrier.
-  constexpr int N_ST = STATE_ONLY ? 2 : STAGES;
-  auto issue_chunk = [&](int ck) {  // called by thread 0 only
-    const int s = (ck - ck_begin) % N_ST;
-    const bool second = STATE_ONLY && s == 1;
-    const uint32_t bar = smem_u32(second ? &sm->full_b : &sm->full[STATE_ONLY ? 0 : s]);
-    mbar_arrive_expect_tx(bar, STATE_ONLY ? 2 * TILE_BYTES : STAGE_BYTES);
-    const uint32_t dst = smem_u32(sm->tiles[STATE_ONLY ? 0 : s]);
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = sm->tmem_base;
+  const uint32_t tm_lane = tm + (uint32_t(32 * qd) << 16);
+
+  const uint32_t q_a = smem_u32(sm->q), k_a = smem_u32(sm->k), kw_a = smem_u32(sm->kw), v_a = smem_u32(sm->v);
+  const uint32_t p0_a = smem_u32(sm->p[0]), p1_a = smem_u32(sm->p[1]), s_a = smem_u32(sm->s);
+
+  // TMA issue (thread 0 only).  Full pass: one stage, q and k under bar_qk[0], v under bar_v[0].  State-only
+  // pass: two stages (the q and P buffers are free): stage 1 puts k in the q buffer and v in p[0].
+  auto issue_qk = [&](int ck) {
+    const int st = STATE_ONLY ? ((ck - ck_begin) & 1) : 0;
+    const uint32_t bar = smem_u32(&sm->bar_qk[st]);
     const int r = row0 + ck * CH;
-    if (!STATE_ONLY) tma_load_2d(dst, &tm_q, h * D, r, bar);
-    tma_load_2d(second ? smem_u32(sm->s_bf16[0]) : dst + TILE_BYTES, &tm_k, h * D, r, bar);
-    tma_load_2d(second ? smem_u32(sm->s_bf16[1]) : dst + 2 * TILE_BYTES, &tm_v, h * D, r, bar);
+    mbar_arrive_expect_tx(bar, STATE_ONLY ? TILE_BYTES : 2 * TILE_BYTES);
+    if (!STATE_ONLY) tma_load_2d(q_a, &tm_q, h * D, r, bar);
+    tma_load_2d(st ? q_a : k_a, &tm_k, h * D, r, bar);
+  };
+  auto issue_v = [&](int ck) {
+    const int st = STATE_ONLY ? ((ck - ck_begin) & 1) : 0;
+    const uint32_t bar = smem_u32(&sm->bar_v[st]);
+    mbar_arrive_expect_tx(bar, TILE_BYTES);
+    tma_load_2d(st ? p0_a : v_a, &tm_v, h * D, row0 + ck * CH, bar);
   };
   if (tid == 0) {
-    for (int ck = ck_begin; ck < ck_begin + N_ST && ck < ck_end; ++ck) issue_chunk(ck);
+    for (int ck = ck_begin; ck < ck_begin + (STATE_ONLY ? 2 : 1) && ck < ck_end; ++ck) {
+      issue_qk(ck);
+      issue_v(ck);
+    }
   }
 
-  const uint32_t vw_a = smem_u32(sm->vw);
   bool ok = true;
   for (int ck = ck_begin; ck < ck_end; ++ck) {
     const int lc = ck - ck_begin;
-    const int s = lc % N_ST;
-    const bool second = STATE_ONLY && s == 1;
+    const int st = STATE_ONLY ? (lc & 1) : 0;                  // input stage of this chunk
+    const uint32_t in_ph = STATE_ONLY ? uint32_t(lc >> 1) & 1u : uint32_t(lc) & 1u;
+    const uint32_t ph = uint32_t(lc) & 1u;                     // phase of the once-per-chunk MMA barriers
     const int c_len = min(CH, T - ck * CH);
-    uint8_t* q_p = sm->tiles[STATE_ONLY ? 0 : s];
-    uint8_t* k_p = second ? sm->s_bf16[0] : q_p + TILE_BYTES;
-    uint8_t* v_p = second ? sm->s_bf16[1] : q_p + 2 * TILE_BYTES;
-    const uint32_t q_a = smem_u32(q_p), k_a = smem_u32(k_p), v_a = smem_u32(v_p);
-    const uint32_t sb_a = smem_u32(sm->s_bf16[lc & 1]);
-    uint8_t* sb_next = sm->s_bf16[(lc + 1) & 1];
+    uint8_t* k_p = st ? sm->q : sm->k;
 
-    if (!mbar_wait(smem_u32(second ? &sm->full_b : &sm->full[STATE_ONLY ? 0 : s]), uint32_t(lc / N_ST) & 1u,
-                   &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) {
-      ok = false;
-    }
-    if (__syncthreads_or(!ok)) break;   // leave together if any thread's wait ran out
+    if (!mbar_wait(smem_u32(&sm->bar_qk[st]), in_ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) ok = false;
 
-    // ---- prologue: feature map + RoPE on q and k (pairs d, d+32), Vw = v * gamma^(c-1-j) ----------
-    // 64 rows x 4 column groups of 8; 2 items per thread
+    // ---- prologue: feature map + RoPE on q and k (pairs d, d+32), kw = k' * gamma^(c-1-j) -------------------
+    // 128 rows x 4 column groups of 8 pairs; 2 items per thread.  Eight consecutive lanes take 4 groups of two
+    // rows that are 4 apart, so that their 16-byte accesses to the swizzled tile fall into different banks.
+    if (ok) {
 #pragma unroll
-    for (int it = 0; it < (p.qk_prepared ? 0 : 2); ++it) {
-      const int item = tid + it * ATTN_THREADS;
-      const int r = item >> 2, cg = item & 3;   // token row, 16-byte chunk in the first half
-      int pos = pos_base + ck * CH + r;
-      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
-      float cs[8], sn[8];
-      {
-        const float4* cp = reinterpret_cast<const float4*>(p.cos_tab + size_t(pos) * 32 + cg * 8);
-        const float4* sp = reinterpret_cast<const float4*>(p.sin_tab + size_t(pos) * 32 + cg * 8);
-        const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-      }
-#pragma unroll
-      for (int which = STATE_ONLY ? 1 : 0; which < 2; ++which) {  // 0: q, 1: k
-        uint8_t* tp = which == 0 ? q_p : k_p;
-        uint4* lo_p = reinterpret_cast<uint4*>(tp + swz(r, cg));
-        uint4* hi_p = reinterpret_cast<uint4*>(tp + swz(r, cg + 4));
-        const uint4 lo = *lo_p, hi = *hi_p;
-        const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
-        uint32_t ol[4], oh[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a0 = elu1(bf16_lo(lw[j])), a1 = elu1(bf16_hi(lw[j]));   // d
-          const float b0 = elu1(bf16_lo(hw[j])), b1 = elu1(bf16_hi(hw[j]));   // d + 32
-          // x*cos + rotate_half(x)*sin:  out[d] = x[d]cos - x[d+32]sin,  out[d+32] = x[d+32]cos + x[d]sin
-          ol[j] = pack_bf16x2(a0 * cs[2 * j] - b0 * sn[2 * j], a1 * cs[2 * j + 1] - b1 * sn[2 * j + 1]);
-          oh[j] = pack_bf16x2(b0 * cs[2 * j] + a0 * sn[2 * j], b1 * cs[2 * j + 1] + a1 * sn[2 * j + 1]);
+      for (int it = 0; it < 2; ++it) {
+        const int item = tid + it * ATTN_THREADS;
+        const int cg = item & 3;
+        const int r = (item >> 5) * 8 + ((item >> 2) & 1) * 4 + ((item >> 3) & 3);
+        const float w = r < c_len ? sm->pw[c_len - 1 - r] : 0.f;   // rows past the end contribute nothing
+        if (p.qk_prepared) {
+          // q', k' came out of the projection's epilogue: only the decay-weighted copy of k is made here
+          const uint4 lo = *reinterpret_cast<const uint4*>(k_p + swz(r, cg));
+          const uint4 hi = *reinterpret_cast<const uint4*>(k_p + swz(r, cg + 4));
+          *reinterpret_cast<uint4*>(sm->kw + swz(r, cg)) =
+              make_uint4(pack_bf16x2(bf16_lo(lo.x) * w, bf16_hi(lo.x) * w), pack_bf16x2(bf16_lo(lo.y) * w, bf16_hi(lo.y) * w),
+                         pack_bf16x2(bf16_lo(lo.z) * w, bf16_hi(lo.z) * w), pack_bf16x2(bf16_lo(lo.w) * w, bf16_hi(lo.w) * w));
+          *reinterpret_cast<uint4*>(sm->kw + swz(r, cg + 4)) =
+              make_uint4(pack_bf16x2(bf16_lo(hi.x) * w, bf16_hi(hi.x) * w), pack_bf16x2(bf16_lo(hi.y) * w, bf16_hi(hi.y) * w),
+                         pack_bf16x2(bf16_lo(hi.z) * w, bf16_hi(hi.z) * w), pack_bf16x2(bf16_lo(hi.w) * w, bf16_hi(hi.w) * w));
+          continue;
         }
-        *lo_p = make_uint4(ol[0], ol[1], ol[2], ol[3]);
-        *hi_p = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+        int pos = pos_base + ck * CH + r;
+        pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+        float cs[8], sn[8];
+        {
+          const float4* cp = reinterpret_cast<const float4*>(p.cos_tab + size_t(pos) * 32 + cg * 8);
+          const float4* sp = reinterpret_cast<const float4*>(p.sin_tab + size_t(pos) * 32 + cg * 8);
+          const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
+          cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+        }
+#pragma unroll
+        for (int which = STATE_ONLY ? 1 : 0; which < 2; ++which) {  // 0: q, 1: k
+          uint8_t* tp = which == 0 ? sm->q : k_p;
+          uint4* lo_p = reinterpret_cast<uint4*>(tp + swz(r, cg));
+          uint4* hi_p = reinterpret_cast<uint4*>(tp + swz(r, cg + 4));
+          const uint4 lo = *lo_p, hi = *hi_p;
+          const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+          uint32_t ol[4], oh[4], wl[4], wh[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a0 = elu1(bf16_lo(lw[j])), a1 = elu1(bf16_hi(lw[j]));   // d
+            const float b0 = elu1(bf16_lo(hw[j])), b1 = elu1(bf16_hi(hw[j]));   // d + 32
+            // x*cos + rotate_half(x)*sin:  out[d] = x[d]cos - x[d+32]sin,  out[d+32] = x[d+32]cos + x[d]sin
+            const float l0 = a0 * cs[2 * j] - b0 * sn[2 * j], l1 = a1 * cs[2 * j + 1] - b1 * sn[2 * j + 1];
+            const float h0 = b0 * cs[2 * j] + a0 * sn[2 * j], h1 = b1 * cs[2 * j + 1] + a1 * sn[2 * j + 1];
+            ol[j] = pack_bf16x2(l0, l1);
+            oh[j] = pack_bf16x2(h0, h1);
+            if (which == 1) {
+              wl[j] = pack_bf16x2(l0 * w, l1 * w);
+              wh[j] = pack_bf16x2(h0 * w, h1 * w);
+            }
+          }
+          if (!(STATE_ONLY && which == 1)) {       // the state-only pass needs only the weighted copy of k
+            *lo_p = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+            *hi_p = make_uint4(oh[0], oh[1], oh[2], oh[3]);
+          }
+          if (which == 1) {
+            *reinterpret_cast<uint4*>(sm->kw + swz(r, cg)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            *reinterpret_cast<uint4*>(sm->kw + swz(r, cg + 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+          }
+        }
       }
     }
-    // Vw: 64 rows x 8 chunks = 512 items, 4 per thread
+    fence_proxy_async_smem();   // q', k', kw (and the state copy of the previous chunk) -> visible to the tensor core
+    tc_fence_before_sync();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+
+    if (tid == 0) {
+      if (!STATE_ONLY) {
+        // MMA A: scores = Q' K'^T, O2 = Q' S^T
+        constexpr uint32_t id_sc = umma_idesc(128, 128, 0, 0), id_o2 = umma_idesc(128, 64, 0, 0);
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int item = tid + it * ATTN_THREADS;
-      const int r = item >> 3, cg = item & 7;
-      const float w = r < c_len ? sm->pw[c_len - 1 - r] : 0.f;   // rows past the end contribute nothing
-      const uint4 v = *reinterpret_cast<const uint4*>(v_p + swz(r, cg));
-      *reinterpret_cast<uint4*>(sm->vw + swz(r, cg)) =
-          make_uint4(pack_bf16x2(bf16_lo(v.x) * w, bf16_hi(v.x) * w), pack_bf16x2(bf16_lo(v.y) * w, bf16_hi(v.y) * w),
-                     pack_bf16x2(bf16_lo(v.z) * w, bf16_hi(v.z) * w), pack_bf16x2(bf16_lo(v.w) * w, bf16_hi(v.w) * w));
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ss(tm + TM_SCORES, umma_desc(q_a, 16, 1024) + uint64_t(ks * 2), umma_desc(k_a, 16, 1024) + uint64_t(ks * 2),
+                       id_sc, ks != 0);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ss(tm + TM_O2, umma_desc(q_a, 16, 1024) + uint64_t(ks * 2), umma_desc(s_a, 16, 1024) + uint64_t(ks * 2),
+                       id_o2, ks != 0);
+        umma_commit(smem_u32(&sm->bar_a));
+      }
+      // MMA S: dS = V^T Kw over the chunk's tokens (16 per step = two 8-row groups of the [token][64] tiles)
+      if (mbar_wait(smem_u32(&sm->bar_v[st]), in_ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) {
+        constexpr uint32_t id_ds = umma_idesc(128, 64, 1, 1);
+        const uint32_t vv = st ? p0_a : v_a;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tm + TM_DS, umma_desc(vv + ks * 2048, 0, 1024), umma_desc(kw_a + ks * 2048, 1024, 1024), id_ds,
+                       ks != 0);
+        umma_commit(smem_u32(&sm->bar_s));
+      }
     }
-    __syncthreads();
 
     if (!STATE_ONLY) {
-    // ---- Q fragments of this warp's 16 rows (A operand, 4 k-steps over d) ---------------------------
-    uint32_t qf[4][4];
-    {
-      const int r = 16 * warp + (lane & 7) + 8 * ((lane >> 3) & 1);
+      // ---- decay mask: scores -> P (bf16, K-major tiles) ------------------------------------------------------
+      if (!mbar_wait(smem_u32(&sm->bar_a), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
+      if (tid == 0 && ok && ck + 1 < ck_end) issue_qk(ck + 1);    // q and k tiles are free: both MMAs that read them are done
+      tc_fence_after_sync();
+      __syncwarp();               // tcgen05.ld is warp-collective: rejoin after the per-thread waits and thread 0's issue work
+      if (ok) {
+        const int i = 32 * qd + lane;                  // query row = TMEM lane
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) ldsm_x4(q_a + swz(r, 2 * ks + (lane >> 4)), qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3]);
-    }
-    const int i_lo = 16 * warp + (lane >> 2);   // query row of c0,c1 ; c2,c3 are row i_lo + 8
-    const int i_hi = i_lo + 8;
-
-    // ---- cross-chunk: O = (Q S^T) * gamma^(i+1);  B[k=dk][n=dv] = S[dv][dk] -------------------------
-    float O[8][4];
+        for (int jj = 0; jj < 2; ++jj) {
+          const int jb = 2 * hf + jj;                  // 32-key block
+          if (jb > qd) continue;                       // above the diagonal for all 32 rows of this warp (stays zero)
+          uint32_t r[32];
+          tmem_ld_32x32(tm_lane + TM_SCORES + 32 * jb, r);
+          tmem_ld_wait();
+          const float* f = sm->pwm + (i - 32 * jb + CH);     // f[-c]: factor of key 32*jb + c
+          uint32_t w[16];
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      O[nt][0] = O[nt][1] = O[nt][2] = O[nt][3] = 0.f;
-      uint32_t bfr[8];
-      const int r = nt * 8 + (lane & 7);
-      ldsm_x4(sb_a + swz(r, (lane >> 3)), bfr[0], bfr[1], bfr[2], bfr[3]);       // dk 0..31
-      ldsm_x4(sb_a + swz(r, 4 + (lane >> 3)), bfr[4], bfr[5], bfr[6], bfr[7]);   // dk 32..63
+          for (int c2 = 0; c2 < 16; ++c2)
+            w[c2] = pack_bf16x2(__uint_as_float(r[2 * c2]) * f[-2 * c2], __uint_as_float(r[2 * c2 + 1]) * f[-2 * c2 - 1]);
+          uint8_t* prow = sm->p[hf];
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) mma16816(O[nt], qf[ks], bfr[2 * ks], bfr[2 * ks + 1]);
-    }
-    {
-      const float g_lo = 0.125f * sm->pw[min(i_lo + 1, CH)], g_hi = 0.125f * sm->pw[min(i_hi + 1, CH)];
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) { O[nt][0] *= g_lo; O[nt][1] *= g_lo; O[nt][2] *= g_hi; O[nt][3] *= g_hi; }
-    }
-
-    // ---- intra-chunk: scores over the causal key tiles, decay mask, then P V ---------------------------
-    uint32_t pf[4][4];              // P as A fragments: k-step kj covers keys 16kj..16kj+15
-#pragma unroll
-    for (int kj = 0; kj < 4; ++kj) {
-      if (kj <= warp) {
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const int jt = 2 * kj + half;
-          float sc[4] = {0.f, 0.f, 0.f, 0.f};
-          uint32_t bfr[8];
-          const int r = jt * 8 + (lane & 7);
-          ldsm_x4(k_a + swz(r, (lane >> 3)), bfr[0], bfr[1], bfr[2], bfr[3]);
-          ldsm_x4(k_a + swz(r, 4 + (lane >> 3)), bfr[4], bfr[5], bfr[6], bfr[7]);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) mma16816(sc, qf[ks], bfr[2 * ks], bfr[2 * ks + 1]);
-          const float4 f = sm->mf[2 * warp - jt + 1][lane];   // gamma^(i-j) for j <= i, else 0
-          sc[0] *= f.x; sc[1] *= f.y; sc[2] *= f.z; sc[3] *= f.w;
-          pf[kj][2 * half + 0] = pack_bf16x2(sc[0], sc[1]);
-          pf[kj][2 * half + 1] = pack_bf16x2(sc[2], sc[3]);
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(prow + swz(i, 4 * jj + q4)) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
         }
       }
-    }
-
-    // O += P V ;  B[k=j][n=dv] = V[j][dv]  (transposed load)
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      tc_fence_after_sync();
+      if (tid == 0) {
+        // MMA B: O1 = P V into the (fully read) scores columns
+        constexpr uint32_t id_o1 = umma_idesc(128, 64, 0, 1);
 #pragma unroll
-    for (int kj = 0; kj < 4; ++kj) {
-      if (kj <= warp) {
-        const int r = 16 * kj + (lane & 7) + 8 * ((lane >> 3) & 1);
-#pragma unroll
-        for (int np = 0; np < 4; ++np) {  // pairs of dv n-tiles
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4_t(v_a + swz(r, 2 * np + (lane >> 4)), b0, b1, b2, b3);
-          mma16816(O[2 * np], pf[kj], b0, b1);
-          mma16816(O[2 * np + 1], pf[kj], b2, b3);
-        }
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tm + TM_O1, umma_desc(ks < 4 ? p0_a : p1_a, 16, 1024) + uint64_t((ks & 3) * 2),
+                       umma_desc(v_a + ks * 2048, 1024, 1024), id_o1, ks != 0);
+        umma_commit(smem_u32(&sm->bar_b));
       }
     }
 
-    // ---- output: stage this warp's 16 rows in its own (already consumed) q rows, then 16-byte stores ------
-    __syncwarp();
-    {
-      const int r = 16 * warp + (lane >> 2);
-      const int cb = 2 * (lane & 3);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        const int c = nt * 8 + cb;
-        *reinterpret_cast<uint32_t*>(q_p + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][0], O[nt][1]);
-        *reinterpret_cast<uint32_t*>(q_p + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(O[nt][2], O[nt][3]);
-      }
+    // ---- state update: S = gamma^c S + dS ------------------------------------------------------------------
+    if (!mbar_wait(smem_u32(&sm->bar_s), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
+    tc_fence_after_sync();
+    if (STATE_ONLY && tid == 0 && ok && ck + 2 < ck_end) {   // this chunk's k and v buffers are free again
+      issue_qk(ck + 2);
+      issue_v(ck + 2);
     }
     __syncwarp();
-#pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int rr = 16 * warp + it * 4 + (lane >> 3), cg = lane & 7;
-      if (rr < c_len) {
-        const uint4 v = *reinterpret_cast<const uint4*>(q_p + swz(rr, cg));
-        *reinterpret_cast<uint4*>(p.o + size_t(row0 + ck * CH + rr) * p.ld_o + h * D + cg * 8) = v;
-      }
-    }
-    }  // !STATE_ONLY
-
-    // ---- state update: S = gamma^c S + Vw^T K ;  A[m=dv][k=j] = Vw[j][dv], B[k=j][n=dk] = K[j][dk] -------
-    {
+    if (ok) {
+      uint32_t r[16];
+      tmem_ld_32x16(tm_lane + TM_DS + 16 * s_cg, r);
+      tmem_ld_wait();
       const float gc = sm->pw[c_len];
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) { S[nt][0] *= gc; S[nt][1] *= gc; S[nt][2] *= gc; S[nt][3] *= gc; }
+      for (int e = 0; e < 16; ++e) S[e] = gc * S[e] + __uint_as_float(r[e]);
+      if (!STATE_ONLY) publish_state();      // read by the next chunk's MMA A (made visible by the fence before it)
+    }
+
+    if (!STATE_ONLY) {
+      // ---- output rows: o[i] = O1 + gamma^(i+1)/8 * O2 ------------------------------------------------------
+      if (!mbar_wait(smem_u32(&sm->bar_b), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
+      if (tid == 0 && ok && ck + 1 < ck_end) issue_v(ck + 1);     // both MMAs that read v are done
+      tc_fence_after_sync();
+      __syncwarp();
+      if (ok) {
+        const int i = 32 * qd + lane;
+        uint32_t a[32], c2[32];
+        tmem_ld_32x32(tm_lane + TM_O1 + 32 * hf, a);
+        tmem_ld_32x32(tm_lane + TM_O2 + 32 * hf, c2);
+        tmem_ld_wait();
+        const float g = 0.125f * sm->pw[i + 1];
+        uint32_t w[16];
 #pragma unroll
-      for (int kj = 0; kj < 4; ++kj) {
-        uint32_t af[4];
-        {
-          const int r = 16 * kj + (lane & 7) + 8 * (lane >> 4);
-          ldsm_x4_t(vw_a + swz(r, 2 * warp + ((lane >> 3) & 1)), af[0], af[1], af[2], af[3]);
-        }
-        const int r = 16 * kj + (lane & 7) + 8 * ((lane >> 3) & 1);
+        for (int e = 0; e < 16; ++e)
+          w[e] = pack_bf16x2(fmaf(g, __uint_as_float(c2[2 * e]), __uint_as_float(a[2 * e])),
+                             fmaf(g, __uint_as_float(c2[2 * e + 1]), __uint_as_float(a[2 * e + 1])));
+        if (i < c_len) {
+          __nv_bfloat16* op = p.o + size_t(row0 + ck * CH + i) * p.ld_o + h * D + 32 * hf;
+          if (p.wide_store) {
+            st_global_256(op, w);
+            st_global_256(op + 16, w + 8);
+          } else {
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
-          uint32_t b0, b1, b2, b3;
-          ldsm_x4_t(k_a + swz(r, 2 * np + (lane >> 4)), b0, b1, b2, b3);
-          mma16816(S[2 * np], af, b0, b1);
-          mma16816(S[2 * np + 1], af, b2, b3);
-        }
-      }
-      // publish the bf16 mirror for the next chunk's cross term (a k/v-only pass has none)
-      if (!STATE_ONLY) {
-        const int r = 16 * warp + (lane >> 2);
-        const int cb = 2 * (lane & 3);
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-          const int c = nt * 8 + cb;
-          *reinterpret_cast<uint32_t*>(sb_next + swz(r, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][0], S[nt][1]);
-          *reinterpret_cast<uint32_t*>(sb_next + swz(r + 8, c >> 3) + (c & 7) * 2) = pack_bf16x2(S[nt][2], S[nt][3]);
+            for (int q4 = 0; q4 < 4; ++q4)
+              *reinterpret_cast<uint4*>(op + 8 * q4) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+          }
         }
       }
     }
-
-    fence_proxy_async_smem();  // order this thread's generic accesses to stage s before the next TMA write into it
-    __syncthreads();  // tiles of stage s and vw are free; the new state mirror is complete
-    if (tid == 0 && ck + N_ST < ck_end) issue_chunk(ck + N_ST);
   }
 
+  // final state (or this piece's contribution)
   float* so = nullptr;
   if (STATE_ONLY) so = p.seg_state + ((size_t(b) * p.H + h) * p.n_pieces + seg) * D * D;
   else if (p.s_out && seg == p.nseg - 1) so = p.s_out + (size_t(b) * p.H + h) * D * D;
   if (ok && so) {
-    const int r = 16 * warp + (lane >> 2);
-    const int cb = 2 * (lane & 3);
-    const bool natural = !STATE_ONLY && p.qk_prepared;   // segment contributions stay in the kernel's own order
+    const bool natural = !STATE_ONLY && p.qk_prepared;   // pieces stay in the kernel's own column order
+    float* sp = so + s_row * D;
+    if (natural) {
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      const int c = nt * 8 + cb;
-      if (natural) {
-        const int d = c >> 1;
-        so[r * D + d] = S[nt][0];        so[r * D + d + 32] = S[nt][1];
-        so[(r + 8) * D + d] = S[nt][2];  so[(r + 8) * D + d + 32] = S[nt][3];
-      } else {
-        *reinterpret_cast<float2*>(so + r * D + c) = make_float2(S[nt][0], S[nt][1]);
-        *reinterpret_cast<float2*>(so + (r + 8) * D + c) = make_float2(S[nt][2], S[nt][3]);
+      for (int e = 0; e < 16; ++e) {
+        const int c = 16 * s_cg + e;
+        sp[(c >> 1) + 32 * (c & 1)] = S[e];
       }
+    } else {
+#pragma unroll
+      for (int e4 = 0; e4 < 4; ++e4)
+        *reinterpret_cast<float4*>(sp + 16 * s_cg + 4 * e4) = make_float4(S[4 * e4], S[4 * e4 + 1], S[4 * e4 + 2], S[4 * e4 + 3]);
     }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tm, TMEM_COLS);
   }
 }
 
@@ -517,12 +583,12 @@ int make_map(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
 
 }  // namespace
 
-// Segments: enough CTAs to fill three per SM, each segment at least four chunks long.
+// Segments: enough CTAs to fill two per SM, each segment at least two chunks long.
 static void pick_segments(int B, int T, int H, int sms, int* seg_chunks, int* nseg) {
   const int n_chunks = (T + CH - 1) / CH;
-  long want = (long(sms) * 4) / (long(B) * H);
+  long want = (long(sms) * 2) / (long(B) * H);
   if (want < 1) want = 1;
-  if (want > n_chunks / 4) want = n_chunks / 4 > 0 ? n_chunks / 4 : 1;
+  if (want > n_chunks / 2) want = n_chunks / 2 > 0 ? n_chunks / 2 : 1;
   int sc = int((n_chunks + want - 1) / want);
   *seg_chunks = sc;
   *nseg = (n_chunks + sc - 1) / sc;
@@ -554,18 +620,17 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
              "attn_scan: row strides must cover H*64 columns and be multiples of 8 elements");
   JB_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && (!o || aligned16(o)) && aligned16(cos_tab) && aligned16(sin_tab),
              "attn_scan: pointers must be 16-byte aligned");
-  JB_REQUIRE(!s_in || (reinterpret_cast<uintptr_t>(s_in) & 7u) == 0, "attn_scan: state pointer misaligned");
-  JB_REQUIRE(!s_out || (reinterpret_cast<uintptr_t>(s_out) & 7u) == 0, "attn_scan: state pointer misaligned");
   JB_REQUIRE(size_t(B) * T < (size_t(1) << 31), "attn_scan: too many rows");
   JB_REQUIRE(n_pos >= 1, "attn_scan: empty RoPE table");
   if (!pos0) JB_REQUIRE(pos0_scalar >= 0 && pos0_scalar + T <= n_pos, "attn_scan: RoPE table (%d rows) too short for positions %d..%d", n_pos, pos0_scalar, pos0_scalar + T - 1);
+  JB_REQUIRE(!s_in || aligned16(s_in), "attn_scan: state pointers must be 16-byte aligned");
+  JB_REQUIRE(!s_out || aligned16(s_out), "attn_scan: state pointers must be 16-byte aligned");
   if (T == 1) {
-    JB_REQUIRE(!s_in || aligned16(s_in), "attn_scan: state pointer must be 16-byte aligned for single-token steps");
-    JB_REQUIRE(!s_out || aligned16(s_out), "attn_scan: state pointer must be 16-byte aligned for single-token steps");
     AttnParams dp;
     dp.gamma = gamma; dp.cos_tab = cos_tab; dp.sin_tab = sin_tab; dp.pos0 = pos0; dp.pos0_scalar = pos0_scalar;
     dp.n_pos = n_pos; dp.s_in = s_in; dp.s_out = s_out; dp.o = reinterpret_cast<__nv_bfloat16*>(o); dp.ld_o = ld_o;
-    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.n_pieces = 0; dp.qk_prepared = 0; dp.status = nullptr;
+    dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.n_pieces = 0; dp.qk_prepared = 0;
+    dp.wide_store = 0; dp.status = nullptr;
     attn_decode_kernel<<<dim3(H, B), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q),
                                                         reinterpret_cast<const __nv_bfloat16*>(k),
                                                         reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
@@ -582,6 +647,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.n_pos = n_pos; p.s_in = s_in; p.s_out = s_out; p.o = reinterpret_cast<__nv_bfloat16*>(o); p.ld_o = ld_o;
   p.B = B; p.T = T; p.H = H;
   p.qk_prepared = (flags & JB200_ATTN_QK_PREPARED) ? 1 : 0;
+  p.wide_store = (o && (reinterpret_cast<uintptr_t>(o) & 31u) == 0 && ld_o % 16 == 0) ? 1 : 0;
   p.n_pieces = 0;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
@@ -592,7 +658,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.seg_state = reinterpret_cast<float*>(scratch);
   if (scratch) pick_segments(B, T, H, sms, &p.seg_chunks, &p.nseg);   // without scratch: one segment per sequence
   JB_REQUIRE(p.nseg <= 65535, "attn_scan: too many segments");
-  JB_REQUIRE(!scratch || (reinterpret_cast<uintptr_t>(scratch) & 7u) == 0, "attn_scan: scratch pointer misaligned");
+  JB_REQUIRE(!scratch || aligned16(scratch), "attn_scan: scratch pointer must be 16-byte aligned");
   p.n_pieces = o ? p.nseg - 1 : p.nseg;
   if (!o) {
     // state only: the k/v pass over every piece, then the fold
