@@ -33,6 +33,8 @@
 // zero state and stores its contribution D_s; the main launch starts segment s from
 // S = fold_{s' < s}(gamma^L S + D_s'), which is exact because the recurrence is linear in S.
 // Extra HBM traffic: k and v of the non-final segments are read twice (the second time mostly from L2).
+#include <type_traits>
+
 #include "common.cuh"
 #include "launchers.h"
 
@@ -44,9 +46,6 @@ constexpr int D = 64;             // head dim (fixed by the path: 16 heads x 64)
 constexpr int CH = 128;           // tokens per chunk = rows of one MMA tile
 constexpr int TILE_BYTES = CH * D * 2;          // 16 KiB: [128 tokens][64 bf16], 128B-swizzled
 constexpr int S_BYTES = D * D * 2;              // 8 KiB: bf16 state [dv][dk]
-constexpr int ATTN_THREADS = 256;
-constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t TM_SCORES = 0, TM_O1 = 0, TM_O2 = 128, TM_DS = 192;
 
 struct AttnParams {
   const float* gamma;      // [H] decay in (0,1)
@@ -68,22 +67,6 @@ struct AttnParams {
   int wide_store;          // output rows are 32-byte aligned: 256-bit stores
   unsigned int* status;
 };
-
-struct Smem {
-  uint8_t q[TILE_BYTES];       // state-only pass: second stage of k
-  uint8_t k[TILE_BYTES];
-  uint8_t kw[TILE_BYTES];
-  uint8_t v[TILE_BYTES];
-  uint8_t p[2][TILE_BYTES];    // P as two K-major tiles (keys 0-63, 64-127); state-only pass: p[0] = second stage of v
-  uint8_t s[S_BYTES];
-  float pwm[2 * CH];           // pwm[x + CH] = gamma^x / 8 for x >= 0, 0 for x < 0: the decay mask by (i - j)
-  float pw[CH + 1];            // gamma^n
-  uint64_t bar_qk[2], bar_v[2], bar_a, bar_s, bar_b;
-  uint32_t tmem_base;
-  uint32_t abort_flag;
-};
-
-constexpr size_t ATTN_SMEM_BYTES = sizeof(Smem) + 1024;
 
 __device__ __forceinline__ uint32_t swz(int row, int chunk16) {  // byte offset inside a swizzled [rows][128 B] tile
   return uint32_t(row) * 128u + (uint32_t(chunk16 ^ (row & 7)) << 4);
@@ -127,37 +110,275 @@ __device__ __forceinline__ void st_global_256(void* p, const uint32_t* w) {
 // rounding of the result).  For large positive x the unused exp is +inf, never NaN.
 __device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(x); }
 
-template <bool STATE_ONLY>
-__global__ void __launch_bounds__(ATTN_THREADS, 2)
-attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                 const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+// ------------------------------------------------------------------------------------------------------------
+// k/v-only pass: the state contribution of one piece of a sequence from a zero state (pieces = the non-final
+// segments of a full call, or all pieces of a state-only call).  One CTA per (sequence, head, piece), 256 threads,
+// two CTAs per SM.  Per chunk: TMA k, v (two stages) -> kw = phi(k) with RoPE, times gamma^(c-1-j) ->
+// dS = V^T Kw as tcgen05.mma (accumulator in TMEM) -> S = gamma^c S + dS in registers.  The feature map, the
+// angles and the rounding of kw are instruction for instruction those of the pipeline kernel's prologue, so a
+// segmented call and an unsegmented one see the same bf16 operands.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int STATE_THREADS = 256;
+constexpr uint32_t STATE_TMEM_COLS = 64;
+
+struct StateSmem {
+  uint8_t k[2][TILE_BYTES];
+  uint8_t v[2][TILE_BYTES];
+  uint8_t kw[TILE_BYTES];
+  float pw[CH + 1];            // gamma^n
+  uint64_t full[2], bar_s;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+constexpr size_t STATE_SMEM_BYTES = sizeof(StateSmem) + 1024;
+
+__global__ void __launch_bounds__(STATE_THREADS, 2)
+attn_state_pass_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
-  Smem* sm = reinterpret_cast<Smem*>(smem_raw + (base - raw_addr));
+  StateSmem* sm = reinterpret_cast<StateSmem*>(smem_raw + (base - raw_addr));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int qd = warp & 3;          // TMEM lane quarter this warp may access: lanes 32*qd .. 32*qd+31
-  const int hf = warp >> 2;         // which half of the columns this warp takes
+  const int qd = warp & 3;          // TMEM lane quarter this warp may access
+  const int hf = warp >> 2;
+  const int h = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
+  const int T = p.T;
+  const int n_chunks = (T + CH - 1) / CH;
+  const int ck_begin = seg * p.seg_chunks;
+  const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
+  const int row0 = b * T;
+  const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
+  const float log_g = logf(__ldg(p.gamma + h));
+
+  if (tid == 0) {
+    mbar_init(smem_u32(&sm->full[0]), 1);
+    mbar_init(smem_u32(&sm->full[1]), 1);
+    mbar_init(smem_u32(&sm->bar_s), 1);
+    sm->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 0) {
+    __syncwarp();                 // tcgen05.alloc is warp-collective: lane 0 rejoins from the barrier set-up first
+    tmem_alloc(smem_u32(&sm->tmem_base), STATE_TMEM_COLS);
+    tmem_relinquish();
+  }
+  for (int n = tid; n <= CH; n += STATE_THREADS) sm->pw[n] = expf(log_g * float(n));
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tm = sm->tmem_base;
+  const uint32_t tm_lane = tm + (uint32_t(32 * qd) << 16);
+
+  auto issue = [&](int ck) {      // thread 0 only
+    const int st = (ck - ck_begin) & 1;
+    const uint32_t bar = smem_u32(&sm->full[st]);
+    mbar_arrive_expect_tx(bar, 2 * TILE_BYTES);
+    tma_load_2d(smem_u32(sm->k[st]), &tm_k, h * D, row0 + ck * CH, bar);
+    tma_load_2d(smem_u32(sm->v[st]), &tm_v, h * D, row0 + ck * CH, bar);
+  };
+  if (tid == 0) {
+    for (int ck = ck_begin; ck < ck_begin + 2 && ck < ck_end; ++ck) issue(ck);
+  }
+
+  // the thread's share of the state: row dv = 32*(qd&1) + lane, columns 16*cg .. 16*cg+15 (see the pipeline kernel)
+  const int s_row = 32 * (qd & 1) + lane;
+  const int s_cg = 2 * (qd >> 1) + hf;
+  float S[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) S[e] = 0.f;
+
+  const int cg = tid & 3;
+  const int r_lo = (tid >> 5) * 8 + ((tid >> 2) & 1) * 4 + ((tid >> 3) & 3);
+  float c64[8], s64[8];
+  {
+    const int stp = 64 < p.n_pos ? 64 : p.n_pos - 1;
+    const float4* cq = reinterpret_cast<const float4*>(p.cos_tab + size_t(stp) * 32 + cg * 8);
+    const float4* sq = reinterpret_cast<const float4*>(p.sin_tab + size_t(stp) * 32 + cg * 8);
+    const float4 d0 = __ldg(cq), d1 = __ldg(cq + 1), e0 = __ldg(sq), e1 = __ldg(sq + 1);
+    c64[0] = d0.x; c64[1] = d0.y; c64[2] = d0.z; c64[3] = d0.w; c64[4] = d1.x; c64[5] = d1.y; c64[6] = d1.z; c64[7] = d1.w;
+    s64[0] = e0.x; s64[1] = e0.y; s64[2] = e0.z; s64[3] = e0.w; s64[4] = e1.x; s64[5] = e1.y; s64[6] = e1.z; s64[7] = e1.w;
+  }
+
+  bool ok = true;
+  for (int ck = ck_begin; ck < ck_end; ++ck) {
+    const int lc = ck - ck_begin;
+    const int st = lc & 1;
+    const int c_len = min(CH, T - ck * CH);
+    const uint8_t* k_p = sm->k[st];
+    float cs[8], sn[8];
+    if (!p.qk_prepared) {         // angles of the thread's first row (in flight during the wait below)
+      int pos = pos_base + ck * CH + r_lo;
+      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+      const float4* cp = reinterpret_cast<const float4*>(p.cos_tab + size_t(pos) * 32 + cg * 8);
+      const float4* sp = reinterpret_cast<const float4*>(p.sin_tab + size_t(pos) * 32 + cg * 8);
+      const float4 a0 = __ldg(cp), a1 = __ldg(cp + 1), b0 = __ldg(sp), b1 = __ldg(sp + 1);
+      cs[0] = a0.x; cs[1] = a0.y; cs[2] = a0.z; cs[3] = a0.w; cs[4] = a1.x; cs[5] = a1.y; cs[6] = a1.z; cs[7] = a1.w;
+      sn[0] = b0.x; sn[1] = b0.y; sn[2] = b0.z; sn[3] = b0.w; sn[4] = b1.x; sn[5] = b1.y; sn[6] = b1.z; sn[7] = b1.w;
+    }
+    if (!mbar_wait(smem_u32(&sm->full[st]), uint32_t(lc >> 1) & 1u, &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) ok = false;
+    if (ok) {
+#pragma unroll
+      for (int it = 0; it < 2; ++it) {
+        const int r = r_lo + 64 * it;
+        const float w = r < c_len ? sm->pw[c_len - 1 - r] : 0.f;   // rows past the end contribute nothing
+        const uint4 lo = *reinterpret_cast<const uint4*>(k_p + swz(r, cg));
+        const uint4 hi = *reinterpret_cast<const uint4*>(k_p + swz(r, cg + 4));
+        const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
+        uint32_t wl[4], wh[4];
+        if (p.qk_prepared) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            wl[j] = pack_bf16x2(bf16_lo(lw[j]) * w, bf16_hi(lw[j]) * w);
+            wh[j] = pack_bf16x2(bf16_lo(hw[j]) * w, bf16_hi(hw[j]) * w);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float a0 = elu1(bf16_lo(lw[j])), a1 = elu1(bf16_hi(lw[j]));   // d
+            const float b0 = elu1(bf16_lo(hw[j])), b1 = elu1(bf16_hi(hw[j]));   // d + 32
+            const float l0 = a0 * cs[2 * j] - b0 * sn[2 * j], l1 = a1 * cs[2 * j + 1] - b1 * sn[2 * j + 1];
+            const float h0 = b0 * cs[2 * j] + a0 * sn[2 * j], h1 = b1 * cs[2 * j + 1] + a1 * sn[2 * j + 1];
+            wl[j] = pack_bf16x2(l0 * w, l1 * w);
+            wh[j] = pack_bf16x2(h0 * w, h1 * w);
+          }
+          if (it == 0) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float cn = cs[e] * c64[e] - sn[e] * s64[e];
+              sn[e] = sn[e] * c64[e] + cs[e] * s64[e];
+              cs[e] = cn;
+            }
+          }
+        }
+        *reinterpret_cast<uint4*>(sm->kw + swz(r, cg)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+        *reinterpret_cast<uint4*>(sm->kw + swz(r, cg + 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+      }
+    }
+    fence_proxy_async_smem();   // kw -> visible to the tensor core; orders the reads of k before the next TMA write
+    tc_fence_before_sync();
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    tc_fence_after_sync();
+    if (tid == 0) {
+      constexpr uint32_t id_ds = umma_idesc(128, 64, 1, 1);
+      const uint32_t v_a = smem_u32(sm->v[st]), kw_a = smem_u32(sm->kw);
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks)
+        umma_bf16_ss(tm, umma_desc(v_a + ks * 2048, 0, 1024), umma_desc(kw_a + ks * 2048, 1024, 1024), id_ds, ks != 0);
+      umma_commit(smem_u32(&sm->bar_s));
+    }
+    if (!mbar_wait(smem_u32(&sm->bar_s), uint32_t(lc) & 1u, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
+    tc_fence_after_sync();
+    if (tid == 0 && ok && ck + 2 < ck_end) issue(ck + 2);     // this chunk's k and v buffers are free again
+    __syncwarp();
+    if (ok) {
+      uint32_t r[16];
+      tmem_ld_32x16(tm_lane + 16 * s_cg, r);
+      tmem_ld_wait();
+      const float gc = sm->pw[c_len];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) S[e] = gc * S[e] + __uint_as_float(r[e]);
+    }
+  }
+
+  if (ok) {       // pieces stay in the kernel's own column order (interleaved when q/k were prepared)
+    float* sp = p.seg_state + ((size_t(b) * p.H + h) * p.n_pieces + seg) * D * D + s_row * D + 16 * s_cg;
+#pragma unroll
+    for (int e4 = 0; e4 < 4; ++e4)
+      *reinterpret_cast<float4*>(sp + 4 * e4) = make_float4(S[4 * e4], S[4 * e4 + 1], S[4 * e4 + 2], S[4 * e4 + 3]);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tm, STATE_TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------------
+// The full pass as a warp-specialised pipeline: one CTA per SM, 576 threads, several chunks in flight.
+//   warp 0       TMA producer: q, k, v tiles of chunk c+2 as soon as the MMAs that read stage c%2 have retired
+//   warp 1       MMA issuer (one thread), per chunk c in this order:
+//                  S(c)  dS = V^T Kw                 -> TMEM DS        (needs the prologue of c, v of c)
+//                  A2(c) O2 = Q' S^T                  -> TMEM O2[c%2]   (needs the state after chunk c-1 in smem)
+//                  B(c)  O1 = P V                     -> TMEM SC[c%2] columns 0-63 (needs P of c)
+//                  A1(c+1) scores = Q' K'^T of the NEXT chunk -> TMEM SC[(c+1)%2]
+//                so the scores of chunk c+1 are computed while the consumers finish chunk c
+//   warps 2-9    prologue: feature map + RoPE in place on q and k of a stage, kw = k' * gamma^(c-1-j)
+//   warps 10-17  consumers (two per TMEM lane quarter): decay mask scores -> P, state update, output rows
+// Double-buffered: q/k/kw/v stages, score and O2 accumulators, the bf16 state copy.  Single: P (its reader,
+// MMA B, has retired before the next mask step starts, because the output rows of a chunk wait for it).
+// ------------------------------------------------------------------------------------------------------------
+// Per-role cycle counters of one CTA (block 0,0,0), compiled in with -DJB_ATTN_TIMING only: every role adds the
+// cycles it spends in each of its waits and work phases; a harness reads g_attn_timing after the launch.
+#ifdef JB_ATTN_TIMING
+__device__ long long g_attn_timing[18 * 8];
+#define JB_T_DECL long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
+#define JB_T_MARK(k) { const long long t_now = clock64(); t_acc[k] += t_now - t_last; t_last = t_now; }
+#define JB_T_FLUSH(w) if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0) { for (int kk = 0; kk < 8; ++kk) g_attn_timing[(w) * 8 + kk] = t_acc[kk]; }
+#else
+#define JB_T_DECL
+#define JB_T_MARK(k)
+#define JB_T_FLUSH(w)
+#endif
+
+constexpr int PIPE_THREADS = 576;
+constexpr int PRO_WARP0 = 2, CON_WARP0 = 10;
+constexpr uint32_t PIPE_TMEM_COLS = 512;
+constexpr uint32_t PT_SC = 0, PT_O2 = 256, PT_DS = 384;     // SC[2] x 128, O2[2] x 64, DS x 64
+
+struct PipeSmem {
+  uint8_t q[2][TILE_BYTES];
+  uint8_t k[2][TILE_BYTES];
+  uint8_t kw[2][TILE_BYTES];
+  uint8_t v[2][TILE_BYTES];
+  uint8_t p[2][TILE_BYTES];    // P as two K-major tiles (keys 0-63, 64-127)
+  uint8_t s[2][S_BYTES];       // bf16 state copy, [n & 1] = state after n chunks of this CTA
+  float pwm[2 * CH];
+  float pw[CH + 1];
+  uint64_t full_qk[2], full_v[2], empty_qk[2], empty_v[2], pro_done[2], bar_sc[2], bar_b[2], o_done[2];
+  uint64_t bar_s, s_done, p_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+constexpr size_t PIPE_SMEM_BYTES = sizeof(PipeSmem) + 1024;
+
+__global__ void __launch_bounds__(PIPE_THREADS, 1)
+attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  PipeSmem* sm = reinterpret_cast<PipeSmem*>(smem_raw + (base - raw_addr));
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x, b = blockIdx.y;
   const int T = p.T;
   const int n_chunks = (T + CH - 1) / CH;
   const int seg = blockIdx.z;
   const int ck_begin = seg * p.seg_chunks;
   const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
-  const int row0 = b * T;                       // first row of this sequence in the (B*T, ld) matrices
-  const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
-  const float gamma = __ldg(p.gamma + h);
-  const float log_g = logf(gamma);
+  const int n_loc = ck_end - ck_begin;
+  const int row0 = b * T;
+  const float log_g = logf(__ldg(p.gamma + h));
 
   if (tid == 0) {
     for (int s = 0; s < 2; ++s) {
-      mbar_init(smem_u32(&sm->bar_qk[s]), 1);
-      mbar_init(smem_u32(&sm->bar_v[s]), 1);
+      mbar_init(smem_u32(&sm->full_qk[s]), 1);
+      mbar_init(smem_u32(&sm->full_v[s]), 1);
+      mbar_init(smem_u32(&sm->empty_qk[s]), 1);
+      mbar_init(smem_u32(&sm->empty_v[s]), 1);
+      mbar_init(smem_u32(&sm->pro_done[s]), 256);
+      mbar_init(smem_u32(&sm->bar_sc[s]), 1);
+      mbar_init(smem_u32(&sm->bar_b[s]), 1);
+      mbar_init(smem_u32(&sm->o_done[s]), 256);
     }
-    mbar_init(smem_u32(&sm->bar_a), 1);
     mbar_init(smem_u32(&sm->bar_s), 1);
-    mbar_init(smem_u32(&sm->bar_b), 1);
+    mbar_init(smem_u32(&sm->s_done), 256);
+    mbar_init(smem_u32(&sm->p_done), 256);
     sm->abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tm_q);
@@ -165,145 +386,204 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     tma_prefetch_desc(&tm_v);
   }
   if (warp == 0) {
-    __syncwarp();                 // tcgen05.alloc is warp-collective: lane 0 rejoins from the barrier set-up first
-    tmem_alloc(smem_u32(&sm->tmem_base), TMEM_COLS);
+    __syncwarp();
+    tmem_alloc(smem_u32(&sm->tmem_base), PIPE_TMEM_COLS);
     tmem_relinquish();
   }
-  for (int n = tid; n <= CH; n += ATTN_THREADS) sm->pw[n] = expf(log_g * float(n));
-  for (int n = tid; n < 2 * CH; n += ATTN_THREADS) {
-    // gamma^(i-j) / sqrt(D): the 1/8 of the query feature map is a power of two, so applying it to the scores
-    // (and to the cross-chunk factor) instead of to every element of q gives the same bits
+  for (int n = tid; n <= CH; n += PIPE_THREADS) sm->pw[n] = expf(log_g * float(n));
+  for (int n = tid; n < 2 * CH; n += PIPE_THREADS) {
     const int x = n - CH;
     sm->pwm[n] = x >= 0 ? 0.125f * expf(log_g * float(x)) : 0.f;
   }
-  if (!STATE_ONLY) {
-    // blocks of P above the diagonal are never written again: zero the tile once
-    uint4* pz = reinterpret_cast<uint4*>(sm->p[0]);
-    for (int e = tid; e < 2 * TILE_BYTES / 16; e += ATTN_THREADS) pz[e] = make_uint4(0u, 0u, 0u, 0u);
-  }
-
-  // state: fp32 master copy in registers.  Thread (qd, hf, lane) owns row dv = 32*(qd&1) + lane, columns
-  // dk = 16*cg .. 16*cg+15 with cg = 2*(qd>>1) + hf: the accumulator of MMA S holds the 64 dv rows twice (lanes
-  // 0-63 and 64-127), so all eight warps read their share of it from their own lane quarter.
-  const int s_row = 32 * (qd & 1) + lane;
-  const int s_cg = 2 * (qd >> 1) + hf;
-  float S[16];
   {
-    const size_t bh = size_t(b) * p.H + h;
-    const float* sin_p = (!STATE_ONLY && p.s_in) ? p.s_in + bh * D * D + s_row * D : nullptr;
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const int c = 16 * s_cg + e;
-      // prepared q/k: the kernel's dk axis is the interleaved one (column 2i = feature i, 2i + 1 = feature i + 32);
-      // states cross the API in the natural order
-      const int d = p.qk_prepared ? (c >> 1) + 32 * (c & 1) : c;
-      S[e] = sin_p ? __ldg(sin_p + d) : 0.f;
-    }
-    if (!STATE_ONLY && seg > 0) {
-      // state entering this segment: fold the earlier segments' contributions, oldest first
-      const float gL = expf(log_g * float(p.seg_chunks * CH));
-      const float* dp = p.seg_state + bh * p.n_pieces * D * D + s_row * D + 16 * s_cg;
-      for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
-#pragma unroll
-        for (int e4 = 0; e4 < 4; ++e4) {
-          const float4 v4 = __ldg(reinterpret_cast<const float4*>(dp) + e4);
-          S[4 * e4 + 0] = gL * S[4 * e4 + 0] + v4.x; S[4 * e4 + 1] = gL * S[4 * e4 + 1] + v4.y;
-          S[4 * e4 + 2] = gL * S[4 * e4 + 2] + v4.z; S[4 * e4 + 3] = gL * S[4 * e4 + 3] + v4.w;
-        }
-      }
-    }
+    uint4* pz = reinterpret_cast<uint4*>(sm->p[0]);   // blocks of P above the diagonal are never written again
+    for (int e = tid; e < 2 * TILE_BYTES / 16; e += PIPE_THREADS) pz[e] = make_uint4(0u, 0u, 0u, 0u);
   }
-  auto publish_state = [&]() {   // bf16 copy of this thread's 16 state values -> K-major tile [dv][dk]
-    uint32_t w[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(S[2 * e], S[2 * e + 1]);
-    *reinterpret_cast<uint4*>(sm->s + swz(s_row, 2 * s_cg)) = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4*>(sm->s + swz(s_row, 2 * s_cg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
-  };
-  if (!STATE_ONLY) publish_state();
-
   fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tm = sm->tmem_base;
-  const uint32_t tm_lane = tm + (uint32_t(32 * qd) << 16);
+  volatile uint32_t* abort_flag = &sm->abort_flag;
 
-  const uint32_t q_a = smem_u32(sm->q), k_a = smem_u32(sm->k), kw_a = smem_u32(sm->kw), v_a = smem_u32(sm->v);
-  const uint32_t p0_a = smem_u32(sm->p[0]), p1_a = smem_u32(sm->p[1]), s_a = smem_u32(sm->s);
-
-  // TMA issue (thread 0 only).  Full pass: one stage, q and k under bar_qk[0], v under bar_v[0].  State-only
-  // pass: two stages (the q and P buffers are free): stage 1 puts k in the q buffer and v in p[0].
-  auto issue_qk = [&](int ck) {
-    const int st = STATE_ONLY ? ((ck - ck_begin) & 1) : 0;
-    const uint32_t bar = smem_u32(&sm->bar_qk[st]);
-    const int r = row0 + ck * CH;
-    mbar_arrive_expect_tx(bar, STATE_ONLY ? TILE_BYTES : 2 * TILE_BYTES);
-    if (!STATE_ONLY) tma_load_2d(q_a, &tm_q, h * D, r, bar);
-    tma_load_2d(st ? q_a : k_a, &tm_k, h * D, r, bar);
-  };
-  auto issue_v = [&](int ck) {
-    const int st = STATE_ONLY ? ((ck - ck_begin) & 1) : 0;
-    const uint32_t bar = smem_u32(&sm->bar_v[st]);
-    mbar_arrive_expect_tx(bar, TILE_BYTES);
-    tma_load_2d(st ? p0_a : v_a, &tm_v, h * D, row0 + ck * CH, bar);
-  };
-  if (tid == 0) {
-    for (int ck = ck_begin; ck < ck_begin + (STATE_ONLY ? 2 : 1) && ck < ck_end; ++ck) {
-      issue_qk(ck);
-      issue_v(ck);
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      JB_T_DECL
+      for (int lc = 0; lc < n_loc; ++lc) {
+        const int s = lc & 1;
+        const uint32_t prev = uint32_t((lc >> 1) - 1) & 1u;
+        const int r = row0 + (ck_begin + lc) * CH;
+        JB_T_MARK(0)
+        if (lc >= 2 && !mbar_wait(smem_u32(&sm->empty_qk[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+        JB_T_MARK(1)
+        mbar_arrive_expect_tx(smem_u32(&sm->full_qk[s]), 2 * TILE_BYTES);
+        tma_load_2d(smem_u32(sm->q[s]), &tm_q, h * D, r, smem_u32(&sm->full_qk[s]));
+        tma_load_2d(smem_u32(sm->k[s]), &tm_k, h * D, r, smem_u32(&sm->full_qk[s]));
+        JB_T_MARK(0)
+        if (lc >= 2 && !mbar_wait(smem_u32(&sm->empty_v[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+        JB_T_MARK(2)
+        mbar_arrive_expect_tx(smem_u32(&sm->full_v[s]), TILE_BYTES);
+        tma_load_2d(smem_u32(sm->v[s]), &tm_v, h * D, r, smem_u32(&sm->full_v[s]));
+      }
+      JB_T_MARK(0)
+      JB_T_FLUSH(0)
     }
-  }
-
-  bool ok = true;
-  for (int ck = ck_begin; ck < ck_end; ++ck) {
-    const int lc = ck - ck_begin;
-    const int st = STATE_ONLY ? (lc & 1) : 0;                  // input stage of this chunk
-    const uint32_t in_ph = STATE_ONLY ? uint32_t(lc >> 1) & 1u : uint32_t(lc) & 1u;
-    const uint32_t ph = uint32_t(lc) & 1u;                     // phase of the once-per-chunk MMA barriers
-    const int c_len = min(CH, T - ck * CH);
-    uint8_t* k_p = st ? sm->q : sm->k;
-
-    if (!mbar_wait(smem_u32(&sm->bar_qk[st]), in_ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) ok = false;
-
-    // ---- prologue: feature map + RoPE on q and k (pairs d, d+32), kw = k' * gamma^(c-1-j) -------------------
-    // 128 rows x 4 column groups of 8 pairs; 2 items per thread.  Eight consecutive lanes take 4 groups of two
-    // rows that are 4 apart, so that their 16-byte accesses to the swizzled tile fall into different banks.
-    if (ok) {
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t id_sc = umma_idesc(128, 128, 0, 0), id_o2 = umma_idesc(128, 64, 0, 0);
+      constexpr uint32_t id_ds = umma_idesc(128, 64, 1, 1), id_o1 = umma_idesc(128, 64, 0, 1);
+      // operand descriptors of both stages, built once.  A K-step of 16 elements is +32 bytes (+2 in the address
+      // field) inside a K-major row, +2048 bytes (+128: two 8-row groups) in the MN-major [token][64] tiles.
+      uint64_t d_q[2], d_k[2], d_kw[2], d_va[2], d_vb[2], d_s[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        d_q[s] = umma_desc(smem_u32(sm->q[s]), 16, 1024);
+        d_k[s] = umma_desc(smem_u32(sm->k[s]), 16, 1024);
+        d_kw[s] = umma_desc(smem_u32(sm->kw[s]), 1024, 1024);
+        d_va[s] = umma_desc(smem_u32(sm->v[s]), 0, 1024);       // as the M operand of dS: the 64 dv read twice
+        d_vb[s] = umma_desc(smem_u32(sm->v[s]), 1024, 1024);    // as the N operand of P V
+        d_s[s] = umma_desc(smem_u32(sm->s[s]), 16, 1024);
+      }
+      const uint64_t d_p0 = umma_desc(smem_u32(sm->p[0]), 16, 1024), d_p1 = umma_desc(smem_u32(sm->p[1]), 16, 1024);
+      // The chunk body is instantiated per stage, so that every descriptor is a register plus a constant.
+      auto issue_scores = [&](auto stage) {
+        constexpr int s = decltype(stage)::value;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ss(tm + PT_SC + 128 * s, d_q[s] + uint64_t(ks * 2), d_k[s] + uint64_t(ks * 2), id_sc, ks != 0);
+        umma_commit(smem_u32(&sm->bar_sc[s]));
+      };
+      JB_T_DECL
+      auto chunk = [&](int lc, auto stage) -> bool {
+        constexpr int s = decltype(stage)::value;
+        const uint32_t u = uint32_t(lc >> 1) & 1u;
+        // S(lc): needs v of the chunk, and the consumers to be done with the previous dS (completion #lc of s_done,
+        // which also says that s[lc & 1] holds the state after lc chunks)
+        JB_T_MARK(0)
+        if (!mbar_wait(smem_u32(&sm->full_v[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) return false;
+        JB_T_MARK(1)
+        if (!mbar_wait(smem_u32(&sm->s_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
+        JB_T_MARK(2)
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tm + PT_DS, d_va[s] + uint64_t(ks * 128), d_kw[s] + uint64_t(ks * 128), id_ds, ks != 0);
+        umma_commit(smem_u32(&sm->bar_s));
+        // A2(lc): O2 = Q' S^T.  O2[s] was read by the output rows of chunk lc - 2, which the scores of this chunk
+        // (issued one chunk ago into SC[s]) already waited for.
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ss(tm + PT_O2 + 64 * s, d_q[s] + uint64_t(ks * 2), d_s[s] + uint64_t(ks * 2), id_o2, ks != 0);
+        umma_commit(smem_u32(&sm->empty_qk[s]));       // q, k, kw of this stage: every MMA that reads them is issued
+        // B(lc): O1 = P V into the score columns the mask step has fully read
+        JB_T_MARK(0)
+        if (!mbar_wait(smem_u32(&sm->p_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
+        JB_T_MARK(3)
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tm + PT_SC + 128 * s, (ks < 4 ? d_p0 : d_p1) + uint64_t((ks & 3) * 2), d_vb[s] + uint64_t(ks * 128),
+                       id_o1, ks != 0);
+        umma_commit(smem_u32(&sm->bar_b[s]));
+        umma_commit(smem_u32(&sm->empty_v[s]));
+        // A1(lc + 1): scores of the next chunk into the other accumulator
+        if (lc + 1 < n_loc) {
+          constexpr int s1 = s ^ 1;
+          const uint32_t u1 = uint32_t((lc + 1) >> 1);
+          JB_T_MARK(0)
+          if (!mbar_wait(smem_u32(&sm->pro_done[s1]), u1 & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
+          JB_T_MARK(4)
+          if (lc + 1 >= 2 &&
+              !mbar_wait(smem_u32(&sm->o_done[s1]), (u1 - 1u) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
+          JB_T_MARK(5)
+          tc_fence_after_sync();
+          issue_scores(std::integral_constant<int, s1>{});
+        }
+        return true;
+      };
+      bool ok = n_loc > 0 && mbar_wait(smem_u32(&sm->pro_done[0]), 0u, abort_flag, p.status, JB200_STATUS_ATTN_MMA);
+      JB_T_MARK(4)
+      if (ok) {
+        tc_fence_after_sync();
+        issue_scores(std::integral_constant<int, 0>{});
+      }
+      for (int lc = 0; ok && lc < n_loc; lc += 2) {
+        ok = chunk(lc, std::integral_constant<int, 0>{});
+        if (ok && lc + 1 < n_loc) ok = chunk(lc + 1, std::integral_constant<int, 1>{});
+      }
+      JB_T_MARK(0)
+      JB_T_FLUSH(1)
+    }
+  } else if (warp < CON_WARP0) {
+    // ---------------- prologue warps ----------------
+    const int ptid = tid - PRO_WARP0 * 32;
+    const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
+    // 128 rows x 4 column groups of 8 rotary pairs = 512 items per chunk, two per thread: (row r, group cg) and
+    // (row r + 64, group cg).  Eight consecutive lanes take 4 groups of two rows that are 4 apart, so that their
+    // 16-byte accesses to the swizzled tiles fall into different banks.
+    const int cg = ptid & 3;
+    const int r_lo = (ptid >> 5) * 8 + ((ptid >> 2) & 1) * 4 + ((ptid >> 3) & 3);
+    // RoPE angles: the thread's 8 frequencies are fixed.  The angles of its first row come from the table (the
+    // loads for the NEXT chunk are issued when a chunk is finished, so their latency passes during the wait for
+    // that chunk's tiles); its second row is 64 positions further, one fixed rotation by (cos, sin)(64 theta_i)
+    // away (angle addition in f32: error ~1e-7 against the 4e-3 of the bf16 result).  Every chunk starts from
+    // the table again, so results do not depend on how a sequence is cut into segments or calls.
+    float cs[8], sn[8], c64[8], s64[8];
+    auto load_angles = [&](int ck) {
+      int pos = pos_base + ck * CH + r_lo;
+      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+      const float4* cp = reinterpret_cast<const float4*>(p.cos_tab + size_t(pos) * 32 + cg * 8);
+      const float4* sp = reinterpret_cast<const float4*>(p.sin_tab + size_t(pos) * 32 + cg * 8);
+      const float4 a0 = __ldg(cp), a1 = __ldg(cp + 1), b0 = __ldg(sp), b1 = __ldg(sp + 1);
+      cs[0] = a0.x; cs[1] = a0.y; cs[2] = a0.z; cs[3] = a0.w; cs[4] = a1.x; cs[5] = a1.y; cs[6] = a1.z; cs[7] = a1.w;
+      sn[0] = b0.x; sn[1] = b0.y; sn[2] = b0.z; sn[3] = b0.w; sn[4] = b1.x; sn[5] = b1.y; sn[6] = b1.z; sn[7] = b1.w;
+    };
+    {
+      const int stp = 64 < p.n_pos ? 64 : p.n_pos - 1;     // tables shorter than 65 rows: rows >= 64 are past the end anyway
+      const float4* cq = reinterpret_cast<const float4*>(p.cos_tab + size_t(stp) * 32 + cg * 8);
+      const float4* sq = reinterpret_cast<const float4*>(p.sin_tab + size_t(stp) * 32 + cg * 8);
+      const float4 d0 = __ldg(cq), d1 = __ldg(cq + 1), e0 = __ldg(sq), e1 = __ldg(sq + 1);
+      c64[0] = d0.x; c64[1] = d0.y; c64[2] = d0.z; c64[3] = d0.w; c64[4] = d1.x; c64[5] = d1.y; c64[6] = d1.z; c64[7] = d1.w;
+      s64[0] = e0.x; s64[1] = e0.y; s64[2] = e0.z; s64[3] = e0.w; s64[4] = e1.x; s64[5] = e1.y; s64[6] = e1.z; s64[7] = e1.w;
+      load_angles(ck_begin);
+    }
+    JB_T_DECL
+    for (int lc = 0; lc < n_loc; ++lc) {
+      const int s = lc & 1;
+      const int ck = ck_begin + lc;
+      const int c_len = min(CH, T - ck * CH);
+      uint8_t* q_p = sm->q[s];
+      uint8_t* k_p = sm->k[s];
+      uint8_t* kw_p = sm->kw[s];
+      JB_T_MARK(0)
+      if (!mbar_wait(smem_u32(&sm->full_qk[s]), uint32_t(lc >> 1) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+      JB_T_MARK(1)
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
-        const int item = tid + it * ATTN_THREADS;
-        const int cg = item & 3;
-        const int r = (item >> 5) * 8 + ((item >> 2) & 1) * 4 + ((item >> 3) & 3);
+        const int r = r_lo + 64 * it;
         const float w = r < c_len ? sm->pw[c_len - 1 - r] : 0.f;   // rows past the end contribute nothing
         if (p.qk_prepared) {
-          // q', k' came out of the projection's epilogue: only the decay-weighted copy of k is made here
           const uint4 lo = *reinterpret_cast<const uint4*>(k_p + swz(r, cg));
           const uint4 hi = *reinterpret_cast<const uint4*>(k_p + swz(r, cg + 4));
-          *reinterpret_cast<uint4*>(sm->kw + swz(r, cg)) =
+          *reinterpret_cast<uint4*>(kw_p + swz(r, cg)) =
               make_uint4(pack_bf16x2(bf16_lo(lo.x) * w, bf16_hi(lo.x) * w), pack_bf16x2(bf16_lo(lo.y) * w, bf16_hi(lo.y) * w),
                          pack_bf16x2(bf16_lo(lo.z) * w, bf16_hi(lo.z) * w), pack_bf16x2(bf16_lo(lo.w) * w, bf16_hi(lo.w) * w));
-          *reinterpret_cast<uint4*>(sm->kw + swz(r, cg + 4)) =
+          *reinterpret_cast<uint4*>(kw_p + swz(r, cg + 4)) =
               make_uint4(pack_bf16x2(bf16_lo(hi.x) * w, bf16_hi(hi.x) * w), pack_bf16x2(bf16_lo(hi.y) * w, bf16_hi(hi.y) * w),
                          pack_bf16x2(bf16_lo(hi.z) * w, bf16_hi(hi.z) * w), pack_bf16x2(bf16_lo(hi.w) * w, bf16_hi(hi.w) * w));
           continue;
         }
-        int pos = pos_base + ck * CH + r;
-        pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
-        float cs[8], sn[8];
-        {
-          const float4* cp = reinterpret_cast<const float4*>(p.cos_tab + size_t(pos) * 32 + cg * 8);
-          const float4* sp = reinterpret_cast<const float4*>(p.sin_tab + size_t(pos) * 32 + cg * 8);
-          const float4 c0 = __ldg(cp), c1 = __ldg(cp + 1), s0 = __ldg(sp), s1 = __ldg(sp + 1);
-          cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-          sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-        }
+        // all four 16-byte pieces of the row pair first, so that their latencies overlap
+        uint4* ql_p = reinterpret_cast<uint4*>(q_p + swz(r, cg));
+        uint4* qh_p = reinterpret_cast<uint4*>(q_p + swz(r, cg + 4));
+        uint4* kl_p = reinterpret_cast<uint4*>(k_p + swz(r, cg));
+        uint4* kh_p = reinterpret_cast<uint4*>(k_p + swz(r, cg + 4));
+        const uint4 ql = *ql_p, qh = *qh_p, kl = *kl_p, kh = *kh_p;
 #pragma unroll
-        for (int which = STATE_ONLY ? 1 : 0; which < 2; ++which) {  // 0: q, 1: k
-          uint8_t* tp = which == 0 ? sm->q : k_p;
-          uint4* lo_p = reinterpret_cast<uint4*>(tp + swz(r, cg));
-          uint4* hi_p = reinterpret_cast<uint4*>(tp + swz(r, cg + 4));
-          const uint4 lo = *lo_p, hi = *hi_p;
+        for (int which = 0; which < 2; ++which) {  // 0: q, 1: k
+          const uint4 lo = which == 0 ? ql : kl, hi = which == 0 ? qh : kh;
           const uint32_t lw[4] = {lo.x, lo.y, lo.z, lo.w}, hw[4] = {hi.x, hi.y, hi.z, hi.w};
           uint32_t ol[4], oh[4], wl[4], wh[4];
 #pragma unroll
@@ -320,119 +600,135 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
               wh[j] = pack_bf16x2(h0 * w, h1 * w);
             }
           }
-          if (!(STATE_ONLY && which == 1)) {       // the state-only pass needs only the weighted copy of k
-            *lo_p = make_uint4(ol[0], ol[1], ol[2], ol[3]);
-            *hi_p = make_uint4(oh[0], oh[1], oh[2], oh[3]);
-          }
+          *(which == 0 ? ql_p : kl_p) = make_uint4(ol[0], ol[1], ol[2], ol[3]);
+          *(which == 0 ? qh_p : kh_p) = make_uint4(oh[0], oh[1], oh[2], oh[3]);
           if (which == 1) {
-            *reinterpret_cast<uint4*>(sm->kw + swz(r, cg)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
-            *reinterpret_cast<uint4*>(sm->kw + swz(r, cg + 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+            *reinterpret_cast<uint4*>(kw_p + swz(r, cg)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
+            *reinterpret_cast<uint4*>(kw_p + swz(r, cg + 4)) = make_uint4(wh[0], wh[1], wh[2], wh[3]);
+          }
+        }
+        if (it == 0) {             // advance the angles by 64 positions: to the thread's second row
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float cn = cs[e] * c64[e] - sn[e] * s64[e];
+            sn[e] = sn[e] * c64[e] + cs[e] * s64[e];
+            cs[e] = cn;
+          }
+        }
+      }
+      if (!p.qk_prepared && lc + 1 < n_loc) load_angles(ck + 1);
+      JB_T_MARK(2)
+      fence_proxy_async_smem();                          // generic-proxy writes -> visible to the tensor core
+      mbar_arrive(smem_u32(&sm->pro_done[s]));
+      JB_T_MARK(3)
+    }
+    JB_T_FLUSH(warp)
+  } else {
+    // ---------------- consumers ----------------
+    const int qd = warp & 3;                             // TMEM lane quarter of this warp
+    const int hf = (warp - CON_WARP0) >> 2;              // which half of the columns it takes
+    const uint32_t tm_lane = tm + (uint32_t(32 * qd) << 16);
+    const int i = 32 * qd + lane;                        // query row = TMEM lane
+    // fp32 state: row dv = 32*(qd&1) + lane, columns dk = 16*cg .. 16*cg+15 (the accumulator of MMA S holds the
+    // 64 dv rows twice, lanes 0-63 and 64-127, so every consumer warp finds its share in its own lane quarter)
+    const int s_row = 32 * (qd & 1) + lane;
+    const int s_cg = 2 * (qd >> 1) + hf;
+    const size_t bh = size_t(b) * p.H + h;
+    float S[16];
+    {
+      const float* sin_p = p.s_in ? p.s_in + bh * D * D + s_row * D : nullptr;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int c = 16 * s_cg + e;
+        const int d = p.qk_prepared ? (c >> 1) + 32 * (c & 1) : c;   // prepared q/k: the dk axis is interleaved
+        S[e] = sin_p ? __ldg(sin_p + d) : 0.f;
+      }
+      if (seg > 0) {   // state entering this segment: fold the earlier segments' contributions, oldest first
+        const float gL = expf(log_g * float(p.seg_chunks * CH));
+        const float* dp = p.seg_state + bh * p.n_pieces * D * D + s_row * D + 16 * s_cg;
+        for (int s2 = 0; s2 < seg; ++s2, dp += D * D) {
+#pragma unroll
+          for (int e4 = 0; e4 < 4; ++e4) {
+            const float4 v4 = __ldg(reinterpret_cast<const float4*>(dp) + e4);
+            S[4 * e4 + 0] = gL * S[4 * e4 + 0] + v4.x; S[4 * e4 + 1] = gL * S[4 * e4 + 1] + v4.y;
+            S[4 * e4 + 2] = gL * S[4 * e4 + 2] + v4.z; S[4 * e4 + 3] = gL * S[4 * e4 + 3] + v4.w;
           }
         }
       }
     }
-    fence_proxy_async_smem();   // q', k', kw (and the state copy of the previous chunk) -> visible to the tensor core
-    tc_fence_before_sync();
-    if (__syncthreads_or(!ok)) { ok = false; break; }
-    tc_fence_after_sync();
-
-    if (tid == 0) {
-      if (!STATE_ONLY) {
-        // MMA A: scores = Q' K'^T, O2 = Q' S^T
-        constexpr uint32_t id_sc = umma_idesc(128, 128, 0, 0), id_o2 = umma_idesc(128, 64, 0, 0);
+    auto publish_state = [&](int buf) {
+      uint32_t w[8];
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ss(tm + TM_SCORES, umma_desc(q_a, 16, 1024) + uint64_t(ks * 2), umma_desc(k_a, 16, 1024) + uint64_t(ks * 2),
-                       id_sc, ks != 0);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ss(tm + TM_O2, umma_desc(q_a, 16, 1024) + uint64_t(ks * 2), umma_desc(s_a, 16, 1024) + uint64_t(ks * 2),
-                       id_o2, ks != 0);
-        umma_commit(smem_u32(&sm->bar_a));
-      }
-      // MMA S: dS = V^T Kw over the chunk's tokens (16 per step = two 8-row groups of the [token][64] tiles)
-      if (mbar_wait(smem_u32(&sm->bar_v[st]), in_ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) {
-        constexpr uint32_t id_ds = umma_idesc(128, 64, 1, 1);
-        const uint32_t vv = st ? p0_a : v_a;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tm + TM_DS, umma_desc(vv + ks * 2048, 0, 1024), umma_desc(kw_a + ks * 2048, 1024, 1024), id_ds,
-                       ks != 0);
-        umma_commit(smem_u32(&sm->bar_s));
-      }
-    }
-
-    if (!STATE_ONLY) {
-      // ---- decay mask: scores -> P (bf16, K-major tiles) ------------------------------------------------------
-      if (!mbar_wait(smem_u32(&sm->bar_a), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
-      if (tid == 0 && ok && ck + 1 < ck_end) issue_qk(ck + 1);    // q and k tiles are free: both MMAs that read them are done
-      tc_fence_after_sync();
-      __syncwarp();               // tcgen05.ld is warp-collective: rejoin after the per-thread waits and thread 0's issue work
-      if (ok) {
-        const int i = 32 * qd + lane;                  // query row = TMEM lane
-#pragma unroll
-        for (int jj = 0; jj < 2; ++jj) {
-          const int jb = 2 * hf + jj;                  // 32-key block
-          if (jb > qd) continue;                       // above the diagonal for all 32 rows of this warp (stays zero)
-          uint32_t r[32];
-          tmem_ld_32x32(tm_lane + TM_SCORES + 32 * jb, r);
-          tmem_ld_wait();
-          const float* f = sm->pwm + (i - 32 * jb + CH);     // f[-c]: factor of key 32*jb + c
-          uint32_t w[16];
-#pragma unroll
-          for (int c2 = 0; c2 < 16; ++c2)
-            w[c2] = pack_bf16x2(__uint_as_float(r[2 * c2]) * f[-2 * c2], __uint_as_float(r[2 * c2 + 1]) * f[-2 * c2 - 1]);
-          uint8_t* prow = sm->p[hf];
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
-            *reinterpret_cast<uint4*>(prow + swz(i, 4 * jj + q4)) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
-        }
-      }
+      for (int e = 0; e < 8; ++e) w[e] = pack_bf16x2(S[2 * e], S[2 * e + 1]);
+      *reinterpret_cast<uint4*>(sm->s[buf] + swz(s_row, 2 * s_cg)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(sm->s[buf] + swz(s_row, 2 * s_cg + 1)) = make_uint4(w[4], w[5], w[6], w[7]);
       fence_proxy_async_smem();
       tc_fence_before_sync();
-      if (__syncthreads_or(!ok)) { ok = false; break; }
-      tc_fence_after_sync();
-      if (tid == 0) {
-        // MMA B: O1 = P V into the (fully read) scores columns
-        constexpr uint32_t id_o1 = umma_idesc(128, 64, 0, 1);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tm + TM_O1, umma_desc(ks < 4 ? p0_a : p1_a, 16, 1024) + uint64_t((ks & 3) * 2),
-                       umma_desc(v_a + ks * 2048, 1024, 1024), id_o1, ks != 0);
-        umma_commit(smem_u32(&sm->bar_b));
-      }
-    }
-
-    // ---- state update: S = gamma^c S + dS ------------------------------------------------------------------
-    if (!mbar_wait(smem_u32(&sm->bar_s), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
-    tc_fence_after_sync();
-    if (STATE_ONLY && tid == 0 && ok && ck + 2 < ck_end) {   // this chunk's k and v buffers are free again
-      issue_qk(ck + 2);
-      issue_v(ck + 2);
-    }
-    __syncwarp();
-    if (ok) {
-      uint32_t r[16];
-      tmem_ld_32x16(tm_lane + TM_DS + 16 * s_cg, r);
-      tmem_ld_wait();
-      const float gc = sm->pw[c_len];
-#pragma unroll
-      for (int e = 0; e < 16; ++e) S[e] = gc * S[e] + __uint_as_float(r[e]);
-      if (!STATE_ONLY) publish_state();      // read by the next chunk's MMA A (made visible by the fence before it)
-    }
-
-    if (!STATE_ONLY) {
-      // ---- output rows: o[i] = O1 + gamma^(i+1)/8 * O2 ------------------------------------------------------
-      if (!mbar_wait(smem_u32(&sm->bar_b), ph, &sm->abort_flag, p.status, JB200_STATUS_ATTN_MMA)) ok = false;
-      if (tid == 0 && ok && ck + 1 < ck_end) issue_v(ck + 1);     // both MMAs that read v are done
+      mbar_arrive(smem_u32(&sm->s_done));
+    };
+    publish_state(0);
+    bool ok = true;
+    JB_T_DECL
+    for (int lc = 0; lc < n_loc; ++lc) {
+      const int s = lc & 1;
+      const uint32_t u = uint32_t(lc >> 1) & 1u;
+      const int ck = ck_begin + lc;
+      const int c_len = min(CH, T - ck * CH);
+      // ---- decay mask: scores -> P ----
+      JB_T_MARK(0)
+      if (!mbar_wait(smem_u32(&sm->bar_sc[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
+      JB_T_MARK(1)
       tc_fence_after_sync();
       __syncwarp();
-      if (ok) {
-        const int i = 32 * qd + lane;
-        uint32_t a[32], c2[32];
-        tmem_ld_32x32(tm_lane + TM_O1 + 32 * hf, a);
-        tmem_ld_32x32(tm_lane + TM_O2 + 32 * hf, c2);
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int jb = 2 * hf + jj;                      // 32-key block
+        if (jb > qd) continue;                           // above the diagonal for all rows of this warp: stays zero
+        uint32_t r[32];
+        tmem_ld_32x32(tm_lane + PT_SC + 128 * s + 32 * jb, r);
         tmem_ld_wait();
+        const float* f = sm->pwm + (i - 32 * jb + CH);   // f[-c]: factor of key 32*jb + c
+        uint32_t w[16];
+#pragma unroll
+        for (int c2 = 0; c2 < 16; ++c2)
+          w[c2] = pack_bf16x2(__uint_as_float(r[2 * c2]) * f[-2 * c2], __uint_as_float(r[2 * c2 + 1]) * f[-2 * c2 - 1]);
+        uint8_t* prow = sm->p[hf];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<uint4*>(prow + swz(i, 4 * jj + q4)) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+      }
+      JB_T_MARK(2)
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sm->p_done));
+      JB_T_MARK(3)
+      // ---- state update: S = gamma^c S + dS ----
+      if (!mbar_wait(smem_u32(&sm->bar_s), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
+      JB_T_MARK(4)
+      tc_fence_after_sync();
+      __syncwarp();
+      {
+        uint32_t r[16];
+        tmem_ld_32x16(tm_lane + PT_DS + 16 * s_cg, r);
+        tmem_ld_wait();
+        const float gc = sm->pw[c_len];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) S[e] = gc * S[e] + __uint_as_float(r[e]);
+      }
+      publish_state((lc + 1) & 1);
+      JB_T_MARK(5)
+      // ---- output rows: o[i] = O1 + gamma^(i+1)/8 * O2 ----
+      if (!mbar_wait(smem_u32(&sm->bar_b[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
+      JB_T_MARK(6)
+      tc_fence_after_sync();
+      __syncwarp();
+      {
+        uint32_t a[32], c2[32];
+        tmem_ld_32x32(tm_lane + PT_SC + 128 * s + 32 * hf, a);
+        tmem_ld_32x32(tm_lane + PT_O2 + 64 * s + 32 * hf, c2);
+        tmem_ld_wait();
+        tc_fence_before_sync();
+        mbar_arrive(smem_u32(&sm->o_done[s]));           // both accumulators are in registers now
         const float g = 0.125f * sm->pw[i + 1];
         uint32_t w[16];
 #pragma unroll
@@ -451,26 +747,22 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
+      JB_T_MARK(7)
     }
-  }
-
-  // final state (or this piece's contribution)
-  float* so = nullptr;
-  if (STATE_ONLY) so = p.seg_state + ((size_t(b) * p.H + h) * p.n_pieces + seg) * D * D;
-  else if (p.s_out && seg == p.nseg - 1) so = p.s_out + (size_t(b) * p.H + h) * D * D;
-  if (ok && so) {
-    const bool natural = !STATE_ONLY && p.qk_prepared;   // pieces stay in the kernel's own column order
-    float* sp = so + s_row * D;
-    if (natural) {
+    JB_T_FLUSH(warp)
+    if (ok && p.s_out && seg == p.nseg - 1) {
+      float* sp = p.s_out + bh * D * D + s_row * D;
+      if (p.qk_prepared) {
 #pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const int c = 16 * s_cg + e;
-        sp[(c >> 1) + 32 * (c & 1)] = S[e];
+        for (int e = 0; e < 16; ++e) {
+          const int c = 16 * s_cg + e;
+          sp[(c >> 1) + 32 * (c & 1)] = S[e];
+        }
+      } else {
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4)
+          *reinterpret_cast<float4*>(sp + 16 * s_cg + 4 * e4) = make_float4(S[4 * e4], S[4 * e4 + 1], S[4 * e4 + 2], S[4 * e4 + 3]);
       }
-    } else {
-#pragma unroll
-      for (int e4 = 0; e4 < 4; ++e4)
-        *reinterpret_cast<float4*>(sp + 16 * s_cg + 4 * e4) = make_float4(S[4 * e4], S[4 * e4 + 1], S[4 * e4 + 2], S[4 * e4 + 3]);
     }
   }
 
@@ -478,7 +770,7 @@ attn_scan_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   __syncthreads();
   if (warp == 0) {
     tc_fence_after_sync();
-    tmem_dealloc(tm, TMEM_COLS);
+    tmem_dealloc(tm, PIPE_TMEM_COLS);
   }
 }
 
@@ -583,10 +875,11 @@ int make_map(CUtensorMap* tm, const void* ptr, int rows, int cols, int ld) {
 
 }  // namespace
 
-// Segments: enough CTAs to fill two per SM, each segment at least two chunks long.
+// Segments: the pipeline kernel runs one CTA per SM, so sequences are cut only when B*H leaves SMs idle;
+// each segment is at least two chunks long.
 static void pick_segments(int B, int T, int H, int sms, int* seg_chunks, int* nseg) {
   const int n_chunks = (T + CH - 1) / CH;
-  long want = (long(sms) * 2) / (long(B) * H);
+  long want = long(sms) / (long(B) * H);
   if (want < 1) want = 1;
   if (want > n_chunks / 2) want = n_chunks / 2 > 0 ? n_chunks / 2 : 1;
   int sc = int((n_chunks + want - 1) / want);
@@ -662,22 +955,29 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   p.n_pieces = o ? p.nseg - 1 : p.nseg;
   if (!o) {
     // state only: the k/v pass over every piece, then the fold
-    JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
-    attn_scan_kernel<true><<<dim3(H, B, p.nseg), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
-    JB_LAUNCH_CHECK("attn_scan_kernel<state>");
+    JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
+    attn_state_pass_kernel<<<dim3(H, B, p.nseg), STATE_THREADS, STATE_SMEM_BYTES, stream>>>(tk, tv, p);
+    JB_LAUNCH_CHECK("attn_state_pass_kernel");
     attn_fold_states_kernel<<<dim3(H, B), 256, 0, stream>>>(p);
     JB_LAUNCH_CHECK("attn_fold_states_kernel");
     return JB200_OK;
   }
-  JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
+  JB_CUDA(cudaFuncSetAttribute(attn_scan_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PIPE_SMEM_BYTES)));
   if (p.nseg > 1) {
-    JB_CUDA(cudaFuncSetAttribute(attn_scan_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ATTN_SMEM_BYTES)));
-    attn_scan_kernel<true><<<dim3(H, B, p.nseg - 1), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
-    JB_LAUNCH_CHECK("attn_scan_kernel<state>");
+    JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
+    attn_state_pass_kernel<<<dim3(H, B, p.nseg - 1), STATE_THREADS, STATE_SMEM_BYTES, stream>>>(tk, tv, p);
+    JB_LAUNCH_CHECK("attn_state_pass_kernel");
   }
-  attn_scan_kernel<false><<<dim3(H, B, p.nseg), ATTN_THREADS, ATTN_SMEM_BYTES, stream>>>(tq, tk, tv, p);
-  JB_LAUNCH_CHECK("attn_scan_kernel");
+  attn_scan_pipe_kernel<<<dim3(H, B, p.nseg), PIPE_THREADS, PIPE_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  JB_LAUNCH_CHECK("attn_scan_pipe_kernel");
   return JB200_OK;
 }
+
+#ifdef JB_ATTN_TIMING
+// Timing builds only: copies the per-role cycle counters of the last pipeline launch to the host.
+extern "C" int jb200_debug_attn_timing(long long* out) {
+  return cudaMemcpyFromSymbol(out, g_attn_timing, sizeof(long long) * 18 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 }  // namespace jb

@@ -116,13 +116,17 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t pari
 }
 
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any waiter gives up,
-// every other waiter of the CTA leaves at its next poll as well.
+// every other waiter of the CTA leaves at its next check as well.  The hardware parks a waiting warp only
+// for a short, implementation-defined time per try_wait, so the loop around it runs often: the clock and
+// the abort flag are looked at once per 32 tries to keep a waiting warp's share of the issue slots small.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag,
                                           unsigned int* status, unsigned int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
-    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
       *abort_flag = 1u;
@@ -302,7 +306,9 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   if (mbar_try_wait_cluster_parked(bar, parity, 0u)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (;;) {
-    if (mbar_try_wait_cluster_parked(bar, parity, 20000u)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait_cluster_parked(bar, parity, 20000u)) return true;
     if (*abort_flag) return false;
     if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
       *abort_flag = 1u;
