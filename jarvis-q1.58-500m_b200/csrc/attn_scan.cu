@@ -106,9 +106,16 @@ __device__ __forceinline__ void st_global_256(void* p, const uint32_t* w) {
                : "memory");
 }
 
-// ELU(x)+1 = x+1 for x > 0, exp(x) otherwise; exp through ex2.approx (rel. error 2^-22, far below the bf16
-// rounding of the result).  For large positive x the unused exp is +inf, never NaN.
-__device__ __forceinline__ float elu1(float x) { return x > 0.f ? x + 1.0f : __expf(x); }
+// ELU(x)+1 = max(x, 0) + exp(min(x, 0)) = (x + |x|)/2 + 2^((x - |x|) * log2(e)/2): two adds, one multiply, one
+// ex2.approx (flush-to-zero form: a single MUFU, rel. error 2^-22, far below the bf16 rounding of the result) and
+// one fused multiply-add, all on the FMA / MUFU pipes - no compare, no select.  For x > 0 the exponent is exactly
+// 0 and the result is x + 1 rounded once; for x <= 0 the first term is exactly 0.
+__device__ __forceinline__ float elu1(float x) {
+  const float ax = fabsf(x);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"((x - ax) * 0.72134752044448170368f));
+  return fmaf(x + ax, 0.5f, e);
+}
 
 // ------------------------------------------------------------------------------------------------------------
 // k/v-only pass: the state contribution of one piece of a sequence from a zero state (pieces = the non-final
@@ -477,6 +484,17 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
         for (int ks = 0; ks < 4; ++ks)
           umma_bf16_ss(tm + PT_O2 + 64 * s, d_q[s] + uint64_t(ks * 2), d_s[s] + uint64_t(ks * 2), id_o2, ks != 0);
         umma_commit(smem_u32(&sm->empty_qk[s]));       // q, k, kw of this stage: every MMA that reads them is issued
+        // A1(lc + 1): scores of the next chunk into the other accumulator, ahead of B(lc) when the next chunk's
+        // prologue is already done (then the consumers find them ready when they finish this chunk)
+        constexpr int s1 = s ^ 1;
+        const uint32_t u1 = uint32_t((lc + 1) >> 1);
+        bool scores_issued = lc + 1 >= n_loc;
+        if (!scores_issued && mbar_try_wait(smem_u32(&sm->pro_done[s1]), u1 & 1u) &&
+            (lc + 1 < 2 || mbar_try_wait(smem_u32(&sm->o_done[s1]), (u1 - 1u) & 1u))) {
+          tc_fence_after_sync();
+          issue_scores(std::integral_constant<int, s1>{});
+          scores_issued = true;
+        }
         // B(lc): O1 = P V into the score columns the mask step has fully read
         JB_T_MARK(0)
         if (!mbar_wait(smem_u32(&sm->p_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
@@ -488,10 +506,7 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                        id_o1, ks != 0);
         umma_commit(smem_u32(&sm->bar_b[s]));
         umma_commit(smem_u32(&sm->empty_v[s]));
-        // A1(lc + 1): scores of the next chunk into the other accumulator
-        if (lc + 1 < n_loc) {
-          constexpr int s1 = s ^ 1;
-          const uint32_t u1 = uint32_t((lc + 1) >> 1);
+        if (!scores_issued) {
           JB_T_MARK(0)
           if (!mbar_wait(smem_u32(&sm->pro_done[s1]), u1 & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
           JB_T_MARK(4)
