@@ -334,24 +334,34 @@ __device__ long long g_attn_timing[18 * 8];
 
 constexpr int PIPE_THREADS = 576;
 constexpr int PRO_WARP0 = 2, CON_WARP0 = 10;
+constexpr int NST = 3;                                       // stages of the q / k / kw / v tiles
 constexpr uint32_t PIPE_TMEM_COLS = 512;
-constexpr uint32_t PT_SC = 0, PT_O2 = 256, PT_DS = 384;     // SC[2] x 128, O2[2] x 64, DS x 64
+constexpr uint32_t PT_SC = 0, PT_O2 = 256, PT_DS = 384, PT_P = 448;   // SC[2] x 128, O2[2] x 64, DS x 64, P x 64
 
 struct PipeSmem {
-  uint8_t q[2][TILE_BYTES];
-  uint8_t k[2][TILE_BYTES];
-  uint8_t kw[2][TILE_BYTES];
-  uint8_t v[2][TILE_BYTES];
-  uint8_t p[2][TILE_BYTES];    // P as two K-major tiles (keys 0-63, 64-127)
+  uint8_t q[NST][TILE_BYTES];
+  uint8_t k[NST][TILE_BYTES];
+  uint8_t kw[NST][TILE_BYTES];
+  uint8_t v[NST][TILE_BYTES];
   uint8_t s[2][S_BYTES];       // bf16 state copy, [n & 1] = state after n chunks of this CTA
-  float pwm[2 * CH];
-  float pw[CH + 1];
-  uint64_t full_qk[2], full_v[2], empty_qk[2], empty_v[2], pro_done[2], bar_sc[2], bar_b[2], o_done[2];
+  float pwm[2 * CH];           // pwm[x + CH] = gamma^x / 8 for x >= 0, 0 for x < 0: the decay mask by (i - j)
+  float pw[CH + 1];            // gamma^n
+  uint64_t full_qk[NST], full_v[NST], empty_qk[NST], empty_v[NST], pro_done[NST];
+  uint64_t bar_sc[2], bar_b[2], o_done[2];
   uint64_t bar_s, s_done, p_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 constexpr size_t PIPE_SMEM_BYTES = sizeof(PipeSmem) + 1024;
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 
 __global__ void __launch_bounds__(PIPE_THREADS, 1)
 attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -373,12 +383,14 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const float log_g = logf(__ldg(p.gamma + h));
 
   if (tid == 0) {
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(smem_u32(&sm->full_qk[s]), 1);
       mbar_init(smem_u32(&sm->full_v[s]), 1);
       mbar_init(smem_u32(&sm->empty_qk[s]), 1);
       mbar_init(smem_u32(&sm->empty_v[s]), 1);
       mbar_init(smem_u32(&sm->pro_done[s]), 256);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&sm->bar_sc[s]), 1);
       mbar_init(smem_u32(&sm->bar_b[s]), 1);
       mbar_init(smem_u32(&sm->o_done[s]), 256);
@@ -393,20 +405,17 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tma_prefetch_desc(&tm_v);
   }
   if (warp == 0) {
-    __syncwarp();
+    __syncwarp();                 // tcgen05.alloc is warp-collective: lane 0 rejoins from the barrier set-up first
     tmem_alloc(smem_u32(&sm->tmem_base), PIPE_TMEM_COLS);
     tmem_relinquish();
   }
   for (int n = tid; n <= CH; n += PIPE_THREADS) sm->pw[n] = expf(log_g * float(n));
   for (int n = tid; n < 2 * CH; n += PIPE_THREADS) {
+    // gamma^(i-j) / sqrt(D): the 1/8 of the query feature map is a power of two, so applying it to the scores
+    // (and to the cross-chunk factor) instead of to every element of q gives the same bits
     const int x = n - CH;
     sm->pwm[n] = x >= 0 ? 0.125f * expf(log_g * float(x)) : 0.f;
   }
-  {
-    uint4* pz = reinterpret_cast<uint4*>(sm->p[0]);   // blocks of P above the diagonal are never written again
-    for (int e = tid; e < 2 * TILE_BYTES / 16; e += PIPE_THREADS) pz[e] = make_uint4(0u, 0u, 0u, 0u);
-  }
-  fence_proxy_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -417,21 +426,22 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       JB_T_DECL
+      int s = 0;
+      uint32_t prev = 1u;                       // parity of the PREVIOUS use of the stage
       for (int lc = 0; lc < n_loc; ++lc) {
-        const int s = lc & 1;
-        const uint32_t prev = uint32_t((lc >> 1) - 1) & 1u;
         const int r = row0 + (ck_begin + lc) * CH;
         JB_T_MARK(0)
-        if (lc >= 2 && !mbar_wait(smem_u32(&sm->empty_qk[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+        if (lc >= NST && !mbar_wait(smem_u32(&sm->empty_qk[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
         JB_T_MARK(1)
         mbar_arrive_expect_tx(smem_u32(&sm->full_qk[s]), 2 * TILE_BYTES);
         tma_load_2d(smem_u32(sm->q[s]), &tm_q, h * D, r, smem_u32(&sm->full_qk[s]));
         tma_load_2d(smem_u32(sm->k[s]), &tm_k, h * D, r, smem_u32(&sm->full_qk[s]));
         JB_T_MARK(0)
-        if (lc >= 2 && !mbar_wait(smem_u32(&sm->empty_v[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+        if (lc >= NST && !mbar_wait(smem_u32(&sm->empty_v[s]), prev, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
         JB_T_MARK(2)
         mbar_arrive_expect_tx(smem_u32(&sm->full_v[s]), TILE_BYTES);
         tma_load_2d(smem_u32(sm->v[s]), &tm_v, h * D, r, smem_u32(&sm->full_v[s]));
+        if (++s == NST) { s = 0; prev ^= 1u; }
       }
       JB_T_MARK(0)
       JB_T_FLUSH(0)
@@ -441,92 +451,89 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     if (lane == 0) {
       constexpr uint32_t id_sc = umma_idesc(128, 128, 0, 0), id_o2 = umma_idesc(128, 64, 0, 0);
       constexpr uint32_t id_ds = umma_idesc(128, 64, 1, 1), id_o1 = umma_idesc(128, 64, 0, 1);
-      // operand descriptors of both stages, built once.  A K-step of 16 elements is +32 bytes (+2 in the address
-      // field) inside a K-major row, +2048 bytes (+128: two 8-row groups) in the MN-major [token][64] tiles.
-      uint64_t d_q[2], d_k[2], d_kw[2], d_va[2], d_vb[2], d_s[2];
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        d_q[s] = umma_desc(smem_u32(sm->q[s]), 16, 1024);
-        d_k[s] = umma_desc(smem_u32(sm->k[s]), 16, 1024);
-        d_kw[s] = umma_desc(smem_u32(sm->kw[s]), 1024, 1024);
-        d_va[s] = umma_desc(smem_u32(sm->v[s]), 0, 1024);       // as the M operand of dS: the 64 dv read twice
-        d_vb[s] = umma_desc(smem_u32(sm->v[s]), 1024, 1024);    // as the N operand of P V
-        d_s[s] = umma_desc(smem_u32(sm->s[s]), 16, 1024);
-      }
-      const uint64_t d_p0 = umma_desc(smem_u32(sm->p[0]), 16, 1024), d_p1 = umma_desc(smem_u32(sm->p[1]), 16, 1024);
-      // The chunk body is instantiated per stage, so that every descriptor is a register plus a constant.
-      auto issue_scores = [&](auto stage) {
-        constexpr int s = decltype(stage)::value;
+      // Operand descriptors of stage 0; stage s is +s*TILE_BYTES (+1024 in the address field).  A K-step of 16
+      // elements is +32 bytes (+2) inside a K-major row, +2048 bytes (+128: two 8-row groups) in the MN-major
+      // [token][64] tiles.
+      constexpr uint64_t STG = TILE_BYTES >> 4;
+      const uint64_t d_q0 = umma_desc(smem_u32(sm->q[0]), 16, 1024), d_k0 = umma_desc(smem_u32(sm->k[0]), 16, 1024);
+      const uint64_t d_kw0 = umma_desc(smem_u32(sm->kw[0]), 1024, 1024);
+      const uint64_t d_va0 = umma_desc(smem_u32(sm->v[0]), 0, 1024);      // as the M operand of dS: the 64 dv read twice
+      const uint64_t d_vb0 = umma_desc(smem_u32(sm->v[0]), 1024, 1024);   // as the N operand of P V
+      const uint64_t d_s0 = umma_desc(smem_u32(sm->s[0]), 16, 1024);
+      auto issue_scores = [&](int stage, int buf) {
+        const uint64_t dq = d_q0 + uint64_t(stage) * STG, dk = d_k0 + uint64_t(stage) * STG;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ss(tm + PT_SC + 128 * s, d_q[s] + uint64_t(ks * 2), d_k[s] + uint64_t(ks * 2), id_sc, ks != 0);
-        umma_commit(smem_u32(&sm->bar_sc[s]));
+          umma_bf16_ss(tm + PT_SC + 128 * buf, dq + uint64_t(ks * 2), dk + uint64_t(ks * 2), id_sc, ks != 0);
+        umma_commit(smem_u32(&sm->bar_sc[buf]));
       };
       JB_T_DECL
-      auto chunk = [&](int lc, auto stage) -> bool {
-        constexpr int s = decltype(stage)::value;
-        const uint32_t u = uint32_t(lc >> 1) & 1u;
-        // S(lc): needs v of the chunk, and the consumers to be done with the previous dS (completion #lc of s_done,
-        // which also says that s[lc & 1] holds the state after lc chunks)
-        JB_T_MARK(0)
-        if (!mbar_wait(smem_u32(&sm->full_v[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) return false;
-        JB_T_MARK(1)
-        if (!mbar_wait(smem_u32(&sm->s_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
-        JB_T_MARK(2)
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tm + PT_DS, d_va[s] + uint64_t(ks * 128), d_kw[s] + uint64_t(ks * 128), id_ds, ks != 0);
-        umma_commit(smem_u32(&sm->bar_s));
-        // A2(lc): O2 = Q' S^T.  O2[s] was read by the output rows of chunk lc - 2, which the scores of this chunk
-        // (issued one chunk ago into SC[s]) already waited for.
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_bf16_ss(tm + PT_O2 + 64 * s, d_q[s] + uint64_t(ks * 2), d_s[s] + uint64_t(ks * 2), id_o2, ks != 0);
-        umma_commit(smem_u32(&sm->empty_qk[s]));       // q, k, kw of this stage: every MMA that reads them is issued
-        // A1(lc + 1): scores of the next chunk into the other accumulator, ahead of B(lc) when the next chunk's
-        // prologue is already done (then the consumers find them ready when they finish this chunk)
-        constexpr int s1 = s ^ 1;
-        const uint32_t u1 = uint32_t((lc + 1) >> 1);
-        bool scores_issued = lc + 1 >= n_loc;
-        if (!scores_issued && mbar_try_wait(smem_u32(&sm->pro_done[s1]), u1 & 1u) &&
-            (lc + 1 < 2 || mbar_try_wait(smem_u32(&sm->o_done[s1]), (u1 - 1u) & 1u))) {
-          tc_fence_after_sync();
-          issue_scores(std::integral_constant<int, s1>{});
-          scores_issued = true;
-        }
-        // B(lc): O1 = P V into the score columns the mask step has fully read
-        JB_T_MARK(0)
-        if (!mbar_wait(smem_u32(&sm->p_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
-        JB_T_MARK(3)
-        tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma_bf16_ss(tm + PT_SC + 128 * s, (ks < 4 ? d_p0 : d_p1) + uint64_t((ks & 3) * 2), d_vb[s] + uint64_t(ks * 128),
-                       id_o1, ks != 0);
-        umma_commit(smem_u32(&sm->bar_b[s]));
-        umma_commit(smem_u32(&sm->empty_v[s]));
-        if (!scores_issued) {
-          JB_T_MARK(0)
-          if (!mbar_wait(smem_u32(&sm->pro_done[s1]), u1 & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
-          JB_T_MARK(4)
-          if (lc + 1 >= 2 &&
-              !mbar_wait(smem_u32(&sm->o_done[s1]), (u1 - 1u) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) return false;
-          JB_T_MARK(5)
-          tc_fence_after_sync();
-          issue_scores(std::integral_constant<int, s1>{});
-        }
-        return true;
-      };
       bool ok = n_loc > 0 && mbar_wait(smem_u32(&sm->pro_done[0]), 0u, abort_flag, p.status, JB200_STATUS_ATTN_MMA);
       JB_T_MARK(4)
       if (ok) {
         tc_fence_after_sync();
-        issue_scores(std::integral_constant<int, 0>{});
+        issue_scores(0, 0);
       }
-      for (int lc = 0; ok && lc < n_loc; lc += 2) {
-        ok = chunk(lc, std::integral_constant<int, 0>{});
-        if (ok && lc + 1 < n_loc) ok = chunk(lc + 1, std::integral_constant<int, 1>{});
+      int s = 0;                                 // stage of chunk lc
+      uint32_t sp = 0u;                          // parity of this use of the stage
+      for (int lc = 0; ok && lc < n_loc; ++lc) {
+        const int buf = lc & 1;                  // accumulator buffers SC / O2 and the state copy alternate
+        const uint32_t u = uint32_t(lc >> 1) & 1u;
+        const int s1 = s + 1 == NST ? 0 : s + 1; // stage and parity of chunk lc + 1
+        const uint32_t sp1 = s + 1 == NST ? sp ^ 1u : sp;
+        const uint64_t dq = d_q0 + uint64_t(s) * STG, dkw = d_kw0 + uint64_t(s) * STG;
+        const uint64_t dva = d_va0 + uint64_t(s) * STG, dvb = d_vb0 + uint64_t(s) * STG;
+        const uint64_t ds = d_s0 + uint64_t(buf) * (S_BYTES >> 4);
+        // S(lc): needs v of the chunk, and the consumers to be done with the previous dS (completion #lc of s_done,
+        // which also says that s[lc & 1] holds the state after lc chunks)
+        JB_T_MARK(0)
+        if (!mbar_wait(smem_u32(&sm->full_v[s]), sp, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+        JB_T_MARK(1)
+        if (!mbar_wait(smem_u32(&sm->s_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) break;
+        JB_T_MARK(2)
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ss(tm + PT_DS, dva + uint64_t(ks * 128), dkw + uint64_t(ks * 128), id_ds, ks != 0);
+        umma_commit(smem_u32(&sm->bar_s));
+        // A2(lc): O2 = Q' S^T.  O2[buf] was read by the output rows of chunk lc - 2, which the scores of this chunk
+        // (issued into SC[buf] earlier) already waited for.
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_bf16_ss(tm + PT_O2 + 64 * buf, dq + uint64_t(ks * 2), ds + uint64_t(ks * 2), id_o2, ks != 0);
+        umma_commit(smem_u32(&sm->empty_qk[s]));       // q, k, kw of this stage: every MMA that reads them is issued
+        // A1(lc + 1): scores of the next chunk into the other accumulator, ahead of B(lc) when the next chunk's
+        // prologue is already done (then the consumers find them ready when they finish this chunk)
+        bool scores_issued = lc + 1 >= n_loc;
+        if (!scores_issued && mbar_try_wait(smem_u32(&sm->pro_done[s1]), sp1) &&
+            (lc + 1 < 2 || mbar_try_wait(smem_u32(&sm->o_done[buf ^ 1]), (uint32_t((lc + 1) >> 1) - 1u) & 1u))) {
+          tc_fence_after_sync();
+          issue_scores(s1, buf ^ 1);
+          scores_issued = true;
+        }
+        // B(lc): O1 = P V into the score columns the mask step has fully read; P (bf16 pairs) is read from TMEM
+        JB_T_MARK(0)
+        if (!mbar_wait(smem_u32(&sm->p_done), uint32_t(lc) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) break;
+        JB_T_MARK(3)
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma_bf16_ts(tm + PT_SC + 128 * buf, tm + PT_P + ks * 8, dvb + uint64_t(ks * 128), id_o1, ks != 0);
+        umma_commit(smem_u32(&sm->bar_b[buf]));
+        umma_commit(smem_u32(&sm->empty_v[s]));
+        if (!scores_issued) {
+          JB_T_MARK(0)
+          if (!mbar_wait(smem_u32(&sm->pro_done[s1]), sp1, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) break;
+          JB_T_MARK(4)
+          if (lc + 1 >= 2 && !mbar_wait(smem_u32(&sm->o_done[buf ^ 1]), (uint32_t((lc + 1) >> 1) - 1u) & 1u, abort_flag,
+                                        p.status, JB200_STATUS_ATTN_MMA)) break;
+          JB_T_MARK(5)
+          tc_fence_after_sync();
+          issue_scores(s1, buf ^ 1);
+        }
+        (void)u;
+        s = s1;
+        sp = sp1;
       }
       JB_T_MARK(0)
       JB_T_FLUSH(1)
@@ -565,21 +572,23 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       load_angles(ck_begin);
     }
     JB_T_DECL
+    int s = 0;
+    uint32_t sp = 0u;
     for (int lc = 0; lc < n_loc; ++lc) {
-      const int s = lc & 1;
       const int ck = ck_begin + lc;
       const int c_len = min(CH, T - ck * CH);
       uint8_t* q_p = sm->q[s];
       uint8_t* k_p = sm->k[s];
       uint8_t* kw_p = sm->kw[s];
       JB_T_MARK(0)
-      if (!mbar_wait(smem_u32(&sm->full_qk[s]), uint32_t(lc >> 1) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+      if (!mbar_wait(smem_u32(&sm->full_qk[s]), sp, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
       JB_T_MARK(1)
 #pragma unroll
       for (int it = 0; it < 2; ++it) {
         const int r = r_lo + 64 * it;
         const float w = r < c_len ? sm->pw[c_len - 1 - r] : 0.f;   // rows past the end contribute nothing
         if (p.qk_prepared) {
+          // q', k' came out of the projection's epilogue: only the decay-weighted copy of k is made here
           const uint4 lo = *reinterpret_cast<const uint4*>(k_p + swz(r, cg));
           const uint4 hi = *reinterpret_cast<const uint4*>(k_p + swz(r, cg + 4));
           *reinterpret_cast<uint4*>(kw_p + swz(r, cg)) =
@@ -636,6 +645,7 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       fence_proxy_async_smem();                          // generic-proxy writes -> visible to the tensor core
       mbar_arrive(smem_u32(&sm->pro_done[s]));
       JB_T_MARK(3)
+      if (++s == NST) { s = 0; sp ^= 1u; }
     }
     JB_T_FLUSH(warp)
   } else {
@@ -649,6 +659,19 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     const int s_row = 32 * (qd & 1) + lane;
     const int s_cg = 2 * (qd >> 1) + hf;
     const size_t bh = size_t(b) * p.H + h;
+    // P lives in TMEM as bf16 pairs: lane = query row, column c = keys 2c, 2c+1.  32-key blocks above the diagonal
+    // of this warp's rows are never written by the mask step: zero them once.
+    {
+      uint32_t z[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) z[e] = 0u;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const int jb = 2 * hf + jj;
+        if (jb > qd) tmem_st_32x16(tm_lane + PT_P + 16 * jb, z);
+      }
+      tmem_st_wait();
+    }
     float S[16];
     {
       const float* sin_p = p.s_in ? p.s_in + bh * D * D + s_row * D : nullptr;
@@ -685,35 +708,32 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     bool ok = true;
     JB_T_DECL
     for (int lc = 0; lc < n_loc; ++lc) {
-      const int s = lc & 1;
+      const int buf = lc & 1;
       const uint32_t u = uint32_t(lc >> 1) & 1u;
       const int ck = ck_begin + lc;
       const int c_len = min(CH, T - ck * CH);
       // ---- decay mask: scores -> P ----
       JB_T_MARK(0)
-      if (!mbar_wait(smem_u32(&sm->bar_sc[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&sm->bar_sc[buf]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
       JB_T_MARK(1)
       tc_fence_after_sync();
-      __syncwarp();
+      __syncwarp();               // tcgen05.ld / st are warp-collective: rejoin after the per-thread wait
 #pragma unroll
       for (int jj = 0; jj < 2; ++jj) {
         const int jb = 2 * hf + jj;                      // 32-key block
         if (jb > qd) continue;                           // above the diagonal for all rows of this warp: stays zero
         uint32_t r[32];
-        tmem_ld_32x32(tm_lane + PT_SC + 128 * s + 32 * jb, r);
+        tmem_ld_32x32(tm_lane + PT_SC + 128 * buf + 32 * jb, r);
         tmem_ld_wait();
         const float* f = sm->pwm + (i - 32 * jb + CH);   // f[-c]: factor of key 32*jb + c
         uint32_t w[16];
 #pragma unroll
         for (int c2 = 0; c2 < 16; ++c2)
           w[c2] = pack_bf16x2(__uint_as_float(r[2 * c2]) * f[-2 * c2], __uint_as_float(r[2 * c2 + 1]) * f[-2 * c2 - 1]);
-        uint8_t* prow = sm->p[hf];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(prow + swz(i, 4 * jj + q4)) = make_uint4(w[4 * q4], w[4 * q4 + 1], w[4 * q4 + 2], w[4 * q4 + 3]);
+        tmem_st_32x16(tm_lane + PT_P + 16 * jb, w);
       }
+      tmem_st_wait();
       JB_T_MARK(2)
-      fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&sm->p_done));
       JB_T_MARK(3)
@@ -733,17 +753,17 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       publish_state((lc + 1) & 1);
       JB_T_MARK(5)
       // ---- output rows: o[i] = O1 + gamma^(i+1)/8 * O2 ----
-      if (!mbar_wait(smem_u32(&sm->bar_b[s]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&sm->bar_b[buf]), u, abort_flag, p.status, JB200_STATUS_ATTN_MMA)) { ok = false; break; }
       JB_T_MARK(6)
       tc_fence_after_sync();
       __syncwarp();
       {
         uint32_t a[32], c2[32];
-        tmem_ld_32x32(tm_lane + PT_SC + 128 * s + 32 * hf, a);
-        tmem_ld_32x32(tm_lane + PT_O2 + 64 * s + 32 * hf, c2);
+        tmem_ld_32x32(tm_lane + PT_SC + 128 * buf + 32 * hf, a);
+        tmem_ld_32x32(tm_lane + PT_O2 + 64 * buf + 32 * hf, c2);
         tmem_ld_wait();
         tc_fence_before_sync();
-        mbar_arrive(smem_u32(&sm->o_done[s]));           // both accumulators are in registers now
+        mbar_arrive(smem_u32(&sm->o_done[buf]));         // both accumulators are in registers now
         const float g = 0.125f * sm->pw[i + 1];
         uint32_t w[16];
 #pragma unroll
