@@ -6,14 +6,28 @@
 
 One JSON line on stdout (rank 0).  A step is one full prefill forward of the hot path over one
 batch of synthetic token ids (uniform over the vocabulary) with random-init, absmean-quantised
-2-bit packed weights.  `value` is whole-job tokens/s with the ids resident in HBM; `e2e` is the same
-through the public module API (`Jarvis.forward`) with the ids copied from pinned host memory and the
-last-position logits copied back every step.  `roofline` describes the dominant kernel (the tcgen05
-ternary GEMM) from CUDA events recorded around every one of its launches inside the timed region.
+2-bit packed weights.  `value` is whole-job tokens/s with the ids resident in HBM (nothing but the
+forward inside the timed loop); `e2e` is the same through the public module API (`Jarvis.forward`)
+with the ids copied from pinned host memory and the last-position logits copied back every step.
+
+After the two timed loops a separate pass of a few steps brackets every launch of the three kernel
+classes of the metric with CUDA events on the launching stream: `roofline` describes the dominant
+kernel (the tcgen05 ternary GEMM, against the bf16 tensor peak: the burst figure when the SM clock
+sampled during the timed loop stayed near its maximum, else the sustained one; both fractions are
+given), `roofline_scans` the attention scan and the LSF scan against the HBM copy peak.
+
 `cpu_baseline` / `--impl reference` time the CPU oracle (the reference algorithm restated in torch
 fp32, weights re-quantised per call as the reference does) on a bounded sample of the same workload.
-Multi-GPU: sequences are data-parallel, one independent B=8 batch per GPU (weak scaling); the block
-has no cross-sequence exchange apart from the per-call LSF decay, which stays per batch.
+
+Multi-GPU: the headline line is data parallel over sequences, one independent B=8 batch per GPU
+(weak scaling, no data-path collective: the block has no cross-sequence exchange apart from the
+per-call LSF decay, which stays per batch).  With N > 1 the forms of the path that DO communicate are
+timed afterwards and reported under `multi_gpu`:
+  strong  ONE B=8 batch split over the ranks; every layer all-reduces its MoE statistics
+  ep      the ternary top-2 MoE layer alone on 65,536 tokens, experts spread over the ranks, token rows
+          exchanged over NVLink (Zipf(1.2)-skewed and balanced routing), against one GPU doing all of it
+  cp      B=2 x T=65,536 hidden states with every sequence cut across the ranks (context parallel:
+          per-layer all-gather of the scans' end states)
 """
 from __future__ import annotations
 
@@ -35,10 +49,14 @@ CFG = dict(vocab=50257, d_model=1024, n_layers=24, n_heads=16, n_experts=4, top_
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each of the four GEMM shapes of a layer, from ncu
-# captures of the same kernel (profiles/ternary_gemm_kernel_qkv_and_w2.md): q/k/v 80.9 MB, out-proj + residual
-# 111.5 MB, expert w1 + GELU 152.5 MB, expert w2 174.8 MB.  Below the algorithmic bytes (135 / 168 / 203 / 203 MB)
-# because part of every output is still in L2 when the kernel ends.
+# captures of the same kernel: q/k/v 80.9 MB, out-proj + residual 111.5 MB, expert w1 + GELU 152.5 MB, expert w2
+# 174.8 MB.  Below the algorithmic bytes (135 / 168 / 203 / 203 MB) because part of every output is still in L2
+# when the kernel ends.
 GEMM_DRAM_BYTES_PER_LAUNCH = (80.9e6 + 111.5e6 + 152.5e6 + 174.8e6) / 4
+# the same two counters for one launch of the attention pipeline kernel (B=8 x T=2048: 136.3 MB algorithmic) and
+# of the LSF scan with the fused f32 residual (167.8 MB algorithmic)
+ATTN_DRAM_BYTES_PER_LAUNCH = 114.5e6
+LSF_DRAM_BYTES_PER_LAUNCH = None
 
 
 def measured_peaks():
@@ -117,46 +135,81 @@ def build_model(device, seed=0):
     return model.eval()
 
 
-class GemmTimer:
-    """Wraps ops.ternary_linear / ternary_linear_grouped to bracket every launch with CUDA events on
-    the launching stream and to add up the algorithmic flops (2*M*N*K; for the grouped form M is the
-    number of dispatched rows)."""
+class KernelTimers:
+    """Wraps the ops entry points of the three kernel classes of the metric (ternary GEMMs, attention scan,
+    LSF scan) to bracket every launch with CUDA events on the launching stream and to add up the algorithmic
+    work: 2*M*N*K flops per GEMM (grouped form: M = dispatched rows), 512 B per token-head (+ the f32 state
+    written) per attention scan, bytes read + written per LSF scan (2 B per bf16 element in, 8 B per element
+    for the fused f32 residual read-modify-write, or the output's element size)."""
 
     def __init__(self, ops):
         self.ops = ops
-        self.events = []
-        self.flops = 0.0
         self.enabled = False
-        self._lin, self._grp = ops.ternary_linear, ops.ternary_linear_grouped
+        self.ev = {"gemm": [], "attn": [], "lsf": []}
+        self.work = {"gemm": 0.0, "attn": 0.0, "lsf": 0.0}
+        self._orig = (ops.ternary_linear, ops.ternary_linear_grouped, ops.attn_scan, ops.lsf_scan)
+
+    def _timed(self, kind, work, fn, *a, **kw):
+        if not self.enabled:
+            return fn(*a, **kw)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn(*a, **kw)
+        e1.record()
+        self.ev[kind].append((e0, e1))
+        self.work[kind] += work
+        return out
 
     def install(self):
-        def lin(x, packed, alpha, **kw):
-            if not self.enabled:
-                return self._lin(x, packed, alpha, **kw)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            out = self._lin(x, packed, alpha, **kw)
-            b.record()
-            self.events.append((a, b))
-            self.flops += 2.0 * x.shape[0] * x.shape[1] * packed.shape[0]
-            return out
+        lin, grp, attn, lsf = self._orig
 
-        def grp(x, packed, alpha, offs, **kw):
-            if not self.enabled:
-                return self._grp(x, packed, alpha, offs, **kw)
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            out = self._grp(x, packed, alpha, offs, **kw)
-            b.record()
-            self.events.append((a, b))
-            self.flops += 2.0 * x.shape[0] * x.shape[1] * packed.shape[1]
-            return out
+        def t_lin(x, packed, alpha, **kw):
+            return self._timed("gemm", 2.0 * x.shape[0] * x.shape[1] * packed.shape[0], lin, x, packed, alpha, **kw)
 
-        self.ops.ternary_linear, self.ops.ternary_linear_grouped = lin, grp
+        def t_grp(x, packed, alpha, offs, **kw):
+            return self._timed("gemm", 2.0 * x.shape[0] * x.shape[1] * packed.shape[1], grp, x, packed, alpha, offs, **kw)
 
-    def summary(self):
-        ms = sum(a.elapsed_time(b) for a, b in self.events)
-        return len(self.events), ms, self.flops
+        def t_attn(q, k, v, gamma, cos, sin, B, T, H, **kw):
+            work = 512.0 * B * T * H + (B * H * 64 * 64 * 4 if kw.get("want_state") or kw.get("state_out") is not None else 0)
+            return self._timed("attn", work, attn, q, k, v, gamma, cos, sin, B, T, H, **kw)
+
+        def t_lsf(m, **kw):
+            n = m.numel()
+            work = float(n * m.element_size())
+            if kw.get("resid") is not None:
+                work += 8.0 * n
+            if kw.get("want_out", True):
+                work += float(n * (4 if kw.get("out_dtype") == torch.float32 else m.element_size()))
+            return self._timed("lsf", work, lsf, m, **kw)
+
+        self.ops.ternary_linear, self.ops.ternary_linear_grouped = t_lin, t_grp
+        self.ops.attn_scan, self.ops.lsf_scan = t_attn, t_lsf
+
+    def uninstall(self):
+        (self.ops.ternary_linear, self.ops.ternary_linear_grouped, self.ops.attn_scan, self.ops.lsf_scan) = self._orig
+
+    def summary(self, kind):
+        ms = sum(a.elapsed_time(b) for a, b in self.ev[kind])
+        return len(self.ev[kind]), ms, self.work[kind]
+
+
+def _max_over_ranks(values, device, world):
+    t = torch.tensor(values, dtype=torch.float64, device=device)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def _time_steps(fn, n, barrier):
+    """CUDA-event time of n calls of fn in ms, bracketed by barriers."""
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1)
 
 
 def run_ours(args, rank, world, local_rank):
@@ -175,8 +228,6 @@ def run_ours(args, rank, world, local_rank):
     idx_dev = torch.randint(0, CFG["vocab"], (B, T), generator=gen, device=device)
     idx_host = idx_dev.cpu().pin_memory()
     last_host = torch.empty((B, CFG["vocab"]), dtype=torch.bfloat16).pin_memory()
-    timer = GemmTimer(ops)
-    timer.install()
 
     def barrier():
         torch.cuda.synchronize()
@@ -198,47 +249,47 @@ def run_ours(args, rank, world, local_rank):
     barrier()
     assert _lib.device_status() == 0, "a bounded wait ran out during warm-up"
 
-    # ---- device-resident throughput ------------------------------------------------------------
+    # ---- device-resident throughput: nothing but the forward inside the timed loop ---------------
     sampler = ClockSampler(local_rank)
     sampler.start()
     _lib.kernel_launches(reset=True)
-    timer.enabled = True
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        step_device()
-    e1.record()
-    barrier()
-    timer.enabled = False
+    ms = _time_steps(step_device, args.steps, barrier)
     launches = _lib.kernel_launches(reset=True)
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    n_gemm, gemm_ms, gemm_flops = timer.summary()
 
     # ---- end to end through the module API with host buffers ----------------------------------
     for _ in range(2):
         step_e2e()
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(args.steps):
-        step_e2e()
-    f1.record()
-    barrier()
-    ms_e2e = f0.elapsed_time(f1)
+    ms_e2e = _time_steps(step_e2e, args.steps, barrier)
+
+    # ---- per-kernel pass: events around every GEMM / attention-scan / LSF-scan launch ------------
+    timers = KernelTimers(ops)
+    timers.install()
+    timers.enabled = True
+    n_prof = min(3, args.steps)
+    ms_prof = _time_steps(step_device, n_prof, barrier)
+    timers.enabled = False
+    timers.uninstall()
     status = _lib.device_status()
 
-    t = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=device)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    ms, ms_e2e = float(t[0]), float(t[1])
-    if rank != 0:
-        return None
+    ms, ms_e2e = _max_over_ranks([ms, ms_e2e], device, world)
     peaks = measured_peaks()
     tokens = world * B * T * args.steps
+    n_gemm, gemm_ms, gemm_flops = timers.summary("gemm")
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else 0.0
-    peak_tf = peaks["bf16_tflops_sustained"]
+    # the burst peak is the honest denominator while the SM clock stays near its maximum for the whole (short)
+    # timed region; under the power cap the sustained figure applies
+    near_max = bool(clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] >= 0.9 * clocks["sm_max_mhz"])
+    peak_tf = peaks["bf16_tflops"] if near_max else peaks["bf16_tflops_sustained"]
+    scans = {}
+    for kind, name, traffic in (("attn", "attn_scan_pipe_kernel (+ attn_state_pass_kernel)", ATTN_DRAM_BYTES_PER_LAUNCH),
+                                ("lsf", "lsf_scan_kernel (fused f32 residual)", LSF_DRAM_BYTES_PER_LAUNCH)):
+        n_k, k_ms, k_bytes = timers.summary(kind)
+        gbs = k_bytes / (k_ms * 1e-3) / 1e9 if k_ms > 0 else 0.0
+        scans[kind + "_scan"] = {"bound": "hbm", "kernel": name, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": gbs / peaks["hbm_gbs"], "peak_source": f"hbm_gbs of {peaks['source']}",
+                                 "traffic": traffic, "launches": n_k, "algorithmic_bytes_per_launch": k_bytes / max(n_k, 1),
+                                 "avg_launch_ms": k_ms / max(n_k, 1), "share_of_step": k_ms / ms_prof}
     out = {
         "metric": "prefill tok/s (606M, B=8xT=2048)", "value": tokens / (ms * 1e-3), "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
@@ -256,12 +307,142 @@ def run_ours(args, rank, world, local_rank):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "kernel": "ternary_gemm_kernel (tcgen05)", "achieved": achieved,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-                     "peak_source": f"bf16_tflops_sustained of {peaks['source']}",
+                     "peak_source": f"{'bf16_tflops (burst)' if near_max else 'bf16_tflops_sustained'} of {peaks['source']}: "
+                                    f"median SM clock {clocks.get('sm_mhz')} of {clocks.get('sm_max_mhz')} MHz in the timed loop",
+                     "frac_burst": achieved / peaks["bf16_tflops"], "frac_sustained": achieved / peaks["bf16_tflops_sustained"],
                      "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_unit": "bytes per launch (mean of the 4 shapes, ncu)",
-                     "launches": n_gemm, "flops_per_step": gemm_flops / args.steps,
-                     "avg_launch_ms": gemm_ms / max(n_gemm, 1), "gemm_share_of_step": gemm_ms / ms},
+                     "launches": n_gemm, "flops_per_step": gemm_flops / n_prof,
+                     "avg_launch_ms": gemm_ms / max(n_gemm, 1), "gemm_share_of_step": gemm_ms / ms_prof,
+                     "measured_in": f"a separate pass of {n_prof} steps with events around every launch ({ms_prof / n_prof:.2f} ms per step)"},
+        "roofline_scans": scans,
         "device_status": status,
     }
+    if world > 1 and not args.batch_split and not args.no_multi_gpu_records:
+        # The headline numbers are final at this point.  Should one of the communicating forms below stall (a rank
+        # lost, a collective that never completes), the watchdog prints the line without them and ends the process
+        # instead of leaving the launcher to its own time limit.
+        def bail():
+            if rank == 0:
+                out["multi_gpu"] = {"error": f"no result within {args.multi_gpu_limit_s} s"}
+                print(json.dumps(out), flush=True)
+            os._exit(0)
+
+        dog = threading.Timer(args.multi_gpu_limit_s, bail)
+        dog.daemon = True
+        dog.start()
+        sub = multi_gpu_records(model, device, rank, world, barrier)
+        dog.cancel()
+        out["multi_gpu"] = sub
+    return out if rank == 0 else None
+
+
+# --------------------------------------------------------------------------------------------
+# N > 1: the forms of the path that communicate (timed after the headline loop)
+# --------------------------------------------------------------------------------------------
+def multi_gpu_records(model, device, rank, world, barrier):
+    """-> {"strong": ..., "ep": ..., "cp": ...}; every rank takes part, rank 0 keeps the numbers.  Each record is
+    independent: an exception inside one is caught on every rank alike (the code paths do not depend on the
+    rank) and reported in its place."""
+    import torch.distributed as dist
+    from jarvis_b200 import modules as jm, parallel as par, synthetic
+
+    out = {}
+    B, T = CFG["B"], CFG["T"]
+
+    # ---- strong scaling: one B=8 batch split over the ranks -------------------------------------------
+    try:
+        if B % world:
+            raise ValueError(f"world size {world} does not divide the batch of {B}")
+        whole = torch.randint(0, CFG["vocab"], (B, T), generator=torch.Generator().manual_seed(77)).to(device)
+        per = B // world
+        mine = whole[rank * per:(rank + 1) * per].contiguous()
+        model.set_batch_split(dist.group.WORLD, global_tokens=B * T)
+        for _ in range(2):
+            model(mine)
+        n = 5
+        ms = _max_over_ranks([_time_steps(lambda: model(mine), n, barrier)], device, world)[0] / n
+        model.set_batch_split(None)
+        out["strong"] = {"workload": "ONE batch of B=8 x T=2048 split over the ranks (per-layer NCCL all-reduce of the MoE "
+                                     "statistics keeps the LSF decay that of the unsplit batch)",
+                         "ms_per_step": ms, "tok_per_s": B * T / (ms * 1e-3), "sequences_per_gpu": per}
+    except Exception as exc:  # noqa: BLE001
+        model.set_batch_split(None)
+        out["strong"] = {"error": f"{type(exc).__name__}: {exc}"}
+
+    # ---- expert parallel: the MoE layer alone on 65,536 tokens --------------------------------------------
+    try:
+        N, C, E = 65536, CFG["d_model"], CFG["n_experts"]
+        if N % world or (world > E and world % E) or (world <= E and E % world):
+            raise ValueError(f"world size {world} does not fit 65,536 tokens / {E} experts")
+        torch.manual_seed(0)
+        moe = synthetic.gaussian_ternary_(jm.SparseMoELayer(C), seed=0).to(device).eval()
+        peer = world <= E
+        ep = par.PeerExpertParallelMoE(moe, max_tokens=N // world) if peer else par.ExpertParallelMoE(moe)
+        rec = {"workload": "ternary top-2 MoE layer alone, 65,536 tokens x 1024 bf16, experts 1024->2048->1024, tokens "
+                           "data parallel, experts spread over the ranks, rows " +
+                           ("pulled over NVLink by the gather / combine kernels (peer loads)" if peer
+                            else "exchanged with NCCL all-to-all (uneven splits), each expert served by world/4 ranks"),
+               "cases": {}}
+        for case in ("zipf_1.2", "balanced"):
+            if case == "zipf_1.2":
+                x, w_r, shares = synthetic.zipf_router_inputs(N, C, E, seed=0)
+            else:
+                g = torch.Generator().manual_seed(5)
+                x = torch.randn(N, C, generator=g).to(torch.bfloat16)
+                w_r = (torch.rand(E, C, generator=g) * 2 - 1) / C ** 0.5
+                shares = None
+            with torch.no_grad():
+                moe.router.weight.copy_(w_r.to(device))
+            x = x.to(device)
+            n_loc = N // world
+            x_loc = x[rank * n_loc:(rank + 1) * n_loc].contiguous()
+            got, _ = ep.run_rows(x_loc)
+            ref, _ = moe.run_rows(x_loc)
+            err = float((got.float() - ref.float()).norm() / ref.float().norm())
+            n = 10
+            for _ in range(2):
+                ep.run_rows(x_loc)
+            ms = _max_over_ranks([_time_steps(lambda: ep.run_rows(x_loc), n, barrier)], device, world)[0] / n
+            # one GPU doing the whole layer, timed on every rank at once (same work everywhere)
+            for _ in range(2):
+                moe.run_rows(x)
+            ms_one = _max_over_ranks([_time_steps(lambda: moe.run_rows(x), n, barrier)], device, world)[0] / n
+            recv = (ep.seg[-1:].to(torch.int64) if peer
+                    else torch.tensor([sum(sum(r) for r in ep.last_recv_counts)], device=device))
+            allrecv = [torch.zeros_like(recv) for _ in range(world)]
+            dist.all_gather(allrecv, recv)
+            rows = [int(v) for v in allrecv]
+            rec["cases"][case] = {"ms": ms, "ms_one_gpu": ms_one, "speedup_vs_one_gpu": ms_one / ms,
+                                  "tokens_per_s": N / (ms * 1e-3), "rows_received_per_rank": rows,
+                                  "load_imbalance": max(rows) / (sum(rows) / world),
+                                  "top1_shares": None if shares is None else [round(float(v), 4) for v in shares],
+                                  "rel_l2_vs_single_gpu_layer": _max_over_ranks([err], device, world)[0]}
+        if peer:
+            ep.close()
+        out["ep"] = rec
+    except Exception as exc:  # noqa: BLE001
+        out["ep"] = {"error": f"{type(exc).__name__}: {exc}"}
+
+    # ---- context parallel: B=2 x T=65,536 hidden states ---------------------------------------------------
+    try:
+        Bc, Tc = 2, 65536
+        if Tc % world:
+            raise ValueError(f"world size {world} does not divide T={Tc}")
+        idx = torch.randint(0, CFG["vocab"], (Bc, Tc), generator=torch.Generator().manual_seed(78)).to(device)
+        tl = Tc // world
+        mine = idx[:, rank * tl:(rank + 1) * tl].contiguous()
+        model.set_context_parallel(dist.group.WORLD)
+        for _ in range(2):
+            model.hidden_rows(mine)
+        n = 3
+        ms = _max_over_ranks([_time_steps(lambda: model.hidden_rows(mine), n, barrier)], device, world)[0] / n
+        model.set_context_parallel(None)
+        out["cp"] = {"workload": "24 layers, hidden states, B=2 x T=65,536, every sequence cut into equal slices over the ranks "
+                                 "(per layer: NCCL all-gather of the attention and LSF end states, all-reduce of the MoE statistics)",
+                     "ms": ms, "tok_per_s": Bc * Tc / (ms * 1e-3), "tokens_per_gpu": Bc * tl}
+    except Exception as exc:  # noqa: BLE001
+        model.set_context_parallel(None)
+        out["cp"] = {"error": f"{type(exc).__name__}: {exc}"}
     return out
 
 
@@ -345,6 +526,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU oracle leg of the default run")
     ap.add_argument("--batch-split", action="store_true",
                     help="strong scaling: ONE B=8 batch split over the ranks, MoE statistics all-reduced per layer")
+    ap.add_argument("--no-multi-gpu-records", action="store_true",
+                    help="N > 1: skip the strong-scaling / expert-parallel / context-parallel records")
+    ap.add_argument("--multi-gpu-limit-s", type=float, default=240.0,
+                    help="N > 1: time limit of those records; past it the line is printed without them")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
