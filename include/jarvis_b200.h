@@ -37,7 +37,6 @@ extern "C" {
 #define JB200_EPI_F32 3       /* out f32  [M][N]  = alpha * acc                       */
 #define JB200_EPI_QK_ROPE_BF16 4 /* jb200_qkv_linear_rope only: bf16 out, attention prologue on the q/k heads */
 #define JB200_ATTN_QK_PREPARED 1 /* jb200_attn_scan flag: q, k come from jb200_qkv_linear_rope */
-#define JB200_TILE_CTA_PAIR 0x1000 /* flag added to token_tile: run on CTA pairs (tcgen05 cta_group::2) */
 
 /* device status codes (0 = no bounded wait ever ran out) */
 #define JB200_STATUS_GEMM_PRODUCER 0x11u
@@ -102,14 +101,19 @@ int jb200_unpack_ternary(const uint8_t* packed, size_t n_bytes, int out_dtype, v
  * x: bf16 [M][K].  packed: u8 [N][K/4].  alpha: f32 [N / alpha_rows] (alpha_rows = N for the
  * per-tensor scale; several matrices stacked along N, e.g. q/k/v, each keep their own).
  * N % 128 == 0, K % 64 == 0, alpha_rows % 128 == 0.  out: per `epilogue`.
- * token_tile: 0 = choose, else one of 32/64/128/256.  Adding JB200_TILE_CTA_PAIR selects the variant that runs a
- * 256 out-feature x token_tile tile on a pair of SMs (tcgen05 cta_group::2; needs N % 256 == 0 and a tile of
- * 0, 128 or 256).  Results are identical; on the shapes of this model the one-CTA kernel is the faster one,
- * so it is the default.
+ * token_tile: 0 = choose, else one of 32/64/128/256.
  * w_layout: 0 = `packed` is the canonical weight_packing.py layout; 1 = `packed` was re-encoded by
  * jb200_prepare_weights (same size, about 4x fewer decode instructions in the kernel). */
 int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int alpha_rows,
                          int N, int epilogue, void* out, int token_tile, int w_layout, void* stream);
+
+/* Dense bf16 linear layer without bias on the same tensor-core pipeline: Y = X W^T.  Replaces the one dense
+ * projection of the path, lm_head = nn.Linear(d_model, vocab_size, bias=False) (jarvis_engine/jarvis_model.py:458, 535),
+ * which the reference does not quantise.  x: bf16 [M][K]; w: bf16 [N][K] (N % 128 == 0: pad the vocabulary rows with
+ * zeros; K % 64 == 0); out: [M][N] bf16 (out_dtype 1) or f32 (out_dtype 0), row stride N.  Weight tiles are loaded
+ * by TMA next to the activation tiles; token_tile as in jb200_ternary_linear. */
+int jb200_dense_linear(const void* x, int M, int K, const void* w, int N, int out_dtype, void* out, int token_tile,
+                       void* stream);
 
 /* The q/k/v projection fused with the prologue of the attention scan: as jb200_ternary_linear with a bf16
  * output, but out-features [0, rope_feats) (the q and k heads, 64 features each) come out as

@@ -17,7 +17,6 @@ _HEADER = os.path.join(os.path.dirname(_build.PKG_DIR), "include", "jarvis_b200.
 OK, ERR_ARG, ERR_CUDA = 0, -1, 1
 EPI_BF16, EPI_GELU_BF16, EPI_RESID_F32, EPI_F32 = 0, 1, 2, 3
 ATTN_QK_PREPARED = 1   # JB200_ATTN_QK_PREPARED
-TILE_CTA_PAIR = 0x1000  # JB200_TILE_CTA_PAIR: added to token_tile, runs the GEMM on CTA pairs (cta_group::2)
 
 _P = C.c_void_p
 _I = C.c_int
@@ -37,6 +36,7 @@ PROTOTYPES = {
     "jb200_unpack_ternary": (_I, [_P, _Z, _I, _P, _P]),
     "jb200_ternary_linear": (_I, [_P, _I, _I, _P, _P, _I, _I, _I, _P, _I, _I, _P]),
     "jb200_prepare_weights": (_I, [_P, _Z, _P, _P]),
+    "jb200_dense_linear": (_I, [_P, _I, _I, _P, _I, _I, _P, _I, _P]),
     "jb200_host_decode16_prepared": (None, [C.c_uint32, C.POINTER(C.c_uint32)]),
     "jb200_rmsnorm": (_I, [_P, _I, _P, _F, _P, _I, _I, _I, _P]),
     "jb200_embedding": (_I, [_P, _P, _I, _P, _I, _I, _P]),

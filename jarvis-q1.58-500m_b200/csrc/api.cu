@@ -147,6 +147,14 @@ int jb200_ternary_linear(const void* x, int M, int K, const uint8_t* packed, con
                              static_cast<cudaStream_t>(stream));
 }
 
+int jb200_dense_linear(const void* x, int M, int K, const void* w, int N, int out_dtype, void* out, int token_tile,
+                       void* stream) {
+  JB_REQUIRE(out_dtype == 0 || out_dtype == 1, "dense_linear: out_dtype must be 0 (f32) or 1 (bf16)");
+  return launch_ternary_gemm(x, M, K, static_cast<const uint8_t*>(w), nullptr, N, N, 1, nullptr,
+                             out_dtype == 1 ? JB200_EPI_BF16 : JB200_EPI_F32, out, token_tile, 2,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int jb200_ternary_linear_grouped(const void* x, int M, int K, const uint8_t* packed, const float* alpha, int N,
                                  int G, const int32_t* seg_offsets, int epilogue, void* out, int token_tile,
                                  int w_layout, void* stream) {

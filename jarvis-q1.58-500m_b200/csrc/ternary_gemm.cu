@@ -34,6 +34,8 @@
 //      every 32-bit word the even in-features sit in the low half and the odd ones in the high half,
 //      each as (sign << 1 | nonzero), so (w << (14 - 2j)) & 0xC000C000 IS the bf16 pair
 //      {0, +2.0, -2.0} for in-features (2j, 2j+1): 2 ops / 2 weights; the factor 2 is folded into alpha.
+//   2  dense bf16 weights [N][K] (the lm_head, jarvis_model.py:535, which the reference keeps as nn.Linear): nothing to
+//      decode, the weight tile is a second TMA load into the same swizzled stage buffer and the decoder warps retire.
 // The decoders, the TMA writes, the tensor core's operand reads and the epilogue all go through the same
 // shared memory and issue slots; per-role cycle counters put the MMA issue interval at 126 cycles (of 128) for
 // K = 4096 and 154 for K = 1024, so the cheap decode and an epilogue that never touches shared memory are what
@@ -96,7 +98,8 @@ __device__ __forceinline__ bool tile_coord(const SmemCtl* ctl, int t, int n_ft, 
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams p) {
+ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                    const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -110,10 +113,11 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
   const int bn = p.bn;
   const int n_ft = p.N / BM;
   const int n_kb = p.K / BK;
+  const bool dense_w = p.w_layout == 2;     // weight tiles come by TMA: only the producer arrives on `full`
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(smem_u32(&ctl->full[s]), 1 + 128);
+      mbar_init(smem_u32(&ctl->full[s]), dense_w ? 1 : 1 + 128);
       mbar_init(smem_u32(&ctl->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -129,6 +133,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_x);
+    if (dense_w) tma_prefetch_desc(&tmap_w);
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
@@ -156,8 +161,10 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
           const uint32_t ph = (it / STAGES) & 1u;
           if (!mbar_wait(smem_u32(&ctl->empty[s]), ph ^ 1u, abort_flag, p.status, JB200_STATUS_GEMM_PRODUCER))
             goto done;
-          mbar_arrive_expect_tx(smem_u32(&ctl->full[s]), uint32_t(bn) * BK * 2);
+          mbar_arrive_expect_tx(smem_u32(&ctl->full[s]), uint32_t(bn) * BK * 2 + (dense_w ? uint32_t(A_STAGE_BYTES) : 0u));
           tma_load_2d(b_base + s * B_STAGE_BYTES, &tmap_x, kb * BK, tc.tok0, smem_u32(&ctl->full[s]));
+          if (dense_w)
+            tma_load_2d(a_base + s * A_STAGE_BYTES, &tmap_w, kb * BK, tc.group * p.N + tc.ft * BM, smem_u32(&ctl->full[s]));
         }
       }
     }
@@ -193,6 +200,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
     }
   } else if (warp < EPI_WARP0) {
     // ---------------- weight decoders ----------------
+    if (dense_w) goto done;
     const int grp = (warp - DEC_WARP0) >> 2;                      // K-blocks with (it & 1) == grp
     const int r = ((warp - DEC_WARP0) & 3) * 32 + lane;            // weight row inside the tile
     const size_t row_bytes = size_t(p.K) / 4;
@@ -218,7 +226,7 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
 #pragma unroll
         for (int wi = 0; wi < 4; ++wi) {
           uint32_t v[8];
-          if (p.w_layout) decode16_prepared(words[wi], v); else decode16(words[wi], v);
+          if (p.w_layout == 1) decode16_prepared(words[wi], v); else decode16(words[wi], v);
           const uint32_t c0 = uint32_t(2 * wi), c1 = uint32_t(2 * wi + 1);
           *reinterpret_cast<uint4*>(arow + ((c0 ^ swz) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
           *reinterpret_cast<uint4*>(arow + ((c1 ^ swz) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
@@ -244,8 +252,9 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmParams
         goto done;
       tc_fence_after_sync();
       const int feat = tc.ft * BM + q * 32 + lane;
-      const float alpha = __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows) *
-                          (p.w_layout ? 0.5f : 1.0f);   // prepared weights decode to +-2
+      const float alpha = dense_w ? 1.0f
+                                  : __ldg(p.alpha + size_t(tc.group) * (p.N / p.alpha_rows) + feat / p.alpha_rows) *
+                                        (p.w_layout ? 0.5f : 1.0f);   // prepared weights decode to +-2
       const uint32_t t_lane = tmem_base + (uint32_t(q * 32) << 16) + acc * BN_MAX;
       for (int c0 = half * 32; c0 < bn; c0 += 64) {
         if (tc.tok0 + c0 >= tc.tok_end) break;   // warp-uniform
@@ -283,9 +292,6 @@ int pick_bn(int M, int G, int n_ft, int sms) {
 
 }  // namespace
 
-int pair_token_tile(int M, int N, int G, int bn_override, int sms);
-int launch_ternary_gemm_pair(const void* x_bf16, const GemmParams& p, cudaStream_t stream);
-
 int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packed, const float* alpha,
                         int alpha_rows, int N, int G, const int32_t* seg_offsets, int epilogue, void* out,
                         int bn_override, int w_layout, cudaStream_t stream, const GemmRope* rope) {
@@ -305,22 +311,19 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
     JB_REQUIRE(rope->rope_feats >= 0 && rope->rope_feats <= N && rope->rope_feats % 64 == 0,
                "qkv_linear_rope: rotated features (%d) must be whole 64-wide heads within out_features", rope->rope_feats);
   }
-  JB_REQUIRE(w_layout == 0 || w_layout == 1, "ternary_linear: weight layout must be 0 (canonical) or 1 (prepared)");
+  JB_REQUIRE(w_layout >= 0 && w_layout <= 2, "ternary_linear: weight layout must be 0 (canonical), 1 (prepared) or 2 (dense bf16)");
+  JB_REQUIRE(w_layout != 2 || (G == 1 && !rope && (epilogue == JB200_EPI_BF16 || epilogue == JB200_EPI_F32)),
+             "dense_linear: one weight matrix, plain bf16 or f32 output");
   if (M == 0) return JB200_OK;   // nothing to do: an empty batch may come with null row pointers
-  JB_REQUIRE(x_bf16 && w_packed && alpha && out, "ternary_linear: null pointer");
+  JB_REQUIRE(x_bf16 && w_packed && (alpha || w_layout == 2) && out, "ternary_linear: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(w_packed) && aligned16(out), "ternary_linear: pointers must be 16-byte aligned");
   if (M == 0) return JB200_OK;
   const int sms = sm_count();
   if (sms <= 0) return JB200_ERR_CUDA;
   const int n_ft = N / BM;
-  const bool want_pair = (bn_override & JB200_TILE_CTA_PAIR) != 0;
-  bn_override &= ~JB200_TILE_CTA_PAIR;
   JB_REQUIRE(bn_override == 0 || bn_override == 32 || bn_override == 64 || bn_override == 128 || bn_override == 256,
              "ternary_linear: token tile %d not in {32,64,128,256}", bn_override);
-  const int pair_bn = want_pair ? pair_token_tile(M, N, G, bn_override, sms) : 0;
-  JB_REQUIRE(!want_pair || pair_bn != 0,
-             "ternary_linear: the CTA-pair kernel needs out_features %% 256 == 0 and a token tile of 0, 128 or 256");
-  const int bn = pair_bn ? pair_bn : (bn_override > 0 ? bn_override : pick_bn(M, G, n_ft, sms));
+  const int bn = bn_override > 0 ? bn_override : pick_bn(M, G, n_ft, sms);
 
   GemmParams p;
   p.w_packed = w_packed;
@@ -341,7 +344,6 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   p.rope_feats = rope ? rope->rope_feats : 0;
   p.status = device_status_ptr();
   if (!p.status) return JB200_ERR_CUDA;
-  if (pair_bn) return launch_ternary_gemm_pair(x_bf16, p, stream);
 
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) {
@@ -362,11 +364,24 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   }
 
 
+  CUtensorMap tmap_w = tmap;     // packed weights: the decoders read them with plain loads, the map is not used
+  if (w_layout == 2) {
+    const cuuint64_t wdim[2] = {cuuint64_t(K), cuuint64_t(N)};
+    const cuuint32_t wbox[2] = {cuuint32_t(BK), cuuint32_t(BM)};
+    cr = enc(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint8_t*>(w_packed), wdim, gstride, wbox, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+      set_error("dense_linear: cuTensorMapEncodeTiled failed for the weights (%d)", int(cr));
+      return JB200_ERR_CUDA;
+    }
+  }
+
   // per device and cheap: set on every call rather than remembering which devices have seen it
   JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
   const long max_tiles = long((M + bn - 1) / bn + (G - 1)) * n_ft;
   const int grid = int(max_tiles < sms ? max_tiles : sms);
-  ternary_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap, p);
+  ternary_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap, tmap_w, p);
   JB_LAUNCH_CHECK("ternary_gemm_kernel");
   return JB200_OK;
 }

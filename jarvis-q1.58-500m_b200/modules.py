@@ -504,7 +504,7 @@ class Jarvis(nn.Module):
         w = self.lm_head.weight
         key = (w.data_ptr(), w._version)
         if self._lm_head_bf16 is None or self._lm_head_bf16[0] != key:
-            # rows padded to a multiple of 128 so the library GEMM can use its aligned tensor-core kernels
+            # rows padded with zeros to a multiple of 128, the out-feature tile of the GEMM kernel
             v = w.shape[0]
             wp = torch.zeros(((v + 127) // 128 * 128, w.shape[1]), dtype=torch.bfloat16, device=w.device)
             wp[:v] = w.detach().to(torch.bfloat16)
@@ -570,7 +570,7 @@ class Jarvis(nn.Module):
             new_s.append(S)
         hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
         vocab = self.lm_head.weight.shape[0]
-        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)[..., :vocab]
+        logits = ops.dense_linear(hidden, self._lm_head_weight()).view(B, T, -1)[..., :vocab]
         return logits, {"h": new_h, "S": new_s}
 
     @torch.no_grad()
@@ -578,8 +578,9 @@ class Jarvis(nn.Module):
         B, T = idx.shape
         hidden = self.hidden_rows(idx, persist_state)
         vocab = self.lm_head.weight.shape[0]
-        # dense bf16 lm_head: a plain library GEMM; the padded columns are sliced off as a view
-        logits = torch.matmul(hidden, self._lm_head_weight().t()).view(B, T, -1)[..., :vocab]
+        # dense bf16 lm_head on the same tcgen05 pipeline as the ternary layers (weight tiles by TMA); the padded
+        # vocabulary columns are sliced off as a view
+        logits = ops.dense_linear(hidden, self._lm_head_weight()).view(B, T, -1)[..., :vocab]
         if self.logits_dtype != torch.bfloat16:
             logits = logits.to(self.logits_dtype)
         loss = None

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import ATTN_QK_PREPARED, EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32, TILE_CTA_PAIR  # noqa: F401
+from ._lib import ATTN_QK_PREPARED, EPI_BF16, EPI_F32, EPI_GELU_BF16, EPI_RESID_F32  # noqa: F401
 
 
 def _stream() -> int:
@@ -155,6 +155,29 @@ def ternary_linear_grouped(x: torch.Tensor, packed: torch.Tensor, alpha: torch.T
                                          _ptr(out), token_tile, 1 if prepared else 0, _stream()),
         "jb200_ternary_linear_grouped",
     )
+    return out
+
+
+def dense_linear(x: torch.Tensor, w: torch.Tensor, *, out_dtype=torch.bfloat16, out: torch.Tensor | None = None,
+                 token_tile: int = 0) -> torch.Tensor:
+    """x @ w^T with dense bf16 weights on the tensor-core pipeline of the ternary GEMM (weight tiles by TMA instead
+    of the 2-bit decode): the lm_head, nn.Linear(d_model, vocab, bias=False) (jarvis_engine/jarvis_model.py:458, 535).
+    x: bf16 (M, K); w: bf16 (N, K) with N % 128 == 0 (pad the vocabulary with zero rows) -> (M, N)."""
+    lib = _lib.load()
+    _need(x, torch.bfloat16, "dense_linear.x")
+    _need(w, torch.bfloat16, "dense_linear.w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise RuntimeError(f"dense_linear: weight has K={w.shape[1]}, x has K={K}")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    else:
+        _need(out, out_dtype, "dense_linear.out")
+        if tuple(out.shape) != (M, N):
+            raise RuntimeError("dense_linear: out has the wrong shape")
+    _lib.check(lib.jb200_dense_linear(_ptr(x), M, K, _ptr(w), N, _dt(out), _ptr(out), token_tile, _stream()),
+               "jb200_dense_linear")
     return out
 
 

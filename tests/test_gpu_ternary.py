@@ -167,56 +167,40 @@ def test_grouped_ternary_linear(counts):
     assert _lib.device_status() == 0
 
 
-@pytest.mark.parametrize("tile", [0, 128, 256])
-@pytest.mark.parametrize("M,K,N", [(256, 64, 256), (300, 512, 512), (1000, 1024, 1024), (77, 128, 256)])
-def test_cta_pair_kernel_exact_on_integers(M, K, N, tile):
-    """The cta_group::2 variant (two SMs per 256-feature tile) must give the one-CTA kernel's results
-    bit for bit: exact integer GEMM in f32, and the same bf16 / GELU / residual outputs."""
-    g = torch.Generator().manual_seed(M + K + N + tile)
+@pytest.mark.parametrize("M,K,N", [(1, 64, 128), (300, 256, 384), (2048, 1024, 1152)])
+def test_dense_linear_exact_on_integers(M, K, N):
+    """Dense bf16 weights through the same pipeline (weight tiles by TMA): exact on small integers, for both
+    output types, and equal to an fp32 matmul of the same bf16 operands on random data."""
+    g = torch.Generator().manual_seed(M + K + N)
     x = torch.randint(-4, 5, (M, K), generator=g).float()
-    q = torch.randint(-1, 2, (N, K), generator=g).float()
-    xb, one = x.bfloat16().cuda(), torch.ones(1).cuda()
-    for prepared in (False, True):
-        pk = orc.pack_ternary(q).cuda()
-        pk = ops.prepare_weights(pk) if prepared else pk
-        y = ops.ternary_linear(xb, pk, one, epilogue=ops.EPI_F32, token_tile=tile | ops.TILE_CTA_PAIR, prepared=prepared)
-        assert torch.equal(y.cpu(), x @ q.t())
-        for epi in (ops.EPI_BF16, ops.EPI_GELU_BF16):
-            a = torch.full((1,), 0.01).cuda()
-            y1 = ops.ternary_linear(xb, pk, a, epilogue=epi, prepared=prepared)
-            y2 = ops.ternary_linear(xb, pk, a, epilogue=epi, token_tile=tile | ops.TILE_CTA_PAIR, prepared=prepared)
-            assert torch.equal(y1, y2)
-    resid = torch.randn(M, N, generator=g)
-    o1, o2 = resid.clone().cuda(), resid.clone().cuda()
-    pk = orc.pack_ternary(q).cuda()
-    ops.ternary_linear(xb, pk, torch.full((1,), 0.3).cuda(), epilogue=ops.EPI_RESID_F32, out=o1)
-    ops.ternary_linear(xb, pk, torch.full((1,), 0.3).cuda(), epilogue=ops.EPI_RESID_F32, out=o2,
-                       token_tile=tile | ops.TILE_CTA_PAIR)
-    assert torch.equal(o1, o2)
-    assert _lib.device_status() == 0
-
-
-@pytest.mark.parametrize("counts", [[100, 0, 37, 263], [0, 0, 0, 512], [1, 1, 1, 1], [300, 300, 300, 300]])
-def test_cta_pair_kernel_grouped(counts):
-    g = torch.Generator().manual_seed(sum(counts) + 1)
-    K, N, G = 256, 512, len(counts)
-    M = sum(counts)
-    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
-    x = torch.randint(-3, 4, (M, K), generator=g).float()
-    q = torch.randint(-1, 2, (G, N, K), generator=g).float()
-    alphas = torch.tensor([1.0, 0.5, 2.0, 4.0])[:G]
-    y = ops.ternary_linear_grouped(x.bfloat16().cuda(), orc.pack_ternary(q).cuda(), alphas.cuda(), offs.cuda(),
-                                   epilogue=ops.EPI_F32, token_tile=ops.TILE_CTA_PAIR)
-    ref = torch.cat([alphas[e] * (x[offs[e]:offs[e + 1]] @ q[e].t()) for e in range(G)])
+    w = torch.randint(-3, 4, (N, K), generator=g).float()
+    ref = x @ w.t()
+    y = ops.dense_linear(x.bfloat16().cuda(), w.bfloat16().cuda(), out_dtype=torch.float32)
     assert torch.equal(y.cpu(), ref)
+    yb = ops.dense_linear(x.bfloat16().cuda(), w.bfloat16().cuda())
+    assert torch.equal(yb.float().cpu(), ref.bfloat16().float())
+    xr = torch.randn(M, K, generator=g).bfloat16()
+    wr = (torch.randn(N, K, generator=g) * 0.02).bfloat16()
+    yr = ops.dense_linear(xr.cuda(), wr.cuda(), out_dtype=torch.float32)
+    want = xr.float() @ wr.float().t()
+    assert float((yr.cpu() - want).norm() / want.norm()) < 1e-5
     assert _lib.device_status() == 0
 
 
-def test_cta_pair_kernel_rejects_odd_feature_tiles():
-    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
-    packed = torch.zeros(384, 16, dtype=torch.uint8, device="cuda")
-    with pytest.raises(RuntimeError, match="256"):
-        ops.ternary_linear(x, packed, torch.ones(1, device="cuda"), token_tile=ops.TILE_CTA_PAIR)
+def test_dense_linear_lm_head_shape():
+    """The lm_head of the 606M model: 1024 -> 50257 (padded to 50304 rows of zeros), a slice of token rows
+    against fp32 on the CPU."""
+    g = torch.Generator().manual_seed(3)
+    V, Vp, K, M = 50257, 50304, 1024, 512
+    w = torch.zeros(Vp, K)
+    w[:V] = torch.randn(V, K, generator=g) * 0.02
+    x = torch.randn(M, K, generator=g).bfloat16()
+    y = ops.dense_linear(x.cuda(), w.bfloat16().cuda())
+    want = x.float() @ w.bfloat16().float().t()
+    assert float((y.float().cpu() - want).norm() / want.norm()) < 3e-3      # bf16 rounding of the stored logits
+    assert float(y[:, V:].abs().max()) == 0.0
+    with pytest.raises(RuntimeError, match="multiple of 128"):
+        ops.dense_linear(x.cuda(), w[:V].bfloat16().cuda())
 
 
 def test_argument_errors_are_reported():
