@@ -18,7 +18,14 @@
 // sequential), each tile's end value (and decay product) from a zero carry, reading m once more (it was
 // just written by the MoE combine and is normally still in L2); the main launch folds the ends of all
 // earlier tiles into its carry-in, which is exact because the recurrence is an affine map.
+//
+// The two forms the model and the scan sweep run (one scalar decay, bf16 input, and either the fused f32
+// residual update or a bf16 output) take lsf_tma_kernel: the same scan, but the [128 tokens x 64 channels] tiles
+// travel by TMA (cp.async.bulk.tensor) through a ring of shared-memory stages - loads complete on mbarriers
+// (bounded waits), results are written into the tile in place and leave by a TMA store - so the bytes in flight
+// no longer depend on how many registers a thread can spare for outstanding loads.
 #include "common.cuh"
+#include "gemm_shared.cuh"
 #include "launchers.h"
 
 namespace jb {
@@ -255,6 +262,209 @@ int launch_t(const LsfParams& p, cudaStream_t stream) {
   return JB200_OK;
 }
 
+
+// ------------------------------------------------------------------------------------------------------------
+// TMA-staged scan (scalar decay, bf16 m).  FUSED: resid (f32) += h, no other output.  Otherwise: out (bf16) = h.
+// Tensor maps are 3-D (channels, tokens, sequences), so tiles are clipped at the end of a sequence: loads past T
+// read zeros (m = 0 leaves the recurrence a pure decay), stores past T are dropped.
+// ------------------------------------------------------------------------------------------------------------
+constexpr int LT_TOK = LSF_WARPS * 16;       // 128 tokens per tile (= LSF_TILE: the ends pre-pass uses the same tiles)
+constexpr int LT_M_BYTES = LT_TOK * LSF_CH * 2;    // 16 KiB
+constexpr int LT_R_BYTES = LT_TOK * LSF_CH * 4;    // 32 KiB
+
+template <bool FUSED>
+struct LsfTma {
+  static constexpr int STAGE_BYTES = LT_M_BYTES + (FUSED ? LT_R_BYTES : 0);
+  static constexpr size_t CTL_BYTES = 128 + 2 * LSF_WARPS * 32 * sizeof(float2);   // barriers + flag, run ends
+  static constexpr size_t smem_bytes(int stages) { return size_t(stages) * STAGE_BYTES + CTL_BYTES + 128 /* alignment slack */; }
+  // Stages: enough CTAs to put two (fused) or three (plain) on every SM -> a short ring each; a grid that leaves
+  // SMs with one CTA -> that CTA gets a ring of four stages (and sequences are not cut into segments).
+  static constexpr int STAGES_SHARED = FUSED ? 2 : 4;
+  static constexpr int STAGES_ALONE = 4;
+};
+
+template <bool FUSED>
+__global__ void __launch_bounds__(LSF_THREADS, FUSED ? 2 : 3)
+lsf_tma_kernel(const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_io, const LsfParams p,
+               const int n_stages, unsigned int* status) {
+  using Cfg = LsfTma<FUSED>;
+  constexpr int TPW = 16;
+  extern __shared__ uint8_t lsf_smem_raw[];
+  const uint32_t raw_addr = smem_u32(lsf_smem_raw);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  uint8_t* tiles = lsf_smem_raw + (base - raw_addr);
+  uint8_t* ctl = tiles + size_t(n_stages) * Cfg::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(ctl);                       // [STAGES]
+  uint32_t* abort_flag = reinterpret_cast<uint32_t*>(ctl + 64);
+  float2 (*s_end)[LSF_WARPS][32] = reinterpret_cast<float2 (*)[LSF_WARPS][32]>(ctl + 128);   // [2][8][32]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, seg = blockIdx.z;
+  const int ch0 = blockIdx.x * LSF_CH;
+  const int ch = ch0 + lane * 2;
+  const bool ch_ok = ch < p.D;
+  const int t_begin = seg * p.seg_len;
+  const int t_end = min(p.T, t_begin + p.seg_len);
+  const int n_tiles = (t_end - t_begin + LT_TOK - 1) / LT_TOK;
+
+  float alpha;
+  if (p.alpha_s) {
+    alpha = __ldg(p.alpha_s);
+  } else {
+    const float z = -__ldg(p.var_scale) * __ldg(p.act_var);
+    alpha = p.alpha_min + (p.alpha_max - p.alpha_min) * (1.0f / (1.0f + expf(-z)));
+  }
+  float pw[TPW];   // alpha^(i+1)
+  {
+    float a = alpha;
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) { pw[i] = a; a *= alpha; }
+  }
+  float2 carry = make_float2(0.f, 0.f);
+  if (p.h0 && ch_ok) carry = __ldg(reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch));
+  if (seg > 0 && ch_ok) {   // fold the ends of all earlier tiles (left by the ends pre-pass) into the carry-in
+    const float a_tile = expf(float(LT_TOK) * logf(alpha));
+    const size_t e0 = (size_t(b) * p.n_pre_tiles) * p.D + ch;
+    const int n_before = seg * (p.seg_len / LT_TOK);
+    for (int s2 = 0; s2 < n_before; ++s2) {
+      const float2 e = __ldg(reinterpret_cast<const float2*>(p.seg_end + e0 + size_t(s2) * p.D));
+      carry.x = a_tile * carry.x + e.x;
+      carry.y = a_tile * carry.y + e.y;
+    }
+  }
+
+  auto issue = [&](int i) {      // thread 0 only
+    const int s = i % n_stages;
+    const uint32_t bar = smem_u32(&full[s]);
+    const uint32_t dst = smem_u32(tiles + size_t(s) * Cfg::STAGE_BYTES);
+    mbar_arrive_expect_tx(bar, Cfg::STAGE_BYTES);
+    tma_load_3d(dst, &tm_m, ch0, t_begin + i * LT_TOK, b, bar);
+    if (FUSED) tma_load_3d(dst + LT_M_BYTES, &tm_io, ch0, t_begin + i * LT_TOK, b, bar);
+  };
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) mbar_init(smem_u32(&full[s]), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tm_m);
+    tma_prefetch_desc(&tm_io);
+    for (int i = 0; i < n_stages && i < n_tiles; ++i) issue(i);
+  }
+  __syncthreads();
+
+  bool ok = true;
+  for (int i = 0; i < n_tiles; ++i) {
+    const int s = i % n_stages;
+    const int buf = i & 1;
+    uint8_t* m_tile = tiles + size_t(s) * Cfg::STAGE_BYTES;
+    uint8_t* r_tile = m_tile + LT_M_BYTES;
+    if (!mbar_wait(smem_u32(&full[s]), uint32_t(i / n_stages) & 1u, abort_flag, status, JB200_STATUS_LSF_LOAD)) ok = false;
+    const int tl0 = warp * TPW;                          // first token of this warp's run inside the tile
+    const int t0 = t_begin + i * LT_TOK + tl0;
+    float2 loc[TPW];
+    float2 h = make_float2(0.f, 0.f);
+    if (ok) {
+#pragma unroll
+      for (int j = 0; j < TPW; ++j) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(m_tile + size_t(tl0 + j) * (LSF_CH * 2) + lane * 4);
+        h.x = alpha * h.x + (1.0f - alpha) * bf16_lo(w);
+        h.y = alpha * h.y + (1.0f - alpha) * bf16_hi(w);
+        loc[j] = h;
+      }
+    }
+    s_end[buf][warp][lane] = h;
+    if (__syncthreads_or(!ok)) { ok = false; break; }
+    // carry into this warp's run, and the carry out of the whole tile (the recurrence is an affine map)
+    float2 c = carry, cn = carry;
+#pragma unroll
+    for (int w = 0; w < LSF_WARPS; ++w) {
+      if (w == warp) cn = c;
+      const float2 e = s_end[buf][w][lane];
+      c.x = pw[TPW - 1] * c.x + e.x;
+      c.y = pw[TPW - 1] * c.y + e.y;
+    }
+    carry = c;
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const float hx = loc[j].x + pw[j] * cn.x, hy = loc[j].y + pw[j] * cn.y;
+      if (FUSED) {
+        float2* r = reinterpret_cast<float2*>(r_tile + size_t(tl0 + j) * (LSF_CH * 4) + lane * 8);
+        const float2 old = *r;
+        *r = make_float2(old.x + hx, old.y + hy);
+      } else {
+        *reinterpret_cast<uint32_t*>(m_tile + size_t(tl0 + j) * (LSF_CH * 2) + lane * 4) = pack_bf16x2(hx, hy);
+      }
+      if (t0 + j == p.T - 1 && p.h_last && ch_ok)
+        *reinterpret_cast<float2*>(p.h_last + size_t(b) * p.D + ch) = make_float2(hx, hy);
+    }
+    fence_proxy_async_smem();        // the tile's new contents -> visible to the TMA store
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      tma_store_3d(&tm_io, ch0, t_begin + i * LT_TOK, b, smem_u32(FUSED ? r_tile : m_tile));
+      bulk_commit_group();
+      if (i + n_stages < n_tiles) {
+        bulk_wait_group_read<0>();   // the store has read the stage: it may be filled again
+        issue(i + n_stages);
+      }
+    }
+  }
+  if (threadIdx.x == 0) bulk_wait_group<0>();   // every store has landed before the CTA gives up its shared memory
+}
+
+int make_lsf_map(CUtensorMap* tm, const void* ptr, CUtensorMapDataType dt, int elem, int B, int T, int D) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) {
+    set_error("lsf_scan: cuTensorMapEncodeTiled entry point not available");
+    return JB200_ERR_CUDA;
+  }
+  const cuuint64_t gdim[3] = {cuuint64_t(D), cuuint64_t(T), cuuint64_t(B)};
+  const cuuint64_t gstride[2] = {cuuint64_t(D) * elem, cuuint64_t(T) * D * elem};
+  const cuuint32_t box[3] = {cuuint32_t(LSF_CH), cuuint32_t(LT_TOK), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult cr = fn(tm, dt, 3, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS) {
+    set_error("lsf_scan: cuTensorMapEncodeTiled failed (%d)", int(cr));
+    return JB200_ERR_CUDA;
+  }
+  return JB200_OK;
+}
+
+template <bool FUSED>
+int launch_tma(LsfParams p, cudaStream_t stream) {
+  using Cfg = LsfTma<FUSED>;
+  const int sms = sm_count();
+  if (sms <= 0) return JB200_ERR_CUDA;
+  const long ctas = long((p.D + LSF_CH - 1) / LSF_CH) * p.B;
+  int stages = Cfg::STAGES_SHARED;
+  if (2 * ctas >= sms && ctas <= 2L * sms) {
+    // between half a wave and two CTAs per SM: one uncut CTA per (sequence, 64 channels) with a deep ring keeps
+    // the SM's loads in flight by itself; cutting T would cost the ends pre-pass (a second read of m, a launch)
+    stages = Cfg::STAGES_ALONE;
+    p.nseg = 1;
+    p.seg_len = (p.T + LT_TOK - 1) / LT_TOK * LT_TOK;
+    p.n_pre_tiles = 0;
+  }
+  CUtensorMap tm_m, tm_io;
+  int rc;
+  if ((rc = make_lsf_map(&tm_m, p.m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.B, p.T, p.D)) != JB200_OK) return rc;
+  if (FUSED) rc = make_lsf_map(&tm_io, p.resid, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.B, p.T, p.D);
+  else rc = make_lsf_map(&tm_io, p.out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, p.B, p.T, p.D);
+  if (rc != JB200_OK) return rc;
+  unsigned int* status = device_status_ptr();
+  if (!status) return JB200_ERR_CUDA;
+  if (p.nseg > 1) {
+    dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.n_pre_tiles);
+    lsf_scan_kernel<false, __nv_bfloat16, __nv_bfloat16, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);
+    JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
+  }
+  JB_CUDA(cudaFuncSetAttribute(lsf_tma_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               int(Cfg::smem_bytes(Cfg::STAGES_ALONE))));
+  dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
+  lsf_tma_kernel<FUSED><<<grid, LSF_THREADS, Cfg::smem_bytes(stages), stream>>>(tm_m, tm_io, p, stages, status);
+  JB_LAUNCH_CHECK("lsf_tma_kernel");
+  return JB200_OK;
+}
+
 // Segments so that about two CTAs per SM exist, each at least four tiles long.
 void pick_lsf_segments(int B, int T, int D, int sms, int* seg_len, int* nseg) {
   const long ctas = long((D + LSF_CH - 1) / LSF_CH) * B;
@@ -317,6 +527,11 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
   JB_REQUIRE(p.nseg <= 65535 && p.n_pre_tiles <= 65535, "lsf_scan: too many segments");
   const bool ta = alpha_tensor != nullptr;
   using bf = __nv_bfloat16;
+  // the forms the model and the scan sweep run: tiles by TMA (3-D maps need 16-byte aligned rows)
+  if (!ta && m_dtype == 1 && T > 8 && D % 8 == 0 && aligned16(m) && B * long(T) * D < (1L << 40)) {
+    if (resid && !out && aligned16(resid)) return launch_tma<true>(p, stream);
+    if (out && !resid && out_dtype == 1 && aligned16(out)) return launch_tma<false>(p, stream);
+  }
   if (!ta) {
     if (m_dtype == 1 && out_dtype == 1) return launch_t<false, bf, bf>(p, stream);
     if (m_dtype == 1 && out_dtype == 0) return launch_t<false, bf, float>(p, stream);
