@@ -376,12 +376,13 @@ def multi_gpu_records(model, device, rank, world, barrier):
             raise ValueError(f"world size {world} does not fit 65,536 tokens / {E} experts")
         torch.manual_seed(0)
         moe = synthetic.gaussian_ternary_(jm.SparseMoELayer(C), seed=0).to(device).eval()
-        peer = world <= E
+        peer = (world <= E and E % world == 0) or (world > E and world % E == 0)
         ep = par.PeerExpertParallelMoE(moe, max_tokens=N // world) if peer else par.ExpertParallelMoE(moe)
         rec = {"workload": "ternary top-2 MoE layer alone, 65,536 tokens x 1024 bf16, experts 1024->2048->1024, tokens "
                            "data parallel, experts spread over the ranks, rows " +
-                           ("pulled over NVLink by the gather / combine kernels (peer loads)" if peer
-                            else "exchanged with NCCL all-to-all (uneven splits), each expert served by world/4 ranks"),
+                           ("pulled over NVLink by the gather / combine kernels (peer loads); with more ranks than experts "
+                            "every expert is served by world/4 ranks" if peer
+                            else "exchanged with NCCL all-to-all (uneven splits)"),
                "cases": {}}
         for case in ("zipf_1.2", "balanced"):
             if case == "zipf_1.2":

@@ -279,7 +279,9 @@ int jb200_peer_buffer_close(void* ptr);
 int jb200_peer_buffer_free(void* ptr);
 
 /* The dispatch exchange of the MoE layer done by the gather itself: rank `rank` of `world` owns experts
- * [rank*E/world, (rank+1)*E/world) and builds their input rows by reading every rank's routing result and rows
+ * [rank*E/world, (rank+1)*E/world) - or, when world > E (world % E == 0), part rank % (world/E) of expert
+ * rank / (world/E): of every source's cnt rows of that expert the slice [cnt*part/shards, cnt*(part+1)/shards),
+ * with E/world read as 1 in the sizes below - and builds their input rows by reading every rank's routing result and rows
  * directly from that rank's memory (plain loads over NVLink; all pointers in the three device arrays must be
  * mapped in this process, e.g. CUDA IPC handles of the peers' buffers):
  *   peer_offs[s]: i32 [E + 2] = rank s's expert_offsets (jb200_moe_metadata) followed by its n_tokens

@@ -6,7 +6,10 @@
 //   xn     bf16 [n_tokens][C]   the rows the experts consume
 //   gmap   i32  [n_tokens*K]    expert-sorted position -> token (gather_map of jb200_moe_metadata)
 //   offs   i32  [E + 2]         expert_offsets of its own dispatch, then its n_tokens
-// Rank r owns experts [r*per, (r+1)*per).  Its pull-gather kernel builds, for each owned expert, the rows of
+// With world <= E rank r owns the experts [r*per, (r+1)*per), per = E / world.  With world > E every expert is
+// served by shards = world / E consecutive ranks: rank r owns part r % shards of expert r / shards, i.e. of every
+// source's cnt rows of that expert the slice [cnt*part/shards, cnt*(part+1)/shards) (the packed weights are 1 MiB
+// per expert, so replicas are free).  Its pull-gather kernel builds, for each owned expert (part), the rows of
 // every source rank in (source rank, local stable order) - the single-GPU dispatch order when ranks hold
 // contiguous token ranges (moe_compute_metadata_kernel, sparse_model_cuda/sparse_model.cu:23-90) - by reading
 // the peers' offs / gmap / xn directly, and publishes where each source's rows start (`meta`).  After the
@@ -29,7 +32,7 @@ struct PullGatherParams {
   const int32_t* const* offs;          // [world] -> peer offs arrays [E + 2]
   const int32_t* const* gmap;          // [world] -> peer gather maps
   const __nv_bfloat16* const* xn;      // [world] -> peer rows
-  int world, rank, per, E, C, K;
+  int world, rank, per, shards, E, C, K;
   int n_max;                           // capacity of every peer's xn buffer in tokens (its gmap holds n_max * K)
   int max_rows;                        // capacity of `dispatched` in rows
   __nv_bfloat16* dispatched;           // [max_rows][C]
@@ -47,11 +50,13 @@ ep_pull_gather_kernel(const PullGatherParams p) {
   const int W = p.world, per = p.per;
   for (int i = threadIdx.x; i < per * W; i += blockDim.x) {
     const int el = i / W, s = i - el * W;
-    const int e = p.rank * per + el;
+    const int e = p.shards > 1 ? p.rank / p.shards : p.rank * per + el;
+    const int part = p.shards > 1 ? p.rank % p.shards : 0;
     const int32_t* o = p.offs[s];
-    const int lo = o[e], hi = o[e + 1];
-    s_src_off[el][s] = lo;
-    s_pre[el][s + 1] = max(hi - lo, 0);        // counts for now
+    const int lo = o[e], cnt = max(o[e + 1] - lo, 0);
+    const int plo = int(long(cnt) * part / p.shards), phi = int(long(cnt) * (part + 1) / p.shards);
+    s_src_off[el][s] = lo + plo;
+    s_pre[el][s + 1] = phi - plo;              // counts for now
     if (el == 0) s_ntok[s] = o[p.E + 1];
   }
   __syncthreads();
@@ -101,23 +106,25 @@ struct PullCombineParams {
   const int64_t* topk_idx;             // [n_tokens][K]
   const float* gates;                  // [n_tokens][K]
   const int32_t* scatter_map;          // [n_tokens][K] position in this rank's expert-sorted order
-  int world, rank, per, E, C, K, n_tokens, max_rows;
+  int world, rank, per, shards, E, C, K, n_tokens, max_rows;
   double* stats;                       // [2] sum, sum of squares of the output (or null)
 };
 
 template <typename TOut>
 __global__ void __launch_bounds__(256)
 ep_pull_combine_kernel(const PullCombineParams p, TOut* __restrict__ out) {
-  __shared__ int s_base[EP_MAX_WORLD * EP_MAX_OWNED];   // per expert: first row of MY rows in the owner's y
+  __shared__ int s_base[EP_MAX_WORLD * EP_MAX_OWNED];   // per (expert, part): first row of MY rows in the owner's y
   __shared__ int s_off[EP_MAX_WORLD * EP_MAX_OWNED + 1];
   __shared__ float red[2][8];
-  const int W = p.world, per = p.per;
-  for (int e = threadIdx.x; e < p.E; e += blockDim.x) {
-    const int owner = e / per, el = e - owner * per;
+  const int W = p.world, per = p.per, SH = p.shards;
+  for (int i = threadIdx.x; i < p.E * SH; i += blockDim.x) {
+    const int e = i / SH, part = i - e * SH;
+    const int owner = SH > 1 ? e * SH + part : e / per;
+    const int el = SH > 1 ? 0 : e - owner * per;
     const int32_t* m = p.meta[owner];                              // peer loads
-    s_base[e] = m[per * (W + 1) + el] + m[el * (W + 1) + p.rank];
-    s_off[e] = p.offs_local[e];
+    s_base[i] = m[per * (W + 1) + el] + m[el * (W + 1) + p.rank];
   }
+  for (int e = threadIdx.x; e <= p.E; e += blockDim.x) s_off[e] = p.offs_local[e];
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * 8 + warp;
@@ -128,10 +135,18 @@ ep_pull_combine_kernel(const PullCombineParams p, TOut* __restrict__ out) {
       for (int k = 0; k < p.K; ++k) {
         long long e64 = p.topk_idx[size_t(tok) * p.K + k];
         const int e = e64 < 0 ? 0 : (e64 >= p.E ? p.E - 1 : int(e64));
-        int row = s_base[e] + (p.scatter_map[size_t(tok) * p.K + k] - s_off[e]);
+        const int q = p.scatter_map[size_t(tok) * p.K + k] - s_off[e];    // position among MY rows of expert e
+        int part = 0, plo = 0;
+        if (SH > 1) {                       // which owner took that slice of my rows (same bounds as its gather)
+          const int cnt = max(s_off[e + 1] - s_off[e], 0);
+          while (part + 1 < SH && q >= int(long(cnt) * (part + 1) / SH)) ++part;
+          plo = int(long(cnt) * part / SH);
+        }
+        const int owner = SH > 1 ? e * SH + part : e / per;
+        int row = s_base[e * SH + part] + (q - plo);
         row = row < 0 ? 0 : (row >= p.max_rows ? p.max_rows - 1 : row);     // never leave the owner's buffer
         const float g = p.gates[size_t(tok) * p.K + k];
-        const uint4 v = *reinterpret_cast<const uint4*>(p.y[e / per] + size_t(row) * p.C + c);   // peer load
+        const uint4 v = *reinterpret_cast<const uint4*>(p.y[owner] + size_t(row) * p.C + c);   // peer load
         acc[0] += g * bf16_lo(v.x); acc[1] += g * bf16_hi(v.x); acc[2] += g * bf16_lo(v.y); acc[3] += g * bf16_hi(v.y);
         acc[4] += g * bf16_lo(v.z); acc[5] += g * bf16_hi(v.z); acc[6] += g * bf16_lo(v.w); acc[7] += g * bf16_hi(v.w);
       }
@@ -163,8 +178,9 @@ ep_pull_combine_kernel(const PullCombineParams p, TOut* __restrict__ out) {
 }
 
 bool ep_shape_ok(int world, int rank, int E, int C) {
-  return world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world && E >= world && E % world == 0 &&
-         E / world <= EP_MAX_OWNED && E <= EP_MAX_WORLD * EP_MAX_OWNED && C > 0 && C % 8 == 0;
+  if (!(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world && E >= 1 && C > 0 && C % 8 == 0)) return false;
+  if (world <= E) return E % world == 0 && E / world <= EP_MAX_OWNED && E <= EP_MAX_WORLD * EP_MAX_OWNED;
+  return world % E == 0;        // every expert served by world / E ranks
 }
 
 }  // namespace
@@ -182,7 +198,8 @@ int launch_ep_pull_gather(const void* const* peer_offs, const void* const* peer_
   p.offs = reinterpret_cast<const int32_t* const*>(peer_offs);
   p.gmap = reinterpret_cast<const int32_t* const*>(peer_gmap);
   p.xn = reinterpret_cast<const __nv_bfloat16* const*>(peer_xn);
-  p.world = world; p.rank = rank; p.per = E / world; p.E = E; p.C = C; p.K = K; p.n_max = n_max; p.max_rows = max_rows;
+  p.world = world; p.rank = rank; p.per = world <= E ? E / world : 1; p.shards = world <= E ? 1 : world / E;
+  p.E = E; p.C = C; p.K = K; p.n_max = n_max; p.max_rows = max_rows;
   p.dispatched = reinterpret_cast<__nv_bfloat16*>(dispatched);
   p.seg_offsets = seg_offsets;
   p.meta = meta;
@@ -210,7 +227,8 @@ int launch_ep_pull_combine(const void* const* peer_y, const void* const* peer_me
   p.y = reinterpret_cast<const __nv_bfloat16* const*>(peer_y);
   p.meta = reinterpret_cast<const int32_t* const*>(peer_meta);
   p.offs_local = offs_local; p.topk_idx = topk_idx; p.gates = gates; p.scatter_map = scatter_map;
-  p.world = world; p.rank = rank; p.per = E / world; p.E = E; p.C = C; p.K = K; p.n_tokens = n_tokens;
+  p.world = world; p.rank = rank; p.per = world <= E ? E / world : 1; p.shards = world <= E ? 1 : world / E;
+  p.E = E; p.C = C; p.K = K; p.n_tokens = n_tokens;
   p.max_rows = max_rows; p.stats = stats;
   const int blocks = (n_tokens + 7) / 8;
   if (out_dtype == 1)

@@ -257,6 +257,7 @@ class SparseMoELayer(nn.Module):
         # 4 ints per layer).  None: the ranks' batches are independent calls.
         self.stats_group = None
         self._n_total_hint = None   # global token count when known (avoids a host read per layer)
+        self._ep = None             # parallel.PeerExpertParallelMoE: experts spread over the ranks of a group
         self.last_routing = None  # (topk_idx, gates, metadata) of the most recent call, for inspection
 
     def packed(self):
@@ -279,19 +280,29 @@ class SparseMoELayer(nn.Module):
         # norm=(weight, eps): `xn_rows` is the un-normalised f32 residual stream and RMSNorm is fused into
         # the router kernel (one pass over the row, routing bit-identical to the separate kernels)
         w_r = self.router.weight.detach().float().contiguous()
+        ep = self._ep
+        in_slab = False
         if norm is not None and C <= 1024:
-            xn_rows, idx, gates = ops.rmsnorm_router(xn_rows, norm[0], norm[1], w_r, probs_sum=acc[2:], top1_hist=hist)
+            # expert parallel: the normalised rows go straight into the buffer the other ranks read
+            in_slab = ep is not None and N <= ep.ex.n_max
+            xn_rows, idx, gates = ops.rmsnorm_router(xn_rows, norm[0], norm[1], w_r, probs_sum=acc[2:], top1_hist=hist,
+                                                     xn_out=ep.ex.xn[:N] if in_slab else None)
         else:
             if norm is not None:
                 xn_rows = ops.rmsnorm(xn_rows, norm[0], norm[1])
             idx, gates, _ = ops.router_top2(xn_rows, w_r, probs_sum=acc[2:], top1_hist=hist)
         meta = ops.moe_metadata(idx, E)
         counts, offsets, scatter, gather, gate_idx = meta
-        (p1, a1), (p2, a2) = self.packed()
-        disp = ops.dispatch_gather(xn_rows, gather)
-        hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
-        y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16, prepared=True)
-        out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
+        if ep is not None:
+            # the owners of the experts pull their rows from every rank, the home ranks pull the results back
+            out = ep.run_routed(xn_rows, idx, gates, offsets, scatter, gather, x_in_slab=in_slab, out_dtype=out_dtype,
+                                stats=acc[:2])
+        else:
+            (p1, a1), (p2, a2) = self.packed()
+            disp = ops.dispatch_gather(xn_rows, gather)
+            hid = ops.ternary_linear_grouped(disp, p1, a1, offsets, epilogue=ops.EPI_GELU_BF16, prepared=True)
+            y = ops.ternary_linear_grouped(hid, p2, a2, offsets, epilogue=ops.EPI_BF16, prepared=True)
+            out = ops.scatter_combine(y, gates, scatter, out_dtype=out_dtype, stats=acc[:2])
         n_total = N
         if self.stats_group is not None:
             import torch.distributed as dist
@@ -599,6 +610,32 @@ class Jarvis(nn.Module):
         for blk in self.blocks:
             blk.moe.stats_group = group
             blk.moe._n_total_hint = global_tokens
+
+    def set_expert_parallel(self, group, max_tokens: int | None = None, global_tokens: int | None = None):
+        """Spread the experts of every MoE layer over the ranks of `group` (one process per GPU on one node): the
+        ranks hold slices of ONE batch (as with set_batch_split: the per-layer statistics are all-reduced, so the
+        LSF decay and the auxiliary scalars are those of the whole batch), every rank routes its own tokens and
+        the expert rows travel by peer-memory loads (parallel.PeerExpertParallelMoE; the reference has no
+        multi-GPU code, jarvis_model.py:198-251 is the layer being split).  max_tokens: most tokens a rank
+        passes per call.  group=None: back to local experts (frees the exchange buffers)."""
+        from . import parallel
+        ex = getattr(self, "_ep_exchange", None)
+        for blk in self.blocks:
+            blk.moe._ep = None
+        if ex is not None:
+            ex.close()
+            self._ep_exchange = None
+        self.set_batch_split(group, global_tokens)
+        if group is None:
+            return
+        moe = self.blocks[0].moe
+        if max_tokens is None:
+            raise ValueError("set_expert_parallel: max_tokens (tokens per rank and call) is needed")
+        ex = parallel.PeerExchange(moe.num_experts, moe.top_k, self.d_model, moe.w1[0].weight.shape[0], max_tokens,
+                                   self.tok_emb.weight.device, group)
+        self._ep_exchange = ex
+        for blk in self.blocks:
+            blk.moe._ep = parallel.PeerExpertParallelMoE(blk.moe, exchange=ex)
 
     def set_context_parallel(self, group):
         """Sequence parallelism of `forward` / `hidden_rows`: the ranks of `group` hold consecutive T-token slices

@@ -348,15 +348,21 @@ def router_top2(x: torch.Tensor, w_router: torch.Tensor, *, want_probs: bool = F
 
 
 def rmsnorm_router(x: torch.Tensor, w_norm: torch.Tensor, eps: float, w_router: torch.Tensor, *, probs_sum=None,
-                   top1_hist=None):
-    """Fused norm2 + router: x f32 (N, C) -> (xn bf16 (N, C), topk_idx int64 (N, 2), gates f32 (N, 2))."""
+                   top1_hist=None, xn_out: torch.Tensor | None = None):
+    """Fused norm2 + router: x f32 (N, C) -> (xn bf16 (N, C), topk_idx int64 (N, 2), gates f32 (N, 2)).
+    xn_out: where to write the normalised rows (e.g. a buffer other GPUs read) instead of a new tensor."""
     lib = _lib.load()
     _need(x, torch.float32, "rmsnorm_router.x")
     _need(w_norm, torch.float32, "rmsnorm_router.w_norm")
     _need(w_router, torch.float32, "rmsnorm_router.w_router")
     N, C = x.shape
     E = w_router.shape[0]
-    xn = torch.empty((N, C), dtype=torch.bfloat16, device=x.device)
+    if xn_out is None:
+        xn = torch.empty((N, C), dtype=torch.bfloat16, device=x.device)
+    else:
+        xn = _need(xn_out, torch.bfloat16, "rmsnorm_router.xn_out")
+        if tuple(xn.shape) != (N, C):
+            raise RuntimeError("rmsnorm_router: xn_out has the wrong shape")
     idx = torch.empty((N, 2), dtype=torch.int64, device=x.device)
     gates = torch.empty((N, 2), dtype=torch.float32, device=x.device)
     _lib.check(lib.jb200_rmsnorm_router(_ptr(x), _ptr(w_norm), eps, _ptr(xn), _ptr(w_router), N, C, E, _ptr(idx),

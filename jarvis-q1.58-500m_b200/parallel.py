@@ -239,42 +239,35 @@ class ContextParallel:
         return scan(h_in), h_last
 
 
-class PeerExpertParallelMoE:
-    """Expert parallelism with the two exchanges done by kernels that read the other GPUs' memory directly
-    (csrc/ep_peer.cu) instead of NCCL all-to-alls: the owner of an expert pulls its input rows from every rank's
-    routing result, the home rank of a token pulls its expert outputs back.  Needs world <= num_experts,
-    num_experts % world == 0, one process per GPU on one node, and at most `max_tokens` tokens per rank and call.
+class PeerExchange:
+    """The buffers of the peer-memory expert exchange: one slab per rank (rows, gather map, offsets, expert outputs,
+    row bookkeeping) allocated once and mapped into every other rank through its CUDA IPC handle
+    (jb200_peer_buffer_*), plus the stream-ordered barrier that separates the phases.  One exchange serves any
+    number of layers (every call ends with a barrier, so the buffers are free again)."""
 
-    Buffers that peers read (rows, gather map, offsets, expert outputs, row bookkeeping) live in one slab per rank,
-    allocated once and mapped into every other rank through its CUDA IPC handle (jb200_peer_buffer_*).  No count is ever read back to the host; the phases
-    are separated by stream-ordered barriers (a one-element all-reduce).  Results equal the single-GPU layer
-    bit for bit when ranks hold contiguous token ranges (same rows in the same order through the same GEMMs)."""
-
-    def __init__(self, moe, max_tokens: int, group=None, out_dtype=torch.bfloat16):
+    def __init__(self, num_experts: int, top_k: int, d_model: int, hidden: int, max_tokens: int, device, group=None):
         import ctypes as C_
         from . import _lib
         self._lib = _lib
         lib = _lib.load()
-        self.moe = moe
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        E, K = moe.num_experts, moe.top_k
-        if self.world > E or E % self.world:
-            raise ValueError(f"peer expert parallelism needs world ({self.world}) to divide num_experts ({E})")
-        self.per = E // self.world
-        dev = moe.router.weight.device
-        C = moe.router.weight.shape[1]
-        self.C, self.E, self.K, self.n_max = C, E, K, max_tokens
-        self.max_rows = max_tokens * K * self.world          # every slot of every rank on one expert: the worst case
-        # one slab per rank holds everything its peers read; the same layout on every rank
+        E, K, C = num_experts, top_k, d_model
+        if not ((self.world <= E and E % self.world == 0) or (self.world > E and self.world % E == 0)):
+            raise ValueError(f"peer expert parallelism: world ({self.world}) must divide or be a multiple of num_experts ({E})")
+        self.shards = max(1, self.world // E)           # ranks serving one expert
+        self.per = max(1, E // self.world)              # experts (expert parts) owned by a rank
+        self.C, self.E, self.K, self.n_max, self.hidden = C, E, K, max_tokens, hidden
+        # every slot of every rank on one expert, cut into `shards` parts (rounded up): the worst case
+        self.max_rows = (max_tokens * K + self.shards - 1) // self.shards * self.world
         layout, off = {}, 0
         for name, nbytes in (("xn", max_tokens * C * 2), ("y", self.max_rows * C * 2), ("gmap", max_tokens * K * 4),
                              ("offs", (E + 2) * 4), ("meta", (self.per * (self.world + 1) + self.per + 1) * 4)):
             layout[name] = off
             off = (off + nbytes + 255) // 256 * 256
         self._slab_bytes = off
-        with torch.cuda.device(dev):
+        with torch.cuda.device(device):
             ptr, handle = C_.c_void_p(), (C_.c_ubyte * 64)()
             _lib.check(lib.jb200_peer_buffer_alloc(off, C_.byref(ptr), handle), "jb200_peer_buffer_alloc")
             self._slab = ptr.value
@@ -294,7 +287,7 @@ class PeerExpertParallelMoE:
             def __init__(self, address, nbytes):
                 self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (address, False), "version": 2}
 
-        slab = torch.as_tensor(_Raw(self._slab, off), device=dev)
+        slab = torch.as_tensor(_Raw(self._slab, off), device=device)
         slab.zero_()
 
         def view(name, dtype, shape):
@@ -309,16 +302,14 @@ class PeerExpertParallelMoE:
         self.gmap = view("gmap", torch.int32, (max_tokens * K,))
         self.offs = view("offs", torch.int32, (E + 2,))
         self.meta = view("meta", torch.int32, (self.per * (self.world + 1) + self.per + 1,))
-        self._ptrs = {name: torch.tensor([b + layout[name] for b in bases], dtype=torch.int64, device=dev) for name in layout}
-        self.disp = torch.empty((self.max_rows, C), dtype=torch.bfloat16, device=dev)
-        self.hid = None
-        self.seg = torch.zeros((self.per + 1,), dtype=torch.int32, device=dev)
-        self._flag = torch.zeros((1,), dtype=torch.float32, device=dev)
-        (p1, a1), (p2, a2) = moe.packed()
-        sel = torch.arange(self.rank * self.per, (self.rank + 1) * self.per, device=dev)
-        self._w = (p1[sel].contiguous(), a1[sel].contiguous(), p2[sel].contiguous(), a2[sel].contiguous())
-        self.out_dtype = out_dtype
-        torch.cuda.synchronize(dev)
+        self.ptrs = {name: torch.tensor([b + layout[name] for b in bases], dtype=torch.int64, device=device) for name in layout}
+        self.disp = torch.empty((self.max_rows, C), dtype=torch.bfloat16, device=device)
+        self.hid = torch.empty((self.max_rows, hidden), dtype=torch.bfloat16, device=device)
+        self.seg = torch.zeros((self.per + 1,), dtype=torch.int32, device=device)
+        self._flag = torch.zeros((1,), dtype=torch.float32, device=device)
+        self.owned = ([self.rank // self.shards] if self.shards > 1
+                      else list(range(self.rank * self.per, (self.rank + 1) * self.per)))
+        torch.cuda.synchronize(device)
         self.barrier()
 
     def barrier(self):
@@ -341,37 +332,86 @@ class PeerExpertParallelMoE:
         self._lib.check(lib.jb200_peer_buffer_free(self._slab), "jb200_peer_buffer_free")
         self._slab = None
 
+
+class PeerExpertParallelMoE:
+    """Expert parallelism with the two exchanges done by kernels that read the other GPUs' memory directly
+    (csrc/ep_peer.cu) instead of NCCL all-to-alls: the owner of an expert pulls its input rows from every rank's
+    routing result, the home rank of a token pulls its expert outputs back.  One process per GPU on one node;
+    world <= num_experts (E / world experts per rank) or a multiple of it (every expert served by world / E ranks,
+    each taking one contiguous slice of every source's rows); at most `max_tokens` tokens per rank and call.
+
+    No count is ever read back to the host; the phases are separated by stream-ordered barriers (a one-element
+    all-reduce).  Results equal the single-GPU layer bit for bit when ranks hold contiguous token ranges (same rows
+    in the same order through the same GEMMs).  Several layers may share one `PeerExchange`."""
+
+    def __init__(self, moe, max_tokens: int = 0, group=None, out_dtype=torch.bfloat16, exchange: PeerExchange | None = None):
+        from . import _lib
+        self._lib = _lib
+        self.moe = moe
+        self._own_exchange = exchange is None
+        if exchange is None:
+            dev = moe.router.weight.device
+            exchange = PeerExchange(moe.num_experts, moe.top_k, moe.router.weight.shape[1], moe.w1[0].weight.shape[0],
+                                    max_tokens, dev, group)
+        self.ex = exchange
+        self.group, self.world, self.rank = exchange.group, exchange.world, exchange.rank
+        self.out_dtype = out_dtype
+        self._w = None
+        self.seg = exchange.seg
+
+    def _owned_weights(self):
+        (p1, a1), (p2, a2) = self.moe.packed()
+        key = (p1.data_ptr(), p2.data_ptr())
+        if self._w is None or self._w[0] != key:
+            sel = torch.tensor(self.ex.owned, device=p1.device)
+            self._w = (key, p1[sel].contiguous(), a1[sel].contiguous(), p2[sel].contiguous(), a2[sel].contiguous())
+        return self._w[1:]
+
+    def barrier(self):
+        self.ex.barrier()
+
+    def close(self):
+        if self._own_exchange:
+            self.ex.close()
+
+    def run_routed(self, x, idx, gates, offsets, scatter, gather, *, x_in_slab=False, out_dtype=None, stats=None):
+        """The exchange for rows that are already routed: x bf16 (N, C) (or already sitting in the exchange's row
+        buffer), idx / gates / offsets / scatter / gather = this rank's router and dispatch-metadata results."""
+        from . import ops
+        ex = self.ex
+        lib, C, E, K = self._lib.load(), ex.C, ex.E, ex.K
+        N = idx.shape[0]
+        if N > ex.n_max:
+            raise RuntimeError(f"PeerExpertParallelMoE: {N} tokens exceed max_tokens={ex.n_max}")
+        stream = torch.cuda.current_stream().cuda_stream
+        if not x_in_slab:
+            ex.xn[:N].copy_(x)
+        ex.gmap[:N * K].copy_(gather)
+        ex.offs[:E + 1].copy_(offsets)
+        ex.offs[E + 1:].fill_(N)
+        ex.barrier()                                    # every rank's rows and routing are in place
+        self._lib.check(lib.jb200_ep_pull_gather(ex.ptrs["offs"].data_ptr(), ex.ptrs["gmap"].data_ptr(),
+                                                 ex.ptrs["xn"].data_ptr(), ex.world, ex.rank, E, C, K, ex.n_max,
+                                                 ex.max_rows, ex.disp.data_ptr(), ex.seg.data_ptr(),
+                                                 ex.meta.data_ptr(), stream), "jb200_ep_pull_gather")
+        p1, a1, p2, a2 = self._owned_weights()
+        ops.ternary_linear_grouped(ex.disp, p1, a1, ex.seg, epilogue=ops.EPI_GELU_BF16, out=ex.hid, prepared=True)
+        ops.ternary_linear_grouped(ex.hid, p2, a2, ex.seg, epilogue=ops.EPI_BF16, out=ex.y, prepared=True)
+        ex.barrier()                                    # every owner's outputs (and row bookkeeping) are in place
+        odt = out_dtype or self.out_dtype
+        out = torch.empty((N, C), dtype=odt, device=idx.device)
+        self._lib.check(lib.jb200_ep_pull_combine(ex.ptrs["y"].data_ptr(), ex.ptrs["meta"].data_ptr(),
+                                                  offsets.data_ptr(), idx.data_ptr(), gates.data_ptr(), scatter.data_ptr(),
+                                                  ex.world, ex.rank, E, C, K, N, ex.max_rows, out.data_ptr(),
+                                                  1 if odt == torch.bfloat16 else 0,
+                                                  None if stats is None else stats.data_ptr(), stream),
+                        "jb200_ep_pull_combine")
+        ex.barrier()                                    # nobody still reads buffers that the next call overwrites
+        return out
+
     def run_rows(self, x, stats=None):
         """x: bf16 (N_local, C) rows of this rank -> ((N_local, C) MoE output, (topk_idx, gates))."""
         from . import ops
-        lib, C, E, K = self._lib.load(), self.C, self.E, self.K
-        N = x.shape[0]
-        if N > self.n_max:
-            raise RuntimeError(f"PeerExpertParallelMoE: {N} tokens exceed max_tokens={self.n_max}")
-        stream = torch.cuda.current_stream().cuda_stream
         idx, gates, _ = ops.router_top2(x, self.moe.router.weight.detach().float().contiguous())
-        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, E)
-        self.xn[:N].copy_(x)
-        self.gmap[:N * K].copy_(gather)
-        self.offs[:E + 1].copy_(offsets)
-        self.offs[E + 1:].fill_(N)
-        self.barrier()                                  # every rank's rows and routing are in place
-        self._lib.check(lib.jb200_ep_pull_gather(self._ptrs["offs"].data_ptr(), self._ptrs["gmap"].data_ptr(),
-                                                 self._ptrs["xn"].data_ptr(), self.world, self.rank, E, C, K, self.n_max,
-                                                 self.max_rows, self.disp.data_ptr(), self.seg.data_ptr(),
-                                                 self.meta.data_ptr(), stream), "jb200_ep_pull_gather")
-        p1, a1, p2, a2 = self._w
-        if self.hid is None:
-            self.hid = torch.empty((self.max_rows, p1.shape[1]), dtype=torch.bfloat16, device=x.device)
-        ops.ternary_linear_grouped(self.disp, p1, a1, self.seg, epilogue=ops.EPI_GELU_BF16, out=self.hid, prepared=True)
-        ops.ternary_linear_grouped(self.hid, p2, a2, self.seg, epilogue=ops.EPI_BF16, out=self.y, prepared=True)
-        self.barrier()                                  # every owner's outputs (and row bookkeeping) are in place
-        out = torch.empty((N, C), dtype=self.out_dtype, device=x.device)
-        self._lib.check(lib.jb200_ep_pull_combine(self._ptrs["y"].data_ptr(), self._ptrs["meta"].data_ptr(),
-                                                  offsets.data_ptr(), idx.data_ptr(), gates.data_ptr(), scatter.data_ptr(),
-                                                  self.world, self.rank, E, C, K, N, self.max_rows, out.data_ptr(),
-                                                  1 if self.out_dtype == torch.bfloat16 else 0,
-                                                  None if stats is None else stats.data_ptr(), stream),
-                        "jb200_ep_pull_combine")
-        self.barrier()                                  # nobody still reads buffers that the next call overwrites
-        return out, (idx, gates)
+        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, self.ex.E)
+        return self.run_routed(x, idx, gates, offsets, scatter, gather, stats=stats), (idx, gates)

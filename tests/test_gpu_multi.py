@@ -135,3 +135,43 @@ def test_context_parallel_over_two_gpus_reproduces_the_whole_sequence(tmp_path):
     assert line["err"] < 5e-3 and line["err_a"] < 5e-3 and line["err_b"] < 5e-3
     assert line["err_h"] < 5e-3 and line["err_s"] < 5e-3
     assert line["token_pos"] == 640
+
+
+_EP_MODEL_SCRIPT = """
+import os, sys, json, torch, torch.distributed as dist
+sys.path.insert(0, os.getcwd())
+import jarvis_b200
+from jarvis_b200 import modules as jm
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+torch.manual_seed(0)
+model = jm.ternary_init_(jm.Jarvis(vocab_size=512, d_model=256, n_layers=3, n_heads=4, max_seq_len=256)).cuda().eval()
+idx = torch.randint(0, 512, (4, 192), generator=torch.Generator().manual_seed(1)).cuda()
+full, _ = model(idx)                                   # the whole batch with local experts: the reference result
+per = idx.shape[0] // world
+model.set_expert_parallel(dist.group.WORLD, max_tokens=per * idx.shape[1], global_tokens=idx.numel())
+part, _ = model(idx[rank * per:(rank + 1) * per])      # this rank's sequences, experts spread over the ranks
+err = float((part.float() - full[rank * per:(rank + 1) * per].float()).norm() / full.float().norm())
+again, _ = model(idx[rank * per:(rank + 1) * per])     # the exchange buffers are reused call after call
+same = bool(torch.equal(part, again))
+model.set_expert_parallel(None)
+local, _ = model(idx)
+back = bool(torch.equal(local, full))
+t = torch.tensor([err, 0.0 if same else 1.0, 0.0 if back else 1.0], device="cuda"); dist.all_reduce(t, op=dist.ReduceOp.MAX)
+if rank == 0: print(json.dumps({"err": float(t[0]), "repeatable": float(t[1]) == 0.0, "restored": float(t[2]) == 0.0}))
+dist.destroy_process_group()
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_model_with_experts_spread_over_two_gpus(tmp_path):
+    """Jarvis.set_expert_parallel: every MoE layer's experts on different GPUs, rows exchanged by peer-memory
+    loads, statistics all-reduced; logits equal those of the whole batch on one GPU up to the summation order of
+    the statistics (as with set_batch_split)."""
+    script = tmp_path / "ep_model.py"
+    script.write_text(_EP_MODEL_SCRIPT)
+    res = _torchrun(2, [str(script)])
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads(res.stdout.strip().splitlines()[-1])
+    assert line["err"] < 5e-3 and line["repeatable"] and line["restored"]
