@@ -46,6 +46,7 @@ extern "C" {
 #define JB200_STATUS_ATTN_LOAD 0x21u
 #define JB200_STATUS_ATTN_MMA 0x22u
 #define JB200_STATUS_LSF_LOAD 0x31u
+#define JB200_STATUS_PEER_BARRIER 0x41u
 #define JB200_STATUS_SELFTEST_WAIT 0x7Fu
 
 /* ---- library ----------------------------------------------------------------------- */
@@ -277,6 +278,17 @@ int jb200_peer_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64);
 int jb200_peer_buffer_open(const unsigned char* handle64, void** ptr);
 int jb200_peer_buffer_close(void* ptr);
 int jb200_peer_buffer_free(void* ptr);
+
+/* Stream-ordered barrier over the ranks of one node through flags in peer-mapped memory (a few microseconds,
+ * where a one-element collective costs a kernel launch of the communication library per rank).  peer_flags[r]:
+ * a block of JB200_PEER_FLAG_WORDS i32 in rank r's peer-mapped buffer, zeroed once at set-up; word s is written by
+ * rank s, the last word counts this rank's barriers.  The kernel (one warp) tells every rank that this rank's
+ * earlier work on the stream has finished and waits until every rank has said so; kernels launched after it on the
+ * stream see what the peers wrote before their call.  Every rank must call it the same number of times, one GPU
+ * per rank (ranks sharing a GPU would wait for kernels that cannot start).  The wait is bounded (2 s): on expiry
+ * the device status word gets JB200_STATUS_PEER_BARRIER and the kernel returns. */
+#define JB200_PEER_FLAG_WORDS 32
+int jb200_peer_barrier(const void* const* peer_flags, int world, int rank, void* stream);
 
 /* The dispatch exchange of the MoE layer done by the gather itself: rank `rank` of `world` owns experts
  * [rank*E/world, (rank+1)*E/world) - or, when world > E (world % E == 0), part rank % (world/E) of expert

@@ -58,6 +58,7 @@ PROTOTYPES = {
     "jb200_peer_buffer_open": (_I, [_P, _P]),
     "jb200_peer_buffer_close": (_I, [_P]),
     "jb200_peer_buffer_free": (_I, [_P]),
+    "jb200_peer_barrier": (_I, [_P, _I, _I, _P]),
     "jb200_ep_pull_gather": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P, _P]),
     "jb200_ep_pull_combine": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _P, _P]),
     "jb200_sample": (_I, [_P, _I, _I, _I, _I, _F, _I, _F, _P, _P, _P, _P]),

@@ -171,6 +171,10 @@ int jb200_qkv_linear_rope(const void* x, int M, int K, const uint8_t* packed, co
                              w_layout, static_cast<cudaStream_t>(stream), &r);
 }
 
+int jb200_peer_barrier(const void* const* peer_flags, int world, int rank, void* stream) {
+  return launch_peer_barrier(peer_flags, world, rank, static_cast<cudaStream_t>(stream));
+}
+
 int jb200_peer_buffer_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
   JB_REQUIRE(bytes > 0 && ptr && handle64, "peer_buffer_alloc: bad arguments");
   void* d = nullptr;

@@ -81,21 +81,52 @@ ep_pull_gather_kernel(const PullGatherParams p) {
   }
   const int total = min(s_seg[per], p.max_rows);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int row = blockIdx.x * 8 + warp; row < total; row += gridDim.x * 8) {
-    int el = 0;
-    while (el + 1 < per && row >= s_seg[el + 1]) ++el;
-    const int within = row - s_seg[el];
-    int s = 0;
-    while (s + 1 < W && within >= s_pre[el][s + 1]) ++s;
-    const int i = within - s_pre[el][s];
-    const int ntok = min(max(s_ntok[s], 1), p.n_max);
-    int slot = s_src_off[el][s] + i;
-    slot = slot < 0 ? 0 : (slot >= ntok * p.K ? ntok * p.K - 1 : slot);   // never leave the peer's map
-    int tok = p.gmap[s][slot];                                   // peer load
-    tok = tok < 0 ? 0 : (tok >= ntok ? ntok - 1 : tok);          // never leave the peer's buffer
-    const uint4* src = reinterpret_cast<const uint4*>(p.xn[s] + size_t(tok) * p.C);
-    uint4* dst = reinterpret_cast<uint4*>(p.dispatched + size_t(row) * p.C);
-    for (int c = lane; c < p.C / 8; c += 32) dst[c] = src[c];     // peer loads, 16 B per lane
+  // Peer loads have a latency of microseconds, and a row costs two dependent ones (gather map entry, then the row):
+  // a warp therefore works on four rows at once - lanes 0-3 look the four tokens up, then every lane has up to 16
+  // independent 16-byte loads in flight before the first store.
+  constexpr int RPW = 4;
+  const int chunks = p.C / 8;                                    // 16-byte pieces per row
+  for (int row0 = (blockIdx.x * 8 + warp) * RPW; row0 < total; row0 += gridDim.x * 8 * RPW) {
+    int my_src = 0, my_tok = 0;
+    if (lane < RPW && row0 + lane < total) {
+      const int row = row0 + lane;
+      int el = 0;
+      while (el + 1 < per && row >= s_seg[el + 1]) ++el;
+      const int within = row - s_seg[el];
+      int s = 0;
+      while (s + 1 < W && within >= s_pre[el][s + 1]) ++s;
+      const int i = within - s_pre[el][s];
+      const int ntok = min(max(s_ntok[s], 1), p.n_max);
+      int slot = s_src_off[el][s] + i;
+      slot = slot < 0 ? 0 : (slot >= ntok * p.K ? ntok * p.K - 1 : slot);   // never leave the peer's map
+      int tok = p.gmap[s][slot];                                   // peer load
+      tok = tok < 0 ? 0 : (tok >= ntok ? ntok - 1 : tok);          // never leave the peer's buffer
+      my_src = s;
+      my_tok = tok;
+    }
+    const uint4* src[RPW];
+#pragma unroll
+    for (int r = 0; r < RPW; ++r) {
+      const int s = __shfl_sync(0xffffffffu, my_src, r), tok = __shfl_sync(0xffffffffu, my_tok, r);
+      src[r] = reinterpret_cast<const uint4*>(p.xn[s] + size_t(tok) * p.C);
+    }
+    for (int c0 = 0; c0 < chunks; c0 += 128) {                     // 128 pieces = 4 per lane
+      uint4 v[RPW][4];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (row0 + r < total && c < chunks) v[r][j] = src[r][c];   // peer loads, 16 B per lane
+        }
+#pragma unroll
+      for (int r = 0; r < RPW; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (row0 + r < total && c < chunks) reinterpret_cast<uint4*>(p.dispatched + size_t(row0 + r) * p.C)[c] = v[r][j];
+        }
+    }
   }
 }
 
@@ -130,36 +161,87 @@ ep_pull_combine_kernel(const PullCombineParams p, TOut* __restrict__ out) {
   const int tok = blockIdx.x * 8 + warp;
   float s1 = 0.f, s2 = 0.f;
   if (tok < p.n_tokens) {
-    for (int c = lane * 8; c < p.C; c += 256) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int k = 0; k < p.K; ++k) {
-        long long e64 = p.topk_idx[size_t(tok) * p.K + k];
-        const int e = e64 < 0 ? 0 : (e64 >= p.E ? p.E - 1 : int(e64));
-        const int q = p.scatter_map[size_t(tok) * p.K + k] - s_off[e];    // position among MY rows of expert e
-        int part = 0, plo = 0;
-        if (SH > 1) {                       // which owner took that slice of my rows (same bounds as its gather)
-          const int cnt = max(s_off[e + 1] - s_off[e], 0);
-          while (part + 1 < SH && q >= int(long(cnt) * (part + 1) / SH)) ++part;
-          plo = int(long(cnt) * part / SH);
+    // the token's K rows and gates first (lanes 0..K-1 resolve one slot each), then all loads of a 1024-column
+    // span (K x 4 pieces of 16 bytes per lane) are issued before the first is used
+    int my_row = 0, my_owner = 0;
+    float my_gate = 0.f;
+    if (lane < p.K) {
+      const int k = lane;
+      long long e64 = p.topk_idx[size_t(tok) * p.K + k];
+      const int e = e64 < 0 ? 0 : (e64 >= p.E ? p.E - 1 : int(e64));
+      const int q = p.scatter_map[size_t(tok) * p.K + k] - s_off[e];    // position among MY rows of expert e
+      int part = 0, plo = 0;
+      if (SH > 1) {                       // which owner took that slice of my rows (same bounds as its gather)
+        const int cnt = max(s_off[e + 1] - s_off[e], 0);
+        while (part + 1 < SH && q >= int(long(cnt) * (part + 1) / SH)) ++part;
+        plo = int(long(cnt) * part / SH);
+      }
+      my_owner = SH > 1 ? e * SH + part : e / per;
+      int row = s_base[e * SH + part] + (q - plo);
+      my_row = row < 0 ? 0 : (row >= p.max_rows ? p.max_rows - 1 : row);     // never leave the owner's buffer
+      my_gate = p.gates[size_t(tok) * p.K + k];
+    }
+    int rows[8], owners[8];          // all lanes of the warp take part in the exchange, whatever their columns
+    float gs[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      rows[k] = __shfl_sync(0xffffffffu, my_row, k);
+      owners[k] = __shfl_sync(0xffffffffu, my_owner, k);
+      gs[k] = k < p.K ? __shfl_sync(0xffffffffu, my_gate, k) : 0.f;
+    }
+    for (int c0 = lane * 8; c0 < p.C; c0 += 1024) {
+      float acc[4][8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+      for (int k0 = 0; k0 < p.K; k0 += 2) {           // two slots at a time: 8 loads in flight per lane
+        uint4 v[2][4];
+        float g[2];
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const int k = k0 + kk < p.K ? k0 + kk : k0;
+          int row = rows[0], owner = owners[0];
+#pragma unroll
+          for (int t = 1; t < 8; ++t)
+            if (t == k) { row = rows[t]; owner = owners[t]; }
+          float gk = gs[0];
+#pragma unroll
+          for (int t = 1; t < 8; ++t)
+            if (t == k) gk = gs[t];
+          g[kk] = k0 + kk < p.K ? gk : 0.f;
+          const __nv_bfloat16* yr = p.y[owner] + size_t(row) * p.C;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c0 + j * 256;
+            v[kk][j] = c < p.C ? *reinterpret_cast<const uint4*>(yr + c) : make_uint4(0u, 0u, 0u, 0u);   // peer load
+          }
         }
-        const int owner = SH > 1 ? e * SH + part : e / per;
-        int row = s_base[e * SH + part] + (q - plo);
-        row = row < 0 ? 0 : (row >= p.max_rows ? p.max_rows - 1 : row);     // never leave the owner's buffer
-        const float g = p.gates[size_t(tok) * p.K + k];
-        const uint4 v = *reinterpret_cast<const uint4*>(p.y[owner] + size_t(row) * p.C + c);   // peer load
-        acc[0] += g * bf16_lo(v.x); acc[1] += g * bf16_hi(v.x); acc[2] += g * bf16_lo(v.y); acc[3] += g * bf16_hi(v.y);
-        acc[4] += g * bf16_lo(v.z); acc[5] += g * bf16_hi(v.z); acc[6] += g * bf16_lo(v.w); acc[7] += g * bf16_hi(v.w);
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 w = v[kk][j];
+            acc[j][0] += g[kk] * bf16_lo(w.x); acc[j][1] += g[kk] * bf16_hi(w.x); acc[j][2] += g[kk] * bf16_lo(w.y);
+            acc[j][3] += g[kk] * bf16_hi(w.y); acc[j][4] += g[kk] * bf16_lo(w.z); acc[j][5] += g[kk] * bf16_hi(w.z);
+            acc[j][6] += g[kk] * bf16_lo(w.w); acc[j][7] += g[kk] * bf16_hi(w.w);
+          }
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) { s1 += acc[j]; s2 += acc[j] * acc[j]; }
-      if constexpr (sizeof(TOut) == 2) {
-        *reinterpret_cast<uint4*>(out + size_t(tok) * p.C + c) =
-            make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
-      } else {
-        float4* o = reinterpret_cast<float4*>(out + size_t(tok) * p.C + c);
-        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + j * 256;
+        if (c >= p.C) continue;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { s1 += acc[j][i]; s2 += acc[j][i] * acc[j][i]; }
+        if constexpr (sizeof(TOut) == 2) {
+          *reinterpret_cast<uint4*>(out + size_t(tok) * p.C + c) =
+              make_uint4(pack_bf16x2(acc[j][0], acc[j][1]), pack_bf16x2(acc[j][2], acc[j][3]), pack_bf16x2(acc[j][4], acc[j][5]),
+                         pack_bf16x2(acc[j][6], acc[j][7]));
+        } else {
+          float4* o = reinterpret_cast<float4*>(out + size_t(tok) * p.C + c);
+          o[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+          o[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+        }
       }
     }
   }
@@ -177,6 +259,34 @@ ep_pull_combine_kernel(const PullCombineParams p, TOut* __restrict__ out) {
   }
 }
 
+// Barrier over the ranks through flags in peer memory.  Thread t < world writes this rank's barrier count into
+// slot `rank` of rank t's flag block (release, system scope: everything this GPU wrote before is visible to a
+// peer that reads the flag with acquire), then waits for slot t of its own block to reach the same count.
+__global__ void __launch_bounds__(32) peer_barrier_kernel(int32_t* const* flags, int world, int rank, unsigned int* status) {
+  __shared__ int epoch;
+  int32_t* mine = flags[rank];
+  if (threadIdx.x == 0) epoch = ++mine[JB200_PEER_FLAG_WORDS - 1];
+  __syncwarp();
+  const int e = epoch;
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags[t] + rank), "r"(e) : "memory");
+    const unsigned long long t0 = globaltimer_ns();
+    int v;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine + t) : "memory");
+      if (v - e >= 0) break;                       // counts only grow: a peer may already be one barrier ahead
+      if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+        atomicCAS(status, 0u, JB200_STATUS_PEER_BARRIER);
+        break;
+      }
+      __nanosleep(100);
+    }
+    __threadfence_system();
+  }
+}
+
 bool ep_shape_ok(int world, int rank, int E, int C) {
   if (!(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world && E >= 1 && C > 0 && C % 8 == 0)) return false;
   if (world <= E) return E % world == 0 && E / world <= EP_MAX_OWNED && E <= EP_MAX_WORLD * EP_MAX_OWNED;
@@ -184,6 +294,17 @@ bool ep_shape_ok(int world, int rank, int E, int C) {
 }
 
 }  // namespace
+
+int launch_peer_barrier(const void* const* peer_flags, int world, int rank, cudaStream_t stream) {
+  JB_REQUIRE(peer_flags && world >= 1 && world <= JB200_PEER_FLAG_WORDS - 1 && rank >= 0 && rank < world,
+             "peer_barrier: bad arguments (world=%d, rank=%d)", world, rank);
+  unsigned int* status = device_status_ptr();
+  if (!status) return JB200_ERR_CUDA;
+  peer_barrier_kernel<<<1, 32, 0, stream>>>(reinterpret_cast<int32_t* const*>(const_cast<void* const*>(
+                                                reinterpret_cast<const void* const*>(peer_flags))), world, rank, status);
+  JB_LAUNCH_CHECK("peer_barrier_kernel");
+  return JB200_OK;
+}
 
 int launch_ep_pull_gather(const void* const* peer_offs, const void* const* peer_gmap, const void* const* peer_xn,
                           int world, int rank, int E, int C, int K, int n_max, int max_rows, void* dispatched,

@@ -63,6 +63,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
                      int head_dim, int flags, cudaStream_t stream);
 size_t attn_scan_scratch_bytes(int B, int T, int H);
 
+int launch_peer_barrier(const void* const* peer_flags, int world, int rank, cudaStream_t stream);
 int launch_ep_pull_gather(const void* const* peer_offs, const void* const* peer_gmap, const void* const* peer_xn,
                           int world, int rank, int E, int C, int K, int n_max, int max_rows, void* dispatched,
                           int32_t* seg_offsets, int32_t* meta, cudaStream_t stream);

@@ -263,7 +263,8 @@ class PeerExchange:
         self.max_rows = (max_tokens * K + self.shards - 1) // self.shards * self.world
         layout, off = {}, 0
         for name, nbytes in (("xn", max_tokens * C * 2), ("y", self.max_rows * C * 2), ("gmap", max_tokens * K * 4),
-                             ("offs", (E + 2) * 4), ("meta", (self.per * (self.world + 1) + self.per + 1) * 4)):
+                             ("offs", (E + 2) * 4), ("meta", (self.per * (self.world + 1) + self.per + 1) * 4),
+                             ("flags", 32 * 4)):
             layout[name] = off
             off = (off + nbytes + 255) // 256 * 256
         self._slab_bytes = off
@@ -310,18 +311,22 @@ class PeerExchange:
         self.owned = ([self.rank // self.shards] if self.shards > 1
                       else list(range(self.rank * self.per, (self.rank + 1) * self.per)))
         torch.cuda.synchronize(device)
-        self.barrier()
+        dist.all_reduce(self._flag, group=self.group)      # every slab (and its zeroed flag block) exists and is mapped
+        torch.cuda.synchronize(device)
 
     def barrier(self):
         """Stream-ordered barrier over the ranks: every rank's earlier kernels have finished (and their writes are
-        in device memory) before any rank's later kernels start."""
-        dist.all_reduce(self._flag, group=self.group)
+        visible to the peers) before any rank's later kernels start.  Flags in the peer-mapped slabs
+        (jb200_peer_barrier), not a collective of the communication library: a few microseconds."""
+        self._lib.check(self._lib.load().jb200_peer_barrier(self.ptrs["flags"].data_ptr(), self.world, self.rank,
+                                                           torch.cuda.current_stream().cuda_stream), "jb200_peer_barrier")
 
     def close(self):
         """Unmap the peers' slabs and free this rank's (call on every rank before the process group goes away)."""
         if self._slab is None:
             return
-        self.barrier()
+        torch.cuda.synchronize()
+        dist.all_reduce(self._flag, group=self.group)      # every rank is done with the peers' slabs
         torch.cuda.synchronize()
         lib = self._lib.load()
         for p in self._opened:
@@ -406,7 +411,10 @@ class PeerExpertParallelMoE:
                                                   1 if odt == torch.bfloat16 else 0,
                                                   None if stats is None else stats.data_ptr(), stream),
                         "jb200_ep_pull_combine")
-        ex.barrier()                                    # nobody still reads buffers that the next call overwrites
+        # No barrier at the end: what the next call writes before ITS first barrier (rows, gather map, offsets)
+        # was last read by the peers' gathers, which finished before the second barrier above; everything else
+        # (dispatched rows, expert outputs, bookkeeping) is written after that first barrier, which no rank passes
+        # before every rank's combine of this call has finished.
         return out
 
     def run_rows(self, x, stats=None):
