@@ -177,6 +177,13 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, int c0, int c1, i
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(src_smem)
                : "memory");
 }
+// Tile reduction shared -> global: global[tile] += smem[tile] (element type from the tensor map), done by the memory
+// system; rows / columns outside the tensor are clipped.  Coordinates must not be negative.
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, int c0, int c1, uint32_t src_smem) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(src_smem)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until all but the newest `N` bulk groups of this thread have finished READING their shared-memory source.
 template <int N>

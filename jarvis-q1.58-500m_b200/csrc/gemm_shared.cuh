@@ -85,6 +85,9 @@ struct GemmParams {
   int epilogue;
   int w_layout;              // 0 canonical weight_packing.py layout, 1 prepared layout
   unsigned int* status;
+  // JB200_EPI_RESID_F32: 8 staging tiles of [32 tokens][32 features] f32 in shared memory (one per epilogue warp),
+  // from which the tile is ADDED to the residual stream by a TMA reduction; 0 = plain read-modify-write from registers
+  uint32_t resid_stage_smem;
   // JB200_EPI_QK_ROPE_BF16 only: attention feature map + rotary embedding applied to out-features < rope_feats
   const float* cos_tab;      // [n_pos][32]
   const float* sin_tab;      // [n_pos][32]
@@ -130,8 +133,30 @@ __device__ __forceinline__ void prefetch_residual_rows(const GemmParams& p, int 
 // whose bandwidth the tensor core's operand reads, the TMA writes and the decoders already use up.
 // Called by a whole epilogue warp.
 __device__ __forceinline__ void store_acc_chunk(const GemmParams& p, uint32_t taddr, float alpha, size_t row0, int f0,
-                                                int ntok, int lane) {
+                                                int ntok, int lane, const CUtensorMap* tmap_out = nullptr,
+                                                uint32_t stage_smem = 0) {
   uint32_t v[32];
+  if (p.epilogue == JB200_EPI_RESID_F32 && stage_smem != 0) {
+    // x[token][feature] += alpha * acc through the memory system: lane = feature, register = token, so writing
+    // register t to stage[t][lane] is one conflict-free 128-byte row per instruction - no shuffles, no loads of
+    // the old values, nothing waits on global memory.  The tile then leaves as one TMA reduce-add (f32), which
+    // clips token rows past the end of the matrix.
+    tmem_ld_32x32(taddr, v);
+    tmem_ld_wait();
+    if (lane == 0) bulk_wait_group_read<0>();     // the previous reduction has finished reading this warp's stage
+    __syncwarp();
+    const uint32_t dst = stage_smem + uint32_t(lane) * 4u;
+#pragma unroll
+    for (int t = 0; t < 32; ++t)
+      asm volatile("st.shared.f32 [%0], %1;" ::"r"(dst + uint32_t(t) * 128u), "f"(alpha * __uint_as_float(v[t])) : "memory");
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_reduce_add_2d(tmap_out, f0, int(row0), stage_smem);
+      bulk_commit_group();
+    }
+    return;
+  }
   if (p.epilogue == JB200_EPI_QK_ROPE_BF16 && f0 < p.rope_feats) {
     // q / k heads whose weight rows were interleaved so that features d and d + 32 of a head are neighbouring
     // out-features (2i, 2i + 1): the lane pair that already swaps values for the bf16x2 store holds exactly

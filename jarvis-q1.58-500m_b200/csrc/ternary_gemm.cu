@@ -22,7 +22,11 @@
 //                instruction latency per K-block exceeds the 512 cycles its MMAs take); thread r of a
 //                group owns weight row r of the tile
 //   warps 10-17  epilogue (two warps per TMEM lane quadrant, alternate 32-token chunks): TMEM -> registers ->
-//                alpha / GELU / residual add -> row-segment stores straight from registers
+//                alpha / GELU -> row-segment stores straight from registers.  The f32 residual epilogue
+//                (x += alpha * acc) sends every other chunk through a [32 tokens][32 features] staging tile and a
+//                TMA reduce-add (cp.reduce.async.bulk.tensor .add.f32: no load of the old values, no shuffles)
+//                and the rest through a read-modify-write from registers, so that the L2's reduction path and
+//                the load/store path each carry half of the tile
 // Two accumulator buffers (2 x 256 TMEM columns) let the epilogue of tile i overlap the
 // main loop of tile i+1.  Token rows may be split into segments (one per expert), each
 // with its own weight matrix and alpha: the grouped form used by the MoE experts.
@@ -68,8 +72,10 @@ struct SmemCtl {
   int32_t seg[MAX_GROUPS + 1];
 };
 
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + size_t(STAGES) * (A_STAGE_BYTES + B_STAGE_BYTES) +
-                              ((sizeof(SmemCtl) + 127) / 128) * 128;
+constexpr size_t CTL_BYTES = ((sizeof(SmemCtl) + 127) / 128) * 128;
+constexpr int RESID_STAGE_BYTES = 32 * 32 * 4;                   // one [32 tokens][32 features] f32 tile per epilogue warp
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + size_t(STAGES) * (A_STAGE_BYTES + B_STAGE_BYTES) + CTL_BYTES;
+constexpr size_t SMEM_BYTES_RESID = SMEM_BYTES + 8 * RESID_STAGE_BYTES;
 
 struct TileCoord {
   int group;     // segment / expert
@@ -99,7 +105,7 @@ __device__ __forceinline__ bool tile_coord(const SmemCtl* ctl, int t, int n_ft, 
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_out, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -240,6 +246,12 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
     // ---------------- epilogue ----------------
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
     const int half = (warp - EPI_WARP0) >> 2; // which of the alternating 32-token chunks
+    // residual epilogue through TMA reductions: this warp's staging tile sits behind the control block
+    const uint32_t stage_smem = p.resid_stage_smem
+                                    ? base + uint32_t(STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + CTL_BYTES) +
+                                          uint32_t(warp - EPI_WARP0) * RESID_STAGE_BYTES
+                                    : 0u;
+    if (stage_smem && lane == 0) tma_prefetch_desc(&tmap_out);
     uint32_t tile_n = 0;
     TileCoord tc;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_n) {
@@ -259,11 +271,15 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       for (int c0 = half * 32; c0 < bn; c0 += 64) {
         if (tc.tok0 + c0 >= tc.tok_end) break;   // warp-uniform
         const int ntok = min(32, tc.tok_end - (tc.tok0 + c0));
-        store_acc_chunk(p, t_lane + c0, alpha, size_t(tc.tok0 + c0), tc.ft * BM + q * 32, ntok, lane);
+        // the reductions go through the L2's atomic units, the register read-modify-write through the load/store
+        // path: alternate chunks use one and the other, so both carry half of the tile
+        store_acc_chunk(p, t_lane + c0, alpha, size_t(tc.tok0 + c0), tc.ft * BM + q * 32, ntok, lane, &tmap_out,
+                        ((c0 >> 6) & 1) ? 0u : stage_smem);
       }
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&ctl->tmem_empty[acc]));
     }
+    if (stage_smem && lane == 0) bulk_wait_group<0>();   // every reduction has landed before the CTA ends
   }
 
 done:
@@ -377,11 +393,29 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
     }
   }
 
+  // Residual epilogue of a single matrix: the tile is added to the f32 stream by TMA reductions (needs 16-byte
+  // aligned rows); grouped calls and odd strides keep the read-modify-write from registers.
+  CUtensorMap tmap_out = tmap;
+  p.resid_stage_smem = 0;
+  if (epilogue == JB200_EPI_RESID_F32 && G == 1 && N % 4 == 0 && aligned16(out)) {
+    const cuuint64_t odim[2] = {cuuint64_t(N), cuuint64_t(M)};
+    const cuuint64_t ostride[1] = {cuuint64_t(N) * 4};
+    const cuuint32_t obox[2] = {32, 32};
+    cr = enc(&tmap_out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, odim, ostride, obox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) {
+      set_error("ternary_linear: cuTensorMapEncodeTiled failed for the residual stream (%d)", int(cr));
+      return JB200_ERR_CUDA;
+    }
+    p.resid_stage_smem = 1;
+  }
+  const size_t smem_bytes = p.resid_stage_smem ? SMEM_BYTES_RESID : SMEM_BYTES;
+
   // per device and cheap: set on every call rather than remembering which devices have seen it
-  JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES)));
+  JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES_RESID)));
   const long max_tiles = long((M + bn - 1) / bn + (G - 1)) * n_ft;
   const int grid = int(max_tiles < sms ? max_tiles : sms);
-  ternary_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmap, tmap_w, p);
+  ternary_gemm_kernel<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmap, tmap_w, tmap_out, p);
   JB_LAUNCH_CHECK("ternary_gemm_kernel");
   return JB200_OK;
 }
