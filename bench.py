@@ -56,7 +56,7 @@ GEMM_DRAM_BYTES_PER_LAUNCH = (80.9e6 + 111.5e6 + 152.5e6 + 174.8e6) / 4
 # the same two counters for one launch of the attention pipeline kernel (B=8 x T=2048: 136.3 MB algorithmic) and
 # of the LSF scan with the fused f32 residual (167.8 MB algorithmic)
 ATTN_DRAM_BYTES_PER_LAUNCH = 114.5e6
-LSF_DRAM_BYTES_PER_LAUNCH = None
+LSF_DRAM_BYTES_PER_LAUNCH = 112.4e6
 
 
 def measured_peaks():
@@ -283,7 +283,7 @@ def run_ours(args, rank, world, local_rank):
     peak_tf = peaks["bf16_tflops"] if near_max else peaks["bf16_tflops_sustained"]
     scans = {}
     for kind, name, traffic in (("attn", "attn_scan_pipe_kernel (+ attn_state_pass_kernel)", ATTN_DRAM_BYTES_PER_LAUNCH),
-                                ("lsf", "lsf_scan_kernel (fused f32 residual)", LSF_DRAM_BYTES_PER_LAUNCH)):
+                                ("lsf", "lsf_tma_kernel (fused f32 residual)", LSF_DRAM_BYTES_PER_LAUNCH)):
         n_k, k_ms, k_bytes = timers.summary(kind)
         gbs = k_bytes / (k_ms * 1e-3) / 1e9 if k_ms > 0 else 0.0
         scans[kind + "_scan"] = {"bound": "hbm", "kernel": name, "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
