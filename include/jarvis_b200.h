@@ -61,6 +61,14 @@ int jb200_abi_version(void);
  * (returns the count before resetting when `reset` is non-zero). */
 long long jb200_kernel_launches(int reset);
 
+/* The kernels of the forward chain are launched with programmatic stream serialisation: each starts while the
+ * kernel before it on the stream is still running and waits (griddepcontrol.wait) before it touches memory, so
+ * launch latency and set-up overlap the predecessor; captured into CUDA graphs as programmatic edges.  No
+ * reference counterpart (the reference launches each kernel fully serialised).  enable = 0 launches them fully
+ * serialised again; returns the previous setting.  The environment variable JB200_DEPENDENT_LAUNCH=0 sets the
+ * initial state. */
+int jb200_set_dependent_launch(int enable);
+
 /* Reads the current device's status word into *status (synchronises the device) and,
  * when `clear` is non-zero, resets it to 0. */
 int jb200_device_status(unsigned int* status, int clear);
@@ -267,6 +275,18 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
                    const float* act_var, const float* var_scale, float alpha_min, float alpha_max, const float* h0,
                    float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
                    void* stream);
+
+/* Tail of a block for single-token steps (T = 1), three of the calls above in one launch with their results bit
+ * for bit: jb200_moe_finalize (scalars from the accumulators; SparseMoELayer.forward, jarvis_model.py:244-250),
+ * jb200_lsf_scan at T = 1 with the fused residual (decay from act_var; LiquidStateFusion.forward, jarvis_model.py:
+ * 281-314, and the residual add :436: h_out = a*h_in + (1-a)*m, x += h_out) and, when w_norm is given, the
+ * jb200_rmsnorm that follows (norm1 of the next block, jarvis_model.py:430, or the final norm :516) into xn_bf16.
+ * m_bf16, xn_bf16: bf16 [B][C]; h_in (NULL = zeros), h_out (may alias h_in), x: f32 [B][C]; C a multiple of 8,
+ * at most 1024.  n_tokens / n_elems as in jb200_moe_finalize. */
+int jb200_lsf_step_norm(const void* m_bf16, const double* stats, const double* probs_sum, const int32_t* top1_hist,
+                        int E, long long n_tokens, long long n_elems, float balance_alpha, float* scalars,
+                        const float* var_scale, float alpha_min, float alpha_max, const float* h_in, float* h_out,
+                        float* x, const float* w_norm, float eps, void* xn_bf16, int B, int C, void* stream);
 
 /* ---- expert parallelism over peer memory (no counterpart: the reference is single-GPU) ------------------- */
 

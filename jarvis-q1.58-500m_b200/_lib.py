@@ -28,6 +28,7 @@ PROTOTYPES = {
     "jb200_last_error": (C.c_char_p, []),
     "jb200_abi_version": (_I, []),
     "jb200_kernel_launches": (C.c_longlong, [_I]),
+    "jb200_set_dependent_launch": (_I, [_I]),
     "jb200_device_status": (_I, [C.POINTER(C.c_uint), _I]),
     "jb200_selftest_bounded_wait": (_I, [_I, _P]),
     "jb200_pack_ternary_scratch_bytes": (_Z, [_I, _I]),
@@ -54,6 +55,8 @@ PROTOTYPES = {
     "jb200_moe_finalize": (_I, [_P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P]),
     "jb200_lsf_scan": (_I, [_P, _I, _P, _P, _P, _P, _F, _F, _P, _P, _P, _I, _P, _P, _I, _I, _I, _P]),
     "jb200_lsf_scan_scratch_bytes": (_Z, [_I, _I, _I]),
+    "jb200_lsf_step_norm": (_I, [_P, _P, _P, _P, _I, C.c_longlong, C.c_longlong, _F, _P, _P, _F, _F, _P, _P, _P, _P, _F, _P,
+                                 _I, _I, _P]),
     "jb200_peer_buffer_alloc": (_I, [_Z, _P, _P]),
     "jb200_peer_buffer_open": (_I, [_P, _P]),
     "jb200_peer_buffer_close": (_I, [_P]),
@@ -115,6 +118,11 @@ def device_status(clear: bool = True) -> int:
     st = C.c_uint(0)
     check(load().jb200_device_status(C.byref(st), 1 if clear else 0), "jb200_device_status")
     return int(st.value)
+
+
+def set_dependent_launch(enable: bool) -> bool:
+    """Programmatic dependent launch of the library's kernels on/off; returns the previous setting."""
+    return bool(load().jb200_set_dependent_launch(1 if enable else 0))
 
 
 def kernel_launches(reset: bool = False) -> int:

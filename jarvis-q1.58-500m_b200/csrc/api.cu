@@ -2,6 +2,7 @@
 // other translation units.  Also owns the per-thread error message, the device status word
 // that bounded waits report into, and the bounded-wait self test.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <atomic>
 #include <string.h>
 
@@ -20,6 +21,25 @@ std::atomic<long long> g_launches{0};
 }  // namespace
 
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+namespace {
+// -1: not read yet; the environment variable JB200_DEPENDENT_LAUNCH=0 turns the attribute off for a process
+std::atomic<int> g_dep_launch{-1};
+}  // namespace
+bool dependent_launch_enabled() {
+  int v = g_dep_launch.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = getenv("JB200_DEPENDENT_LAUNCH");
+    v = (e && e[0] == '0') ? 0 : 1;
+    g_dep_launch.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
+int set_dependent_launch(int on) {
+  const int before = dependent_launch_enabled() ? 1 : 0;
+  g_dep_launch.store(on ? 1 : 0, std::memory_order_relaxed);
+  return before;
+}
 
 void set_error(const char* fmt, ...) {
   va_list ap;
@@ -98,11 +118,13 @@ extern "C" {
 
 const char* jb200_last_error(void) { return g_err; }
 
-int jb200_abi_version(void) { return 10; }
+int jb200_abi_version(void) { return 11; }
 
 long long jb200_kernel_launches(int reset) {
   return reset ? g_launches.exchange(0) : g_launches.load();
 }
+
+int jb200_set_dependent_launch(int enable) { return jb::set_dependent_launch(enable); }
 
 int jb200_device_status(unsigned int* status, int clear) {
   JB_REQUIRE(status != nullptr, "device_status: null output pointer");
@@ -309,6 +331,15 @@ int jb200_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const f
 }
 
 size_t jb200_lsf_scan_scratch_bytes(int B, int T, int D) { return lsf_scan_scratch_bytes(B, T, D); }
+
+int jb200_lsf_step_norm(const void* m_bf16, const double* stats, const double* probs_sum, const int32_t* top1_hist,
+                        int E, long long n_tokens, long long n_elems, float balance_alpha, float* scalars,
+                        const float* var_scale, float alpha_min, float alpha_max, const float* h_in, float* h_out,
+                        float* x, const float* w_norm, float eps, void* xn_bf16, int B, int C, void* stream) {
+  return launch_lsf_step_norm(m_bf16, stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars,
+                              var_scale, alpha_min, alpha_max, h_in, h_out, x, w_norm, eps, xn_bf16, B, C,
+                              static_cast<cudaStream_t>(stream));
+}
 
 int jb200_prepare_weights(const uint8_t* packed, size_t n_bytes, uint8_t* prepared, void* stream) {
   return launch_prepare_weights(packed, n_bytes, prepared, static_cast<cudaStream_t>(stream));

@@ -156,8 +156,6 @@ attn_state_pass_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
   const int ck_begin = seg * p.seg_chunks;
   const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
   const int row0 = b * T;
-  const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
-  const float log_g = logf(__ldg(p.gamma + h));
 
   if (tid == 0) {
     mbar_init(smem_u32(&sm->full[0]), 1);
@@ -173,6 +171,10 @@ attn_state_pass_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_co
     tmem_alloc(smem_u32(&sm->tmem_base), STATE_TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_wait();        // everything above overlapped the kernel before this one; global memory is read from here on
+  pdl_trigger();
+  const int pos_base = p.pos0 ? p.pos0[b] : p.pos0_scalar;
+  const float log_g = logf(__ldg(p.gamma + h));
   for (int n = tid; n <= CH; n += STATE_THREADS) sm->pw[n] = expf(log_g * float(n));
   tc_fence_before_sync();
   __syncthreads();
@@ -380,7 +382,6 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
   const int n_loc = ck_end - ck_begin;
   const int row0 = b * T;
-  const float log_g = logf(__ldg(p.gamma + h));
 
   if (tid == 0) {
     for (int s = 0; s < NST; ++s) {
@@ -409,6 +410,9 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     tmem_alloc(smem_u32(&sm->tmem_base), PIPE_TMEM_COLS);
     tmem_relinquish();
   }
+  pdl_wait();        // everything above overlapped the kernel before this one; global memory is read from here on
+  pdl_trigger();
+  const float log_g = logf(__ldg(p.gamma + h));
   for (int n = tid; n <= CH; n += PIPE_THREADS) sm->pw[n] = expf(log_g * float(n));
   for (int n = tid; n < 2 * CH; n += PIPE_THREADS) {
     // gamma^(i-j) / sqrt(D): the 1/8 of the query feature map is a power of two, so applying it to the scores
@@ -815,6 +819,8 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 // One CTA per (head, sequence), 16 elements per thread.  The pieces are in the kernel's own column order
 // (interleaved when q/k were prepared); s_in / s_out use the natural one.
 __global__ void __launch_bounds__(256) attn_fold_states_kernel(const AttnParams p) {
+  pdl_wait();
+  pdl_trigger();
   const int h = blockIdx.x, b = blockIdx.y;
   const float log_g = logf(__ldg(p.gamma + h));
   const int L = p.seg_chunks * CH;
@@ -831,6 +837,12 @@ __global__ void __launch_bounds__(256) attn_fold_states_kernel(const AttnParams 
   }
 }
 
+// One element of the single-token state update, S' = gamma S + v k', with its roundings spelled out so that both
+// decode kernels below produce the same state bits.
+__device__ __forceinline__ float decode_update(float gamma, float s, float v, float k) {
+  return __fmaf_rn(gamma, s, __fmul_rn(v, k));
+}
+
 // One-token step (decode): S <- gamma*S + v (x) k', o = S q' for every (sequence, head).  Pure state
 // streaming: 2 x 16 KiB of fp32 state per (sequence, head) against 384 B of q, k, v, so the kernel is a
 // coalesced read-modify-write of S with the feature map + RoPE of the single token done in shared memory.
@@ -839,7 +851,16 @@ __global__ void __launch_bounds__(256)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                    const __nv_bfloat16* __restrict__ v, int ld_qkv, const AttnParams p) {
   __shared__ float sq[D], sk[D], sv[D], rq[D], rk[D];
+  pdl_wait();
+  pdl_trigger();
   const int h = blockIdx.x, b = blockIdx.y, t = threadIdx.x;
+  // the thread's 64 bytes of state first: they are in flight during the feature map of the token below
+  const int row = t >> 2, c0 = (t & 3) * 16;
+  const size_t so = (size_t(b) * p.H + h) * D * D + size_t(row) * D + c0;
+  float4 st[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    st[i] = p.s_in ? *reinterpret_cast<const float4*>(p.s_in + so + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
   const float gamma = __ldg(p.gamma + h);
   if (t < D) {
     const size_t off = size_t(b) * ld_qkv + h * D + t;
@@ -856,17 +877,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     rk[t] = sk[t] * c - sk[t + 32] * sn;  rk[t + 32] = sk[t + 32] * c + sk[t] * sn;
   }
   __syncthreads();
-  const int row = t >> 2, c0 = (t & 3) * 16;
-  const size_t so = (size_t(b) * p.H + h) * D * D + size_t(row) * D + c0;
   const float vr = sv[row];
   float acc = 0.f;
-  float4 st[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    st[i] = p.s_in ? *reinterpret_cast<const float4*>(p.s_in + so + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
     const int c = c0 + 4 * i;
-    st[i].x = gamma * st[i].x + vr * rk[c];      st[i].y = gamma * st[i].y + vr * rk[c + 1];
-    st[i].z = gamma * st[i].z + vr * rk[c + 2];  st[i].w = gamma * st[i].w + vr * rk[c + 3];
+    st[i].x = decode_update(gamma, st[i].x, vr, rk[c]);      st[i].y = decode_update(gamma, st[i].y, vr, rk[c + 1]);
+    st[i].z = decode_update(gamma, st[i].z, vr, rk[c + 2]);  st[i].w = decode_update(gamma, st[i].w, vr, rk[c + 3]);
     acc += st[i].x * rq[c] + st[i].y * rq[c + 1] + st[i].z * rq[c + 2] + st[i].w * rq[c + 3];
   }
   if (p.s_out) {
@@ -876,6 +893,113 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   acc += __shfl_xor_sync(0xffffffffu, acc, 1);
   acc += __shfl_xor_sync(0xffffffffu, acc, 2);
   if ((t & 3) == 0) p.o[size_t(b) * p.ld_o + h * D + row] = __float2bfloat16_rn(acc);
+}
+
+// The same step as a stream of 16 KiB state tiles through shared memory: a fixed grid of CTAs (two per SM), each
+// walking its share of the (sequence, head) pairs with four tiles in flight as untiled bulk copies (global -> shared
+// on an mbarrier, shared -> global as a bulk group), the update done in place in the tile.  Bytes in flight do not
+// depend on registers or on CTA turnover, which is what holds attn_decode_kernel at ~0.6 of the HBM peak.  Needs
+// both s_in and s_out (they may be the same buffer); the feature map of the NEXT pair's token is computed while the
+// current tile is awaited.  Thread t of 256: columns 32*((t>>3)&1) + 4*(t&7) .. +3 of rows 16*i + (t>>4), i = 0..3, so
+// a quarter-warp always touches 128 contiguous bytes of the tile (no bank conflicts).
+constexpr int DEC_STAGES = 4;
+constexpr int DEC_TILE_BYTES = D * D * 4;
+struct DecodeSmem {
+  float tile[DEC_STAGES][D * D];
+  uint64_t full[DEC_STAGES];
+  float rq[2][D], rk[2][D], sv[2][D];
+  uint32_t abort_flag;
+};
+constexpr size_t DEC_SMEM_BYTES = sizeof(DecodeSmem) + 128;
+
+__global__ void __launch_bounds__(256, 2)
+attn_decode_stream_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                          const __nv_bfloat16* __restrict__ v, int ld_qkv, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  DecodeSmem* sm = reinterpret_cast<DecodeSmem*>(smem_raw + (((raw_addr + 127u) & ~127u) - raw_addr));
+  const int t = threadIdx.x, lane = t & 31;
+  if (t == 0) {
+    for (int s = 0; s < DEC_STAGES; ++s) mbar_init(smem_u32(&sm->full[s]), 1);
+    sm->abort_flag = 0;
+    fence_mbar_init();
+  }
+  pdl_wait();
+  pdl_trigger();
+  __syncthreads();
+  volatile uint32_t* abort_flag = &sm->abort_flag;
+  const int n_units = p.B * p.H;
+  const int n_my = (n_units - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);   // units u = blockIdx.x + i * gridDim.x
+  auto unit_of = [&](int i) { return int(blockIdx.x) + i * int(gridDim.x); };
+  auto issue_load = [&](int i) {      // thread 0 only
+    const int s = i % DEC_STAGES;
+    mbar_arrive_expect_tx(smem_u32(&sm->full[s]), DEC_TILE_BYTES);
+    bulk_load_1d(smem_u32(sm->tile[s]), p.s_in + size_t(unit_of(i)) * D * D, DEC_TILE_BYTES, smem_u32(&sm->full[s]));
+  };
+  if (t == 0) {
+    for (int i = 0; i < DEC_STAGES && i < n_my; ++i) issue_load(i);
+  }
+  // feature map + RoPE of the token of unit i into buffer i & 1: threads 0..31 the q / k pairs (d, d + 32), 32..95 v
+  auto token_features = [&](int i) {
+    if (t >= 96) return;
+    const int u = unit_of(i), b = u / p.H, h = u - b * p.H, buf = i & 1;
+    const size_t off = size_t(b) * ld_qkv + h * D;
+    if (t < 32) {
+      const float q0 = elu1(__bfloat162float(q[off + t])) * 0.125f, q1 = elu1(__bfloat162float(q[off + t + 32])) * 0.125f;
+      const float k0 = elu1(__bfloat162float(k[off + t])), k1 = elu1(__bfloat162float(k[off + t + 32]));
+      int pos = p.pos0 ? p.pos0[b] : p.pos0_scalar;
+      pos = pos < 0 ? 0 : (pos >= p.n_pos ? p.n_pos - 1 : pos);
+      const float c = __ldg(p.cos_tab + size_t(pos) * 32 + t), sn = __ldg(p.sin_tab + size_t(pos) * 32 + t);
+      sm->rq[buf][t] = q0 * c - q1 * sn;  sm->rq[buf][t + 32] = q1 * c + q0 * sn;
+      sm->rk[buf][t] = k0 * c - k1 * sn;  sm->rk[buf][t + 32] = k1 * c + k0 * sn;
+    } else {
+      sm->sv[buf][t - 32] = __bfloat162float(v[off + t - 32]);
+    }
+  };
+  if (n_my > 0) token_features(0);
+  __syncthreads();
+  const int col0 = 32 * ((t >> 3) & 1) + 4 * (t & 7), r0 = t >> 4;
+  for (int i = 0; i < n_my; ++i) {
+    const int s = i % DEC_STAGES, buf = i & 1;
+    const int u = unit_of(i), b = u / p.H, h = u - b * p.H;
+    if (i + 1 < n_my) token_features(i + 1);          // its loads overlap the wait for this unit's tile
+    const float gamma = __ldg(p.gamma + h);
+    const float4 kq = *reinterpret_cast<const float4*>(&sm->rk[buf][col0]);
+    const float4 qq = *reinterpret_cast<const float4*>(&sm->rq[buf][col0]);
+    if (!mbar_wait(smem_u32(&sm->full[s]), uint32_t(i / DEC_STAGES) & 1u, abort_flag, p.status, JB200_STATUS_ATTN_LOAD)) break;
+    float acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = 16 * j + r0;
+      float4* cell = reinterpret_cast<float4*>(&sm->tile[s][row * D + col0]);
+      const float vr = sm->sv[buf][row];
+      float4 st = *cell;
+      st.x = decode_update(gamma, st.x, vr, kq.x);  st.y = decode_update(gamma, st.y, vr, kq.y);
+      st.z = decode_update(gamma, st.z, vr, kq.z);  st.w = decode_update(gamma, st.w, vr, kq.w);
+      *cell = st;
+      acc[j] = st.x * qq.x + st.y * qq.y + st.z * qq.z + st.w * qq.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int o = 1; o < 16; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    }
+    if ((lane & 15) == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) p.o[size_t(b) * p.ld_o + h * D + 16 * j + r0] = __float2bfloat16_rn(acc[j]);
+    }
+    fence_proxy_async_smem();      // the updated tile goes out through the async proxy
+    __syncthreads();               // tile complete; also orders this iteration's reads of rq/rk/sv before their reuse
+    if (t == 0) {
+      bulk_store_1d(p.s_out + size_t(u) * D * D, smem_u32(sm->tile[s]), DEC_TILE_BYTES);
+      bulk_commit_group();
+      if (i >= 1 && i - 1 + DEC_STAGES < n_my) {
+        bulk_wait_group_read<1>();   // the store of unit i - 1 has read its tile: the stage takes unit i - 1 + DEC_STAGES
+        issue_load(i - 1 + DEC_STAGES);
+      }
+    }
+  }
+  if (t == 0) bulk_wait_group<0>();
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -958,8 +1082,20 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
     dp.gamma = gamma; dp.cos_tab = cos_tab; dp.sin_tab = sin_tab; dp.pos0 = pos0; dp.pos0_scalar = pos0_scalar;
     dp.n_pos = n_pos; dp.s_in = s_in; dp.s_out = s_out; dp.o = reinterpret_cast<__nv_bfloat16*>(o); dp.ld_o = ld_o;
     dp.B = B; dp.T = 1; dp.H = H; dp.seg_chunks = 1; dp.nseg = 1; dp.seg_state = nullptr; dp.n_pieces = 0; dp.qk_prepared = 0;
-    dp.wide_store = 0; dp.status = nullptr;
-    attn_decode_kernel<<<dim3(H, B), 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(q),
+    dp.wide_store = 0; dp.status = device_status_ptr();
+    if (!dp.status) return JB200_ERR_CUDA;
+    if (s_in && s_out && B * H >= 64) {
+      // the state streams through shared memory as bulk copies: two CTAs per SM walk the (sequence, head) pairs
+      const int sms = sm_count();
+      if (sms <= 0) return JB200_ERR_CUDA;
+      JB_CUDA(cudaFuncSetAttribute(attn_decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(DEC_SMEM_BYTES)));
+      const int grid = B * H < 2 * sms ? B * H : 2 * sms;
+      launch_dep(attn_decode_stream_kernel, grid, 256, DEC_SMEM_BYTES, stream, reinterpret_cast<const __nv_bfloat16*>(q),
+                 reinterpret_cast<const __nv_bfloat16*>(k), reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
+      JB_LAUNCH_CHECK("attn_decode_stream_kernel");
+      return JB200_OK;
+    }
+    launch_dep(attn_decode_kernel, dim3(H, B), 256, 0, stream, reinterpret_cast<const __nv_bfloat16*>(q),
                                                         reinterpret_cast<const __nv_bfloat16*>(k),
                                                         reinterpret_cast<const __nv_bfloat16*>(v), ld_qkv, dp);
     JB_LAUNCH_CHECK("attn_decode_kernel");
@@ -991,19 +1127,19 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   if (!o) {
     // state only: the k/v pass over every piece, then the fold
     JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
-    attn_state_pass_kernel<<<dim3(H, B, p.nseg), STATE_THREADS, STATE_SMEM_BYTES, stream>>>(tk, tv, p);
+    launch_dep(attn_state_pass_kernel, dim3(H, B, p.nseg), STATE_THREADS, STATE_SMEM_BYTES, stream, tk, tv, p);
     JB_LAUNCH_CHECK("attn_state_pass_kernel");
-    attn_fold_states_kernel<<<dim3(H, B), 256, 0, stream>>>(p);
+    launch_dep(attn_fold_states_kernel, dim3(H, B), 256, 0, stream, p);
     JB_LAUNCH_CHECK("attn_fold_states_kernel");
     return JB200_OK;
   }
   JB_CUDA(cudaFuncSetAttribute(attn_scan_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(PIPE_SMEM_BYTES)));
   if (p.nseg > 1) {
     JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
-    attn_state_pass_kernel<<<dim3(H, B, p.nseg - 1), STATE_THREADS, STATE_SMEM_BYTES, stream>>>(tk, tv, p);
+    launch_dep(attn_state_pass_kernel, dim3(H, B, p.nseg - 1), STATE_THREADS, STATE_SMEM_BYTES, stream, tk, tv, p);
     JB_LAUNCH_CHECK("attn_state_pass_kernel");
   }
-  attn_scan_pipe_kernel<<<dim3(H, B, p.nseg), PIPE_THREADS, PIPE_SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  launch_dep(attn_scan_pipe_kernel, dim3(H, B, p.nseg), PIPE_THREADS, PIPE_SMEM_BYTES, stream, tq, tk, tv, p);
   JB_LAUNCH_CHECK("attn_scan_pipe_kernel");
   return JB200_OK;
 }

@@ -48,6 +48,8 @@ int cuda_fail(cudaError_t e, const char* what);
 unsigned int* device_status_ptr();  // device address, resolved once per device
 int sm_count();
 void count_launch();  // bumps the per-process kernel-launch counter (jb200_kernel_launches)
+int set_dependent_launch(int on);
+bool dependent_launch_enabled();  // programmatic dependent launch of the library's kernels (jb200_set_dependent_launch)
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -184,6 +186,14 @@ __device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, int c0, int 
                ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(src_smem)
                : "memory");
 }
+// Untiled bulk copies: both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until all but the newest `N` bulk groups of this thread have finished READING their shared-memory source.
 template <int N>
@@ -299,6 +309,33 @@ __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
+}
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the forward chain is launched with the stream-serialisation
+// attribute and starts with  pdl_wait(); pdl_trigger();  so its launch, CTA placement and whatever it does
+// before the wait (barrier / TMEM set-up, descriptor and L2 prefetches: nothing that reads or writes memory another
+// kernel produces) overlap the kernel before it.  The wait returns when the preceding kernel has completed and its
+// writes are visible; the trigger sits after the wait, so a kernel only ever overlaps its immediate predecessor,
+// which itself has passed its own wait: everything older has completed.  Both are no-ops in a kernel launched
+// without the attribute.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline void launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dependent_launch_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  (void)cudaLaunchKernelEx(&cfg, kernel, KArgs(static_cast<Args&&>(args))...);   // errors: cudaGetLastError in JB_LAUNCH_CHECK
 }
 
 #endif  // __CUDACC__

@@ -41,6 +41,8 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
 template <typename TIn, typename TOut, int MAXV>
 __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_kernel(const TIn* __restrict__ x, const float* __restrict__ w,
                                                               float eps, TOut* __restrict__ y, int n_rows, int C) {
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x * (ROW_THREADS / 32) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int lane = threadIdx.x & 31;
@@ -54,7 +56,7 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_kernel(const TIn* __restr
     if (c < C) {
       load8<TIn>(xr + c, v[i]);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      for (int j = 0; j < 8; ++j) ss = __fmaf_rn(v[i][j], v[i][j], ss);
     }
   }
   ss = warp_sum(ss);
@@ -75,6 +77,8 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_kernel(const TIn* __restr
 __global__ void __launch_bounds__(ROW_THREADS) embedding_kernel(const int64_t* __restrict__ idx,
                                                                 const float* __restrict__ table, int vocab,
                                                                 float* __restrict__ out, int n_rows, int C) {
+  pdl_wait();
+  pdl_trigger();
   const int row = blockIdx.x * (ROW_THREADS / 32) + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int lane = threadIdx.x & 31;
@@ -89,11 +93,11 @@ template <typename TIn, typename TOut>
 int launch_rmsnorm_t(const void* x, const float* w, float eps, void* y, int n_rows, int C, cudaStream_t stream) {
   const int blocks = (n_rows + ROW_THREADS / 32 - 1) / (ROW_THREADS / 32);
   if (C <= 1024)
-    rmsnorm_kernel<TIn, TOut, 4><<<blocks, ROW_THREADS, 0, stream>>>(
-        reinterpret_cast<const TIn*>(x), w, eps, reinterpret_cast<TOut*>(y), n_rows, C);
+    launch_dep(rmsnorm_kernel<TIn, TOut, 4>, blocks, ROW_THREADS, 0, stream, reinterpret_cast<const TIn*>(x), w, eps,
+               reinterpret_cast<TOut*>(y), n_rows, C);
   else
-    rmsnorm_kernel<TIn, TOut, 16><<<blocks, ROW_THREADS, 0, stream>>>(
-        reinterpret_cast<const TIn*>(x), w, eps, reinterpret_cast<TOut*>(y), n_rows, C);
+    launch_dep(rmsnorm_kernel<TIn, TOut, 16>, blocks, ROW_THREADS, 0, stream, reinterpret_cast<const TIn*>(x), w, eps,
+               reinterpret_cast<TOut*>(y), n_rows, C);
   JB_LAUNCH_CHECK("rmsnorm_kernel");
   return JB200_OK;
 }
@@ -124,7 +128,7 @@ int launch_embedding(const int64_t* idx, const float* table, int vocab, float* o
   JB_REQUIRE(aligned16(table) && aligned16(out), "embedding: pointers must be 16-byte aligned");
   if (n_rows == 0) return JB200_OK;
   const int blocks = (n_rows + ROW_THREADS / 32 - 1) / (ROW_THREADS / 32);
-  embedding_kernel<<<blocks, ROW_THREADS, 0, stream>>>(idx, table, vocab, out, n_rows, C);
+  launch_dep(embedding_kernel, blocks, ROW_THREADS, 0, stream, idx, table, vocab, out, n_rows, C);
   JB_LAUNCH_CHECK("embedding_kernel");
   return JB200_OK;
 }

@@ -56,6 +56,10 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
                     float* resid, void* out, int out_dtype, float* h_last, void* scratch, int B, int T, int D,
                     cudaStream_t stream);
 size_t lsf_scan_scratch_bytes(int B, int T, int D);
+int launch_lsf_step_norm(const void* m_bf16, const double* stats, const double* probs_sum, const int* top1_hist, int E,
+                         long long n_tokens, long long n_elems, float balance_alpha, float* scalars,
+                         const float* var_scale, float alpha_min, float alpha_max, const float* h_in, float* h_out,
+                         float* x, const float* w_norm, float eps, void* xn_bf16, int B, int C, cudaStream_t stream);
 
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
                      const float* cos_tab, const float* sin_tab, int n_pos, const int32_t* pos0, int pos0_scalar,

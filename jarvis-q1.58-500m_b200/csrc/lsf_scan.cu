@@ -26,6 +26,7 @@
 // no longer depend on how many registers a thread can spare for outstanding loads.
 #include "common.cuh"
 #include "gemm_shared.cuh"
+#include "moe_finalize.cuh"
 #include "launchers.h"
 
 namespace jb {
@@ -74,6 +75,8 @@ __device__ __forceinline__ void st2<__nv_bfloat16>(__nv_bfloat16* p, float a, fl
 
 template <bool TENSOR_ALPHA, typename TM, typename TOut, int TPW, bool ENDS_ONLY>
 __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_kernel(const LsfParams p) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float2 s_end[2][LSF_WARPS][32];   // end value of each warp's run
   __shared__ float2 s_prod[2][LSF_WARPS][32];  // product of decays over the run (tensor mode)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -210,6 +213,8 @@ __global__ void __launch_bounds__(LSF_THREADS, TENSOR_ALPHA ? 1 : 2) lsf_scan_ke
 // Short sequences (decode steps): one thread per channel pair walks the few tokens itself.
 template <bool TENSOR_ALPHA, typename TM, typename TOut>
 __global__ void __launch_bounds__(256) lsf_short_kernel(const LsfParams p) {
+  pdl_wait();
+  pdl_trigger();
   const size_t pair = size_t(blockIdx.x) * 256 + threadIdx.x;
   const int half_d = p.D / 2;
   if (pair >= size_t(p.B) * half_d) return;
@@ -220,7 +225,7 @@ __global__ void __launch_bounds__(256) lsf_short_kernel(const LsfParams p) {
   float alpha = 0.f;
   if (!TENSOR_ALPHA) {
     if (p.alpha_s) alpha = __ldg(p.alpha_s);
-    else alpha = p.alpha_min + (p.alpha_max - p.alpha_min) * (1.0f / (1.0f + expf(__ldg(p.var_scale) * __ldg(p.act_var))));
+    else alpha = lsf_alpha_from_var(p.alpha_min, p.alpha_max, __ldg(p.var_scale), __ldg(p.act_var));
   }
   float2 h = p.h0 ? *reinterpret_cast<const float2*>(p.h0 + size_t(b) * p.D + ch) : make_float2(0.f, 0.f);
   for (int t = 0; t < p.T; ++t) {
@@ -228,8 +233,8 @@ __global__ void __launch_bounds__(256) lsf_short_kernel(const LsfParams p) {
     const float2 mv = ld2<TM>(m + o);
     float2 a = make_float2(alpha, alpha);
     if (TENSOR_ALPHA) a = ld2<TM>(at + o);
-    h.x = a.x * h.x + (1.0f - a.x) * mv.x;
-    h.y = a.y * h.y + (1.0f - a.y) * mv.y;
+    h.x = lsf_step(a.x, h.x, mv.x);
+    h.y = lsf_step(a.y, h.y, mv.y);
     if (out) st2<TOut>(out + o, h.x, h.y);
     if (p.resid) {
       float2* r = reinterpret_cast<float2*>(p.resid + o);
@@ -240,6 +245,86 @@ __global__ void __launch_bounds__(256) lsf_short_kernel(const LsfParams p) {
   if (p.h_last) *reinterpret_cast<float2*>(p.h_last + size_t(b) * p.D + ch) = h;
 }
 
+// Single-token tail of a block (decode steps), three launches in one: the MoE layer's scalars from its accumulated
+// statistics (moe_finalize_kernel), the LSF step with the fused residual (lsf_short_kernel at T = 1: the decay comes
+// from act_var, h <- alpha h + (1 - alpha) m, x += h) and the RMSNorm that follows (norm1 of the next block or the
+// final norm; rmsnorm_kernel<float, bf16>).  One warp per sequence, lanes on the channels of rmsnorm_kernel with its
+// summation order, every rounding as in the three kernels: the results are theirs bit for bit.
+struct LsfStepParams {
+  const __nv_bfloat16* m;      // [B][C] MoE output
+  const double* stats;         // [2] sum, sum of squares of the MoE output
+  const double* probs_sum;     // [E] or null
+  const int* top1_hist;        // [E] or null
+  int E;
+  long long n_tokens, n_elems;
+  float balance_alpha;
+  float* scalars;              // [3] out: l_balance, act_mean, act_var
+  const float* var_scale;
+  float alpha_min, alpha_max;
+  const float* h_in;           // [B][C] or null (zero membrane)
+  float* h_out;                // [B][C] (may alias h_in)
+  float* x;                    // [B][C] residual stream, in/out
+  const float* w_norm;         // [C] or null: no norm wanted
+  float eps;
+  __nv_bfloat16* xn;           // [B][C] out (with w_norm)
+  int B, C;
+};
+
+__global__ void __launch_bounds__(256) lsf_step_norm_kernel(const LsfStepParams p) {
+  pdl_wait();
+  pdl_trigger();
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    moe_finalize_scalars(p.stats, p.probs_sum, p.top1_hist, p.E, p.n_tokens, p.n_elems, p.balance_alpha, p.scalars);
+  const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= p.B) return;
+  const float alpha = lsf_alpha_from_var(p.alpha_min, p.alpha_max, __ldg(p.var_scale), moe_act_var(p.stats, p.n_elems));
+  const size_t base = size_t(row) * p.C;
+  float v[4][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < p.C) {
+      const uint4 mw = __ldg(reinterpret_cast<const uint4*>(p.m + base + c));
+      const float mv[8] = {bf16_lo(mw.x), bf16_hi(mw.x), bf16_lo(mw.y), bf16_hi(mw.y),
+                           bf16_lo(mw.z), bf16_hi(mw.z), bf16_lo(mw.w), bf16_hi(mw.w)};
+      float h[8];
+      if (p.h_in) {
+        const float4 a = *reinterpret_cast<const float4*>(p.h_in + base + c), b = *reinterpret_cast<const float4*>(p.h_in + base + c + 4);
+        h[0] = a.x; h[1] = a.y; h[2] = a.z; h[3] = a.w; h[4] = b.x; h[5] = b.y; h[6] = b.z; h[7] = b.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = 0.f;
+      }
+      const float4 xa = *reinterpret_cast<const float4*>(p.x + base + c), xb = *reinterpret_cast<const float4*>(p.x + base + c + 4);
+      const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        h[j] = lsf_step(alpha, h[j], mv[j]);
+        v[i][j] = xv[j] + h[j];
+        ss = __fmaf_rn(v[i][j], v[i][j], ss);
+      }
+      *reinterpret_cast<float4*>(p.h_out + base + c) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(p.h_out + base + c + 4) = make_float4(h[4], h[5], h[6], h[7]);
+      *reinterpret_cast<float4*>(p.x + base + c) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      *reinterpret_cast<float4*>(p.x + base + c + 4) = make_float4(v[i][4], v[i][5], v[i][6], v[i][7]);
+    }
+  }
+  if (!p.w_norm) return;
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / float(p.C) + p.eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < p.C) {
+      const float4 wa = __ldg(reinterpret_cast<const float4*>(p.w_norm + c)), wb = __ldg(reinterpret_cast<const float4*>(p.w_norm + c + 4));
+      *reinterpret_cast<uint4*>(p.xn + base + c) =
+          make_uint4(pack_bf16x2(v[i][0] * r * wa.x, v[i][1] * r * wa.y), pack_bf16x2(v[i][2] * r * wa.z, v[i][3] * r * wa.w),
+                     pack_bf16x2(v[i][4] * r * wb.x, v[i][5] * r * wb.y), pack_bf16x2(v[i][6] * r * wb.z, v[i][7] * r * wb.w));
+    }
+  }
+}
+
 constexpr int LSF_TPW = 16;                       // tokens per warp per tile
 constexpr int LSF_TILE = LSF_WARPS * LSF_TPW;     // 128 tokens
 
@@ -247,17 +332,17 @@ template <bool TA, typename TM, typename TOut>
 int launch_t(const LsfParams& p, cudaStream_t stream) {
   if (p.T <= 8) {
     const size_t pairs = size_t(p.B) * (p.D / 2);
-    lsf_short_kernel<TA, TM, TOut><<<unsigned((pairs + 255) / 256), 256, 0, stream>>>(p);
+    launch_dep(lsf_short_kernel<TA, TM, TOut>, unsigned((pairs + 255) / 256), 256, 0, stream, p);
     JB_LAUNCH_CHECK("lsf_short_kernel");
     return JB200_OK;
   }
   if (p.nseg > 1) {
     dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.n_pre_tiles);
-    lsf_scan_kernel<TA, TM, TOut, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);
+    launch_dep(lsf_scan_kernel<TA, TM, TOut, LSF_TPW, true>, grid_a, LSF_THREADS, 0, stream, p);
     JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
   }
   dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
-  lsf_scan_kernel<TA, TM, TOut, LSF_TPW, false><<<grid, LSF_THREADS, 0, stream>>>(p);
+  launch_dep(lsf_scan_kernel<TA, TM, TOut, LSF_TPW, false>, grid, LSF_THREADS, 0, stream, p);
   JB_LAUNCH_CHECK("lsf_scan_kernel");
   return JB200_OK;
 }
@@ -287,6 +372,8 @@ template <bool FUSED>
 __global__ void __launch_bounds__(LSF_THREADS, FUSED ? 2 : 3)
 lsf_tma_kernel(const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_io, const LsfParams p,
                const int n_stages, unsigned int* status) {
+  pdl_wait();
+  pdl_trigger();
   using Cfg = LsfTma<FUSED>;
   constexpr int TPW = 16;
   extern __shared__ uint8_t lsf_smem_raw[];
@@ -454,13 +541,13 @@ int launch_tma(LsfParams p, cudaStream_t stream) {
   if (!status) return JB200_ERR_CUDA;
   if (p.nseg > 1) {
     dim3 grid_a((p.D + LSF_CH - 1) / LSF_CH, p.B, p.n_pre_tiles);
-    lsf_scan_kernel<false, __nv_bfloat16, __nv_bfloat16, LSF_TPW, true><<<grid_a, LSF_THREADS, 0, stream>>>(p);
+    launch_dep(lsf_scan_kernel<false, __nv_bfloat16, __nv_bfloat16, LSF_TPW, true>, grid_a, LSF_THREADS, 0, stream, p);
     JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
   }
   JB_CUDA(cudaFuncSetAttribute(lsf_tma_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(Cfg::smem_bytes(Cfg::STAGES_ALONE))));
   dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
-  lsf_tma_kernel<FUSED><<<grid, LSF_THREADS, Cfg::smem_bytes(stages), stream>>>(tm_m, tm_io, p, stages, status);
+  launch_dep(lsf_tma_kernel<FUSED>, grid, LSF_THREADS, Cfg::smem_bytes(stages), stream, tm_m, tm_io, p, stages, status);
   JB_LAUNCH_CHECK("lsf_tma_kernel");
   return JB200_OK;
 }
@@ -542,6 +629,32 @@ int launch_lsf_scan(const void* m, int m_dtype, const void* alpha_tensor, const 
   if (m_dtype == 1 && out_dtype == 0) return launch_t<true, bf, float>(p, stream);
   if (m_dtype == 0 && out_dtype == 0) return launch_t<true, float, float>(p, stream);
   return launch_t<true, float, bf>(p, stream);
+}
+
+int launch_lsf_step_norm(const void* m_bf16, const double* stats, const double* probs_sum, const int* top1_hist, int E,
+                         long long n_tokens, long long n_elems, float balance_alpha, float* scalars,
+                         const float* var_scale, float alpha_min, float alpha_max, const float* h_in, float* h_out,
+                         float* x, const float* w_norm, float eps, void* xn_bf16, int B, int C, cudaStream_t stream) {
+  JB_REQUIRE(B >= 0 && C > 0, "lsf_step_norm: bad shape (%d, %d)", B, C);
+  JB_REQUIRE(C % 8 == 0 && C <= 1024, "lsf_step_norm: d_model (%d) must be a multiple of 8 and at most 1024", C);
+  JB_REQUIRE(E >= 0 && E <= 64 && n_tokens > 0 && n_elems > 0, "lsf_step_norm: bad counts");
+  if (B == 0) return JB200_OK;
+  JB_REQUIRE(m_bf16 && stats && scalars && var_scale && h_out && x, "lsf_step_norm: null pointer");
+  JB_REQUIRE((w_norm == nullptr) == (xn_bf16 == nullptr), "lsf_step_norm: norm weight and normalised output come together");
+  JB_REQUIRE(aligned16(m_bf16) && aligned16(h_out) && aligned16(x) && (!h_in || aligned16(h_in)) &&
+                 (!w_norm || (aligned16(w_norm) && aligned16(xn_bf16))),
+             "lsf_step_norm: pointers must be 16-byte aligned");
+  LsfStepParams p;
+  p.m = reinterpret_cast<const __nv_bfloat16*>(m_bf16);
+  p.stats = stats; p.probs_sum = probs_sum; p.top1_hist = top1_hist; p.E = E;
+  p.n_tokens = n_tokens; p.n_elems = n_elems; p.balance_alpha = balance_alpha; p.scalars = scalars;
+  p.var_scale = var_scale; p.alpha_min = alpha_min; p.alpha_max = alpha_max;
+  p.h_in = h_in; p.h_out = h_out; p.x = x; p.w_norm = w_norm; p.eps = eps;
+  p.xn = reinterpret_cast<__nv_bfloat16*>(xn_bf16);
+  p.B = B; p.C = C;
+  launch_dep(lsf_step_norm_kernel, (B + 7) / 8, 256, 0, stream, p);
+  JB_LAUNCH_CHECK("lsf_step_norm_kernel");
+  return JB200_OK;
 }
 
 }  // namespace jb

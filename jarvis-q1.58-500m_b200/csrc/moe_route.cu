@@ -13,6 +13,7 @@
 // ballot-ranked scatter.  The order is a pure function of the ids and is bit-exact.
 // All of it is HBM/latency-bound integer and copy work: no tensor cores.
 #include "common.cuh"
+#include "moe_finalize.cuh"
 #include "launchers.h"
 
 namespace jb {
@@ -90,6 +91,8 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
                    int tokens_per_cta,
                    int64_t* __restrict__ topk_idx, float* __restrict__ gates, float* __restrict__ probs_out,
                    double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float w_s[];  // [E][C]
   __shared__ float p_acc[ROUTER_THREADS / 32][E];
   __shared__ int h_acc[E];
@@ -141,6 +144,8 @@ rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_n
                       __nv_bfloat16* __restrict__ xn, const float* __restrict__ w_router, int n_tokens, int C,
                       int tokens_per_cta, int64_t* __restrict__ topk_idx, float* __restrict__ gates,
                       double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
+  pdl_wait();
+  pdl_trigger();
   extern __shared__ float w_s[];  // [E][C]
   __shared__ float p_acc[ROUTER_THREADS / 32][E];
   __shared__ int h_acc[E];
@@ -214,6 +219,8 @@ __device__ __forceinline__ int clamp_expert(long long e, int E) { return e < 0 ?
 
 __global__ void __launch_bounds__(META_CHUNK)
 meta_hist_kernel(const int64_t* __restrict__ flat_idx, int M, int E, int* __restrict__ chunk_counts) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int h[MAX_E];
   if (threadIdx.x < MAX_E) h[threadIdx.x] = 0;
   __syncthreads();
@@ -228,6 +235,8 @@ meta_hist_kernel(const int64_t* __restrict__ flat_idx, int M, int E, int* __rest
 __global__ void __launch_bounds__(32 * MAX_E)
 meta_scan_kernel(const int* __restrict__ chunk_counts, int n_chunks, int E, int* __restrict__ chunk_base,
                  int* __restrict__ expert_counts, int* __restrict__ expert_offsets) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int totals[MAX_E];
   __shared__ int offs[MAX_E + 1];
   const int e = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -265,6 +274,8 @@ meta_scan_kernel(const int* __restrict__ chunk_counts, int n_chunks, int E, int*
 __global__ void __launch_bounds__(META_CHUNK)
 meta_assign_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, const int* __restrict__ chunk_base,
                    int* __restrict__ scatter_map, int* __restrict__ gather_map, int* __restrict__ gate_idx_map) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int warp_cnt[META_CHUNK / 32][MAX_E];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m = blockIdx.x * META_CHUNK + threadIdx.x;
@@ -293,6 +304,8 @@ __global__ void __launch_bounds__(META_SMALL_MAX)
 meta_small_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, int* __restrict__ expert_counts,
                   int* __restrict__ expert_offsets, int* __restrict__ scatter_map, int* __restrict__ gather_map,
                   int* __restrict__ gate_idx_map) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ int warp_cnt[META_SMALL_MAX / 32][MAX_E];
   __shared__ int offs[MAX_E + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -336,6 +349,8 @@ meta_small_kernel(const int64_t* __restrict__ flat_idx, int M, int K, int E, int
 __global__ void __launch_bounds__(256)
 dispatch_gather_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ gather_map, int M, int n_tokens,
                        int C, __nv_bfloat16* __restrict__ dispatched) {
+  pdl_wait();
+  pdl_trigger();
   const int slot = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (slot >= M) return;
   const int lane = threadIdx.x & 31;
@@ -351,6 +366,8 @@ __global__ void __launch_bounds__(256)
 scatter_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ gates,
                        const int* __restrict__ scatter_map, int n_tokens, int K, int M, int C,
                        TOut* __restrict__ out, double* __restrict__ stats) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ float red[2][8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * 8 + warp;
@@ -397,20 +414,10 @@ scatter_combine_kernel(const __nv_bfloat16* __restrict__ y, const float* __restr
 __global__ void moe_finalize_kernel(const double* __restrict__ stats, const double* __restrict__ probs_sum,
                                     const int* __restrict__ top1_hist, int E, long long n_tokens, long long n_elems,
                                     float balance_alpha, float* __restrict__ scalars) {
+  pdl_wait();
+  pdl_trigger();
   if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  if (probs_sum && top1_hist) {
-    double acc = 0.0;
-    for (int e = 0; e < E; ++e)
-      acc += (double(top1_hist[e]) / double(n_tokens)) * (probs_sum[e] / double(n_tokens));
-    scalars[0] = float(double(balance_alpha) * double(E) * acc);
-  }
-  if (stats) {
-    const double mean = stats[0] / double(n_elems);
-    // torch.var of a single element is NaN; keep that
-    const double var = (stats[1] - stats[0] * mean) / double(n_elems - 1);
-    scalars[1] = float(mean);
-    scalars[2] = n_elems > 1 ? float(var > 0.0 ? var : 0.0) : __int_as_float(0x7fc00000);
-  }
+  moe_finalize_scalars(stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars);
 }
 
 }  // namespace
@@ -430,12 +437,12 @@ int launch_router_top2(const void* x_bf16, const float* w_router, int n_tokens, 
   const size_t smem = size_t(E) * C * sizeof(float);
   if (E == 4) {
     JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    router_top2_kernel<4><<<blocks, ROUTER_THREADS, smem, stream>>>(
+    launch_dep(router_top2_kernel<4>, blocks, ROUTER_THREADS, smem, stream,
         reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, tpc, topk_idx, gates, probs_out, probs_sum,
         top1_hist);
   } else {
     JB_CUDA(cudaFuncSetAttribute(router_top2_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    router_top2_kernel<8><<<blocks, ROUTER_THREADS, smem, stream>>>(
+    launch_dep(router_top2_kernel<8>, blocks, ROUTER_THREADS, smem, stream,
         reinterpret_cast<const __nv_bfloat16*>(x_bf16), w_router, n_tokens, C, tpc, topk_idx, gates, probs_out, probs_sum,
         top1_hist);
   }
@@ -459,10 +466,10 @@ int launch_rmsnorm_router(const float* x, const float* w_norm, float eps, void* 
   const size_t smem = size_t(E) * C * sizeof(float);
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(xn_bf16);
   if (E == 4)
-    rmsnorm_router_kernel<4><<<blocks, ROUTER_THREADS, smem, stream>>>(x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
+    launch_dep(rmsnorm_router_kernel<4>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
                                                                        topk_idx, gates, probs_sum, top1_hist);
   else
-    rmsnorm_router_kernel<8><<<blocks, ROUTER_THREADS, smem, stream>>>(x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
+    launch_dep(rmsnorm_router_kernel<8>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
                                                                        topk_idx, gates, probs_sum, top1_hist);
   JB_LAUNCH_CHECK("rmsnorm_router_kernel");
   return JB200_OK;
@@ -484,7 +491,7 @@ int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int
   const int chunks = (M + META_CHUNK - 1) / META_CHUNK;
   JB_REQUIRE(M == 0 || (topk_idx && scatter_map && gather_map && gate_idx_map && scratch), "moe_metadata: null pointer");
   if (M > 0 && M <= META_SMALL_MAX) {
-    meta_small_kernel<<<1, (M + 31) / 32 * 32, 0, stream>>>(topk_idx, M, K, E, expert_counts, expert_offsets, scatter_map,
+    launch_dep(meta_small_kernel, 1, (M + 31) / 32 * 32, 0, stream, topk_idx, M, K, E, expert_counts, expert_offsets, scatter_map,
                                                             gather_map, gate_idx_map);
     JB_LAUNCH_CHECK("meta_small_kernel");
     return JB200_OK;
@@ -492,13 +499,13 @@ int launch_moe_metadata(const int64_t* topk_idx, int n_tokens, int K, int E, int
   int* chunk_counts = reinterpret_cast<int*>(scratch);
   int* chunk_base = chunk_counts + size_t(chunks) * E;
   if (M > 0) {
-    meta_hist_kernel<<<chunks, META_CHUNK, 0, stream>>>(topk_idx, M, E, chunk_counts);
+    launch_dep(meta_hist_kernel, chunks, META_CHUNK, 0, stream, topk_idx, M, E, chunk_counts);
     JB_LAUNCH_CHECK("meta_hist_kernel");
   }
-  meta_scan_kernel<<<1, 32 * MAX_E, 0, stream>>>(chunk_counts, chunks, E, chunk_base, expert_counts, expert_offsets);
+  launch_dep(meta_scan_kernel, 1, 32 * MAX_E, 0, stream, chunk_counts, chunks, E, chunk_base, expert_counts, expert_offsets);
   JB_LAUNCH_CHECK("meta_scan_kernel");
   if (M > 0) {
-    meta_assign_kernel<<<chunks, META_CHUNK, 0, stream>>>(topk_idx, M, K, E, chunk_base, scatter_map, gather_map,
+    launch_dep(meta_assign_kernel, chunks, META_CHUNK, 0, stream, topk_idx, M, K, E, chunk_base, scatter_map, gather_map,
                                                           gate_idx_map);
     JB_LAUNCH_CHECK("meta_assign_kernel");
   }
@@ -546,7 +553,7 @@ int launch_dispatch_gather(const void* x_bf16, const int* gather_map, int M, int
   if (M == 0) return JB200_OK;
   JB_REQUIRE(n_tokens > 0 && x_bf16 && gather_map && dispatched, "dispatch_gather: null pointer");
   JB_REQUIRE(aligned16(x_bf16) && aligned16(dispatched), "dispatch_gather: pointers must be 16-byte aligned");
-  dispatch_gather_kernel<<<(M + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16), gather_map, M,
+  launch_dep(dispatch_gather_kernel, (M + 7) / 8, 256, 0, stream, reinterpret_cast<const __nv_bfloat16*>(x_bf16), gather_map, M,
                                                           n_tokens, C, reinterpret_cast<__nv_bfloat16*>(dispatched));
   JB_LAUNCH_CHECK("dispatch_gather_kernel");
   return JB200_OK;
@@ -562,11 +569,11 @@ int launch_scatter_combine(const void* y_bf16, const float* gates, const int* sc
   const int blocks = (n_tokens + 7) / 8;
   const int M = n_tokens * K;
   if (out_dtype == 1)
-    scatter_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+    launch_dep(scatter_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream,
         reinterpret_cast<const __nv_bfloat16*>(y_bf16), gates, scatter_map, n_tokens, K, M, C,
         reinterpret_cast<__nv_bfloat16*>(out), stats);
   else
-    scatter_combine_kernel<float><<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(y_bf16), gates,
+    launch_dep(scatter_combine_kernel<float>, blocks, 256, 0, stream, reinterpret_cast<const __nv_bfloat16*>(y_bf16), gates,
                                                               scatter_map, n_tokens, K, M, C,
                                                               reinterpret_cast<float*>(out), stats);
   JB_LAUNCH_CHECK("scatter_combine_kernel");
@@ -577,7 +584,7 @@ int launch_moe_finalize(const double* stats, const double* probs_sum, const int*
                         long long n_elems, float balance_alpha, float* scalars, cudaStream_t stream) {
   JB_REQUIRE(scalars != nullptr, "moe_finalize: null output");
   JB_REQUIRE(n_tokens > 0 && n_elems > 0, "moe_finalize: empty batch");
-  moe_finalize_kernel<<<1, 32, 0, stream>>>(stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars);
+  launch_dep(moe_finalize_kernel, 1, 32, 0, stream, stats, probs_sum, top1_hist, E, n_tokens, n_elems, balance_alpha, scalars);
   JB_LAUNCH_CHECK("moe_finalize_kernel");
   return JB200_OK;
 }

@@ -56,6 +56,8 @@ template <typename T>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const T* __restrict__ logits, int ld, int V, float temperature, int top_k, float top_p,
               const float* __restrict__ u, int64_t* __restrict__ out_token, float* __restrict__ out_prob) {
+  pdl_wait();
+  pdl_trigger();
   __shared__ SampleSmem sm;
   const int row_i = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T* row = logits + size_t(row_i) * ld;
@@ -220,10 +222,10 @@ int launch_sample(const void* logits, int logits_dtype, int ld, int n_rows, int 
   JB_REQUIRE(greedy || (top_p > 0.f && top_p <= 1.f) || top_p <= 0.f, "sample: top_p out of range");
   if (n_rows == 0) return JB200_OK;
   if (logits_dtype == 0)
-    sample_kernel<float><<<n_rows, SAMPLE_THREADS, 0, stream>>>(reinterpret_cast<const float*>(logits), ld, V,
+    launch_dep(sample_kernel<float>, n_rows, SAMPLE_THREADS, 0, stream, reinterpret_cast<const float*>(logits), ld, V,
                                                                 temperature, top_k, top_p, u, out_token, out_prob);
   else
-    sample_kernel<__nv_bfloat16><<<n_rows, SAMPLE_THREADS, 0, stream>>>(
+    launch_dep(sample_kernel<__nv_bfloat16>, n_rows, SAMPLE_THREADS, 0, stream, 
         reinterpret_cast<const __nv_bfloat16*>(logits), ld, V, temperature, top_k, top_p, u, out_token, out_prob);
   JB_LAUNCH_CHECK("sample_kernel");
   return JB200_OK;

@@ -131,19 +131,26 @@ ternary_gemm_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_con
       mbar_init(smem_u32(&ctl->tmem_empty[a]), 256);
     }
     ctl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_x);
+    if (dense_w) tma_prefetch_desc(&tmap_w);
+  }
+  if (warp == 0) {
+    __syncwarp();                 // tcgen05.alloc is warp-collective: lane 0 rejoins from the barrier set-up first
+    tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  // The set-up above overlaps the tail of the kernel before this one on the stream; nothing before this line reads
+  // or writes global memory.
+  pdl_wait();
+  pdl_trigger();
+  if (threadIdx.x == 0) {
     if (p.seg_offsets) {
       for (int g = 0; g <= p.G; ++g) ctl->seg[g] = min(max(p.seg_offsets[g], 0), p.M);
     } else {
       ctl->seg[0] = 0;
       ctl->seg[1] = p.M;
     }
-    fence_mbar_init();
-    tma_prefetch_desc(&tmap_x);
-    if (dense_w) tma_prefetch_desc(&tmap_w);
-  }
-  if (warp == 0) {
-    tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
-    tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -415,7 +422,7 @@ int launch_ternary_gemm(const void* x_bf16, int M, int K, const uint8_t* w_packe
   JB_CUDA(cudaFuncSetAttribute(ternary_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(SMEM_BYTES_RESID)));
   const long max_tiles = long((M + bn - 1) / bn + (G - 1)) * n_ft;
   const int grid = int(max_tiles < sms ? max_tiles : sms);
-  ternary_gemm_kernel<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmap, tmap_w, tmap_out, p);
+  launch_dep(ternary_gemm_kernel, grid, NUM_THREADS, smem_bytes, stream, tmap, tmap_w, tmap_out, p);
   JB_LAUNCH_CHECK("ternary_gemm_kernel");
   return JB200_OK;
 }

@@ -43,7 +43,8 @@ def timeit(fn, iters, flush=True):
     total = 0.0
     for _ in range(iters):
         if flush:
-            scratch.fill_(1)
+            scratch.fill_(1)     # twice: ~90 us of device work, so the host has queued the launch
+            scratch.fill_(2)     # (allocations, tensor maps, ctypes) before the device reaches it
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()

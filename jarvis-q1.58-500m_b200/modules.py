@@ -264,10 +264,13 @@ class SparseMoELayer(nn.Module):
         return (self._p1.get([m.weight for m in self.w1], stack=True),
                 self._p2.get([m.weight for m in self.w2], stack=True))
 
-    def run_rows(self, xn_rows, out_dtype=torch.bfloat16, acc=None, hist=None, scalars=None, norm=None):
+    def run_rows(self, xn_rows, out_dtype=torch.bfloat16, acc=None, hist=None, scalars=None, norm=None,
+                 finalize=True):
         """xn_rows: bf16 (N, C) -> (out (N, C), scalars f32 [l_balance, act_mean, act_var]).
         acc (f64 (2+E,)), hist (i32 (E,)) and scalars (f32 (3,)) may be passed in pre-zeroed (a model
-        zeroes one block of them per forward instead of three small fills per layer)."""
+        zeroes one block of them per forward instead of three small fills per layer).
+        finalize=False (acc and hist passed in): the scalars are left to the caller's fused tail kernel and the
+        second return value is the token count they are to be derived with."""
         if self.training:
             raise RuntimeError("SparseMoELayer (sm_100a): inference only; call .eval() first")
         N, C = xn_rows.shape
@@ -313,8 +316,10 @@ class SparseMoELayer(nn.Module):
             acc.copy_(both[:2 + E])
             hist.copy_(both[2 + E:2 + 2 * E].to(torch.int32))
             n_total = int(both[-1].item()) if self._n_total_hint is None else self._n_total_hint
-        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, n_total, n_total * C, self.balance_alpha, scalars=scalars)
         self.last_routing = (idx, gates, meta)
+        if not finalize:
+            return out, n_total
+        scalars = ops.moe_finalize(acc[:2], acc[2:], hist, E, n_total, n_total * C, self.balance_alpha, scalars=scalars)
         return out, scalars
 
     def forward(self, x):
@@ -450,6 +455,27 @@ class JarvisBlock(nn.Module):
         # x += lsf(moe(norm2(x)))
         return h_last, scalars, state
 
+    def step_rows(self, x, xn, B, h_prev, positions, attn_state, inplace_state, scratch, next_norm):
+        """One token per sequence (decode): x f32 (B, C) residual stream, UPDATED IN PLACE; xn bf16 (B, C) =
+        norm1(x), from the caller (the tail kernel of the block before this one made it).  The tail of the block
+        is ONE launch: the MoE scalars, the LSF step with the residual add, and the RMSNorm `next_norm` =
+        (weight, eps) of whatever follows (the next block's norm1 or the model's final norm).
+        Returns (h_last, scalars, attention state, normalised rows for the next consumer)."""
+        C = x.shape[1]
+        o, state = self.attn.scan_rows(xn, B, 1, positions, attn_state, True, inplace_state)
+        po, ao = self.attn.out_proj.packed()
+        ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)
+        acc, hist, scalars = scratch
+        moe, lq = self.moe, self.liquid
+        moe_out, n_total = moe.run_rows(x, acc=acc, hist=hist, norm=(self.norm2.weight.detach().float(), self.norm2.eps),
+                                        finalize=False)
+        xn_next, h_last = ops.lsf_step_norm(
+            moe_out, acc[:2], acc[2:], hist, moe.num_experts, n_total, n_total * C, moe.balance_alpha, scalars,
+            lq.var_scale.detach().float().reshape(1), lq.alpha_min, lq.alpha_max,
+            None if h_prev is None else h_prev.float().contiguous(), x, norm=next_norm,
+            h_out=h_prev if (inplace_state and h_prev is not None and h_prev.dtype == torch.float32) else None)
+        return h_last, scalars, state, xn_next
+
     def forward(self, x, h_prev=None, start_pos: int = 0):
         B, T, C = x.shape
         rows = x.reshape(B * T, C).float().clone()
@@ -573,13 +599,25 @@ class Jarvis(nn.Module):
         Ss = state["S"] if state is not None else [None] * n
         new_h, new_s = [], []
         scratch = self._layer_scratch(x.device)
-        for i, block in enumerate(self.blocks):
-            block.attn.max_position = max_position
-            h_last, _, S = block.forward_rows(x, B, T, hs[i], pos, Ss[i], want_attn_state=True,
-                                              inplace_state=inplace and state is not None, scratch=scratch[i])
-            new_h.append(h_last)
-            new_s.append(S)
-        hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
+        if T == 1 and self.d_model <= 1024 and self.d_model % 8 == 0:
+            # decode: every block's tail (MoE scalars + LSF step + the norm that follows) is one launch
+            norms = [b.norm1 for b in self.blocks[1:]] + [self.final_norm]
+            xn = ops.rmsnorm(x, self.blocks[0].norm1.weight.detach().float(), self.blocks[0].norm1.eps)
+            for i, block in enumerate(self.blocks):
+                block.attn.max_position = max_position
+                h_last, _, S, xn = block.step_rows(x, xn, B, hs[i], pos, Ss[i], inplace and state is not None, scratch[i],
+                                                   (norms[i].weight.detach().float(), norms[i].eps))
+                new_h.append(h_last)
+                new_s.append(S)
+            hidden = xn
+        else:
+            for i, block in enumerate(self.blocks):
+                block.attn.max_position = max_position
+                h_last, _, S = block.forward_rows(x, B, T, hs[i], pos, Ss[i], want_attn_state=True,
+                                                  inplace_state=inplace and state is not None, scratch=scratch[i])
+                new_h.append(h_last)
+                new_s.append(S)
+            hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
         vocab = self.lm_head.weight.shape[0]
         logits = ops.dense_linear(hidden, self._lm_head_weight()).view(B, T, -1)[..., :vocab]
         return logits, {"h": new_h, "S": new_s}

@@ -467,6 +467,37 @@ def lsf_scan(m: torch.Tensor, *, alpha_tensor=None, alpha_scalar=None, act_var=N
     return out, h_last
 
 
+def lsf_step_norm(m: torch.Tensor, stats, probs_sum, top1_hist, E: int, n_tokens: int, n_elems: int,
+                  balance_alpha: float, scalars: torch.Tensor, var_scale: torch.Tensor, alpha_min: float,
+                  alpha_max: float, h_in, x: torch.Tensor, norm=None, h_out: torch.Tensor | None = None):
+    """Single-token tail of a block in one launch: moe_finalize -> `scalars`, the LSF step h = a h_in + (1 - a) m
+    with x += h in place, and (norm = (weight, eps)) the RMSNorm of the updated x.  m: bf16 (B, C); h_in f32 (B, C)
+    or None; x: f32 (B, C).  Returns (xn bf16 (B, C) or None, h_out f32 (B, C)); h_out may be h_in."""
+    lib = _lib.load()
+    _need(m, torch.bfloat16, "lsf_step_norm.m")
+    _need(x, torch.float32, "lsf_step_norm.x")
+    B, C = m.shape
+    if tuple(x.shape) != (B, C):
+        raise RuntimeError("lsf_step_norm: x must have the shape of m")
+    for name, t in (("h_in", h_in), ("h_out", h_out)):
+        if t is not None and tuple(_need(t, torch.float32, "lsf_step_norm." + name).shape) != (B, C):
+            raise RuntimeError(f"lsf_step_norm: {name} must be f32 (B, C)")
+    _need(scalars, torch.float32, "lsf_step_norm.scalars")
+    _need(var_scale, torch.float32, "lsf_step_norm.var_scale")
+    if h_out is None:
+        h_out = torch.empty((B, C), dtype=torch.float32, device=m.device)
+    xn = w = None
+    eps = 0.0
+    if norm is not None:
+        w, eps = _need(norm[0], torch.float32, "lsf_step_norm.norm weight"), float(norm[1])
+        xn = torch.empty((B, C), dtype=torch.bfloat16, device=m.device)
+    _lib.check(lib.jb200_lsf_step_norm(_ptr(m), _ptr(stats), _ptr(probs_sum), _ptr(top1_hist), E, n_tokens, n_elems,
+                                       balance_alpha, _ptr(scalars), _ptr(var_scale), alpha_min, alpha_max, _ptr(h_in),
+                                       _ptr(h_out), _ptr(x), _ptr(w), eps, _ptr(xn), B, C, _stream()),
+               "jb200_lsf_step_norm")
+    return xn, h_out
+
+
 def sample(logits: torch.Tensor, u: torch.Tensor | None = None, *, temperature: float = 0.7, top_k: int = 50,
            top_p: float = 0.9, want_prob: bool = False):
     """One token per row of `logits` ((B, V) f32 or bf16, rows may be strided): temperature / top-k / top-p

@@ -144,6 +144,49 @@ def test_decode_session_graph_replay_matches_eager_steps():
     assert torch.equal(sess.positions, pos + 3)
 
 
+def test_dependent_launch_on_and_off_give_the_same_results():
+    """The kernels of the chain start while their predecessor is still running and wait before they touch memory
+    (programmatic dependent launch): a prefill forward, eager decode steps and a captured decode graph must give
+    what fully serialised launches give (the only run-to-run freedom is the order of the fp64 atomics behind
+    act_var, far below the comparison's resolution)."""
+    torch.manual_seed(6)
+    model = jm.ternary_init_(jm.Jarvis(vocab_size=256, d_model=128, n_layers=3, n_heads=2, max_seq_len=512)).cuda().eval()
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    idx = torch.randint(0, 256, (3, 300), generator=gen, device="cuda")
+    B = 6
+    pos = torch.randint(1, 300, (B,), generator=gen, device="cuda", dtype=torch.int32)
+    state0 = {"h": [torch.randn(B, 128, generator=gen, device="cuda") for _ in range(3)],
+              "S": [torch.randn(B, 2, 64, 64, generator=gen, device="cuda") for _ in range(3)]}
+    toks = torch.randint(0, 256, (4, B, 1), generator=gen, device="cuda")
+    results = {}
+    assert _lib.set_dependent_launch(True) is True          # on by default
+    try:
+        for on in (False, True):
+            _lib.set_dependent_launch(on)
+            with torch.no_grad():
+                logits = model(idx)[0].float().clone()
+            st = {k: [t.clone() for t in v] for k, v in state0.items()}
+            steps = []
+            for i in range(4):
+                out, st = model.step(toks[i], pos + i, st, max_position=400)
+                steps.append(out.float().clone())
+            sess = jm.DecodeSession(model, {k: [t.clone() for t in v] for k, v in state0.items()}, pos.clone(),
+                                    max_position=400).capture()
+            sess.load_state(state0, pos)
+            graph_steps = [sess.step(toks[i]).float().clone() for i in range(4)]
+            torch.cuda.synchronize()
+            results[on] = (logits, steps, graph_steps, [t.clone() for t in st["S"]])
+    finally:
+        _lib.set_dependent_launch(True)
+    assert _lib.device_status() == 0
+    off, on = results[False], results[True]
+    assert rel_l2(on[0], off[0]) < 1e-5
+    for a, b, c in zip(on[1], off[1], on[2]):
+        assert rel_l2(a, b) < 1e-5 and rel_l2(c, b) < 1e-5
+    for a, b in zip(on[3], off[3]):
+        assert rel_l2(a, b) < 1e-6
+
+
 def test_attention_state_handoff_matches_single_call():
     """Beyond the reference: carrying S makes prefill(T1) + prefill(T2) equal one prefill of the
     attention stage (the LSF decay stays per call, so the comparison is at the attention module)."""

@@ -87,6 +87,33 @@ def test_attn_scan_carried_state_and_positions():
     assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
 
 
+@pytest.mark.parametrize("B,H", [(3, 2), (40, 4), (301, 16)])
+def test_attn_single_token_steps_with_carried_state(B, H):
+    """T = 1 with a carried state and ragged positions: a handful of (sequence, head) pairs take the per-pair
+    kernel, 64 pairs or more stream the state tiles through shared memory; in place and out of place."""
+    pos = torch.randint(0, 3000, (B,), generator=torch.Generator().manual_seed(B), dtype=torch.int32)
+    eo, es = _scan_case(B, H, 1, seed=7 * B + H, start_pos=pos, with_state=True)
+    assert eo <= TOL_BF16 and es <= 1e-5, (eo, es)
+    # in place == out of place, bit for bit, and two different batch sizes of the same rows agree
+    g = torch.Generator(device="cuda").manual_seed(B)
+    qkv = torch.randn(B, 3 * H * 64, generator=g, device="cuda").bfloat16()
+    gamma = torch.rand(H, generator=g, device="cuda") * 0.099 + 0.9
+    S0 = torch.randn(B, H, 64, 64, generator=g, device="cuda")
+    cos, sin = rope_tabs(3001)
+    C = H * 64
+    args = (qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin)
+    o1, S1 = ops.attn_scan(*args, B, 1, H, start_pos=pos.cuda(), state_in=S0, want_state=True)
+    S2 = S0.clone()
+    o2, S2r = ops.attn_scan(*args, B, 1, H, start_pos=pos.cuda(), state_in=S2, want_state=True, state_out=S2)
+    assert S2r.data_ptr() == S2.data_ptr() and torch.equal(S1, S2) and torch.equal(o1, o2)
+    # the first sequences alone (fewer pairs: possibly the other kernel): same state bits
+    nb = min(B, 3)
+    sub = tuple(a[:nb] for a in args[:3]) + args[3:]
+    _, S3 = ops.attn_scan(*sub, nb, 1, H, start_pos=pos[:nb].cuda(), state_in=S0[:nb].contiguous(), want_state=True)
+    assert torch.equal(S3, S1[:nb])
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize("T", [1000, 2048])
 def test_attn_scan_segmented_long_sequences(T):
     """Long sequences are cut into parallel segments (state pre-pass + fold); result must match the
@@ -319,6 +346,47 @@ def test_lsf_scan_bf16_with_residual(B, T, D):
     assert rel_l2(r, resid + ref) < 1e-6
     outb, _ = ops.lsf_scan(m.cuda(), alpha_scalar=alpha.cuda(), h0=h0.cuda())
     assert rel_l2(outb.float(), ref) < 4e-3
+
+
+@pytest.mark.parametrize("B,C,with_h,with_norm", [(5, 128, True, True), (256, 1024, True, True), (3, 1024, False, True),
+                                                   (9, 520, True, False)])
+def test_fused_single_token_tail_is_bit_identical_to_the_three_kernels(B, C, with_h, with_norm):
+    """moe_finalize + the T = 1 LSF step with the fused residual + the RMSNorm that follows, in one launch."""
+    gen = torch.Generator(device="cuda").manual_seed(B * 7 + C)
+    m = (torch.randn(B, C, generator=gen, device="cuda") * 0.3).bfloat16()
+    x = torch.randn(B, C, generator=gen, device="cuda")
+    h = torch.randn(B, C, generator=gen, device="cuda") if with_h else None
+    w = torch.rand(C, generator=gen, device="cuda") + 0.5
+    E, n_tok = 4, B
+    stats = torch.stack([m.double().sum(), (m.double() ** 2).sum()])
+    probs = torch.rand(E, generator=gen, device="cuda", dtype=torch.float64) * n_tok
+    hist = torch.tensor([B - 2, 1, 1, 0], dtype=torch.int32, device="cuda")
+    vs = torch.tensor([1.3], device="cuda")
+    # the three kernels
+    sc_ref = ops.moe_finalize(stats, probs, hist, E, n_tok, n_tok * C, 0.01)
+    x_ref = x.clone()
+    _, h_ref = ops.lsf_scan(m.view(B, 1, C), act_var=sc_ref[2:3], var_scale=vs, alpha_min=0.1, alpha_max=0.99, h0=h,
+                            resid=x_ref.view(B, 1, C), want_out=False)
+    xn_ref = ops.rmsnorm(x_ref, w, 1e-6) if with_norm else None
+    # one launch
+    sc = torch.zeros(3, device="cuda")
+    x_got = x.clone()
+    xn, h_got = ops.lsf_step_norm(m, stats, probs, hist, E, n_tok, n_tok * C, 0.01, sc, vs, 0.1, 0.99, h, x_got,
+                                  norm=(w, 1e-6) if with_norm else None)
+    assert torch.equal(sc, sc_ref) and torch.equal(h_got, h_ref) and torch.equal(x_got, x_ref)
+    assert (xn is None and xn_ref is None) or torch.equal(xn, xn_ref)
+    # against the oracle's formulas
+    alpha = 0.1 + 0.89 * torch.sigmoid(-vs.cpu() * sc_ref[2].cpu())
+    h_want = alpha * (h.cpu() if with_h else 0.0) + (1 - alpha) * m.float().cpu()
+    assert rel_l2(h_got, h_want) < 2e-6 and rel_l2(x_got, x.cpu() + h_want) < 2e-6
+    if with_norm:
+        assert rel_l2(xn.float(), orc.rmsnorm(x_got.cpu(), w.cpu())) < 4e-3
+    # in place on the membrane
+    if with_h:
+        h2, x2 = h.clone(), x.clone()
+        _, out = ops.lsf_step_norm(m, stats, probs, hist, E, n_tok, n_tok * C, 0.01, sc, vs, 0.1, 0.99, h2, x2, h_out=h2)
+        assert out is h2 and torch.equal(h2, h_ref)
+    assert _lib.device_status() == 0
 
 
 def test_lsf_segmented_matches_single_pass_and_oracle():
