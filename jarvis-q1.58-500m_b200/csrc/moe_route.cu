@@ -139,10 +139,10 @@ router_top2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 // logits in the same summation order as router_top2_kernel, so routing is bit-identical to running
 // the two kernels separately while the row is read from HBM once.
 template <int E>
-__global__ void __launch_bounds__(ROUTER_THREADS, 4)
+__global__ void __launch_bounds__(ROUTER_THREADS, 2)
 rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_norm, float eps,
                       __nv_bfloat16* __restrict__ xn, const float* __restrict__ w_router, int n_tokens, int C,
-                      int tokens_per_cta, int64_t* __restrict__ topk_idx, float* __restrict__ gates,
+                      int64_t* __restrict__ topk_idx, float* __restrict__ gates,
                       double* __restrict__ probs_sum, int* __restrict__ top1_hist) {
   pdl_wait();
   pdl_trigger();
@@ -156,48 +156,70 @@ rmsnorm_router_kernel(const float* __restrict__ x, const float* __restrict__ w_n
   float p_local[E];
 #pragma unroll
   for (int e = 0; e < E; ++e) p_local[e] = 0.f;
-  const int tok0 = blockIdx.x * tokens_per_cta;
-  for (int tt = warp; tt < tokens_per_cta; tt += ROUTER_THREADS / 32) {
-    const int tok = tok0 + tt;
-    if (tok >= n_tokens) break;
-    const float* xr = x + size_t(tok) * C;
-    float v[4][8];
-    float ss = 0.f;
+  // A warp takes TWO tokens per pass: their loads are in flight together, the two dependency chains interleave,
+  // and the router weights read from shared memory serve both.  The CTAs are persistent (two per SM) and stride
+  // over the token pairs, so the router matrix is staged once per CTA.
+  const int n_pairs = (n_tokens + 1) >> 1;
+  for (int pair = blockIdx.x * (ROUTER_THREADS / 32) + warp; pair < n_pairs; pair += gridDim.x * (ROUTER_THREADS / 32)) {
+    const int tok = 2 * pair;
+    const bool two = tok + 1 < n_tokens;
+    const float* xr0 = x + size_t(tok) * C;
+    const float* xr1 = x + size_t(two ? tok + 1 : tok) * C;     // a lone last token is processed twice, stored once
+    float v[2][4][8];
+    float ss0 = 0.f, ss1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int c = (i * 32 + lane) * 8;
       if (c < C) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(xr + c));
-        const float4 b = __ldg(reinterpret_cast<const float4*>(xr + c) + 1);
-        v[i][0] = a.x; v[i][1] = a.y; v[i][2] = a.z; v[i][3] = a.w; v[i][4] = b.x; v[i][5] = b.y; v[i][6] = b.z; v[i][7] = b.w;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+        const float4 a0 = __ldg(reinterpret_cast<const float4*>(xr0 + c)), b0 = __ldg(reinterpret_cast<const float4*>(xr0 + c) + 1);
+        const float4 a1 = __ldg(reinterpret_cast<const float4*>(xr1 + c)), b1 = __ldg(reinterpret_cast<const float4*>(xr1 + c) + 1);
+        v[0][i][0] = a0.x; v[0][i][1] = a0.y; v[0][i][2] = a0.z; v[0][i][3] = a0.w;
+        v[0][i][4] = b0.x; v[0][i][5] = b0.y; v[0][i][6] = b0.z; v[0][i][7] = b0.w;
+        v[1][i][0] = a1.x; v[1][i][1] = a1.y; v[1][i][2] = a1.z; v[1][i][3] = a1.w;
+        v[1][i][4] = b1.x; v[1][i][5] = b1.y; v[1][i][6] = b1.z; v[1][i][7] = b1.w;
       }
     }
-    ss = warp_sum(ss);
-    const float r = rsqrtf(ss / float(C) + eps);
-    float acc[E];
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+    for (int i = 0; i < 4; ++i) {
+      if ((i * 32 + lane) * 8 < C) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { ss0 = __fmaf_rn(v[0][i][j], v[0][i][j], ss0); ss1 = __fmaf_rn(v[1][i][j], v[1][i][j], ss1); }
+      }
+    }
+    ss0 = warp_sum(ss0);
+    ss1 = warp_sum(ss1);
+    const float r0 = rsqrtf(ss0 / float(C) + eps), r1 = rsqrtf(ss1 / float(C) + eps);
+    float acc0[E], acc1[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) { acc0[e] = 0.f; acc1[e] = 0.f; }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int c = (i * 32 + lane) * 8;
       if (c < C) {
         const float4 wa = __ldg(reinterpret_cast<const float4*>(w_norm + c));
         const float4 wb = __ldg(reinterpret_cast<const float4*>(w_norm + c) + 1);
-        const uint4 pk = make_uint4(pack_bf16x2(v[i][0] * r * wa.x, v[i][1] * r * wa.y),
-                                    pack_bf16x2(v[i][2] * r * wa.z, v[i][3] * r * wa.w),
-                                    pack_bf16x2(v[i][4] * r * wb.x, v[i][5] * r * wb.y),
-                                    pack_bf16x2(v[i][6] * r * wb.z, v[i][7] * r * wb.w));
-        *reinterpret_cast<uint4*>(xn + size_t(tok) * C + c) = pk;
-        const float xv[8] = {bf16_lo(pk.x), bf16_hi(pk.x), bf16_lo(pk.y), bf16_hi(pk.y),
-                             bf16_lo(pk.z), bf16_hi(pk.z), bf16_lo(pk.w), bf16_hi(pk.w)};
-        router_dot8<E>(xv, w_s, C, c, acc);
+        const uint4 pk0 = make_uint4(pack_bf16x2(v[0][i][0] * r0 * wa.x, v[0][i][1] * r0 * wa.y),
+                                     pack_bf16x2(v[0][i][2] * r0 * wa.z, v[0][i][3] * r0 * wa.w),
+                                     pack_bf16x2(v[0][i][4] * r0 * wb.x, v[0][i][5] * r0 * wb.y),
+                                     pack_bf16x2(v[0][i][6] * r0 * wb.z, v[0][i][7] * r0 * wb.w));
+        const uint4 pk1 = make_uint4(pack_bf16x2(v[1][i][0] * r1 * wa.x, v[1][i][1] * r1 * wa.y),
+                                     pack_bf16x2(v[1][i][2] * r1 * wa.z, v[1][i][3] * r1 * wa.w),
+                                     pack_bf16x2(v[1][i][4] * r1 * wb.x, v[1][i][5] * r1 * wb.y),
+                                     pack_bf16x2(v[1][i][6] * r1 * wb.z, v[1][i][7] * r1 * wb.w));
+        *reinterpret_cast<uint4*>(xn + size_t(tok) * C + c) = pk0;
+        if (two) *reinterpret_cast<uint4*>(xn + size_t(tok + 1) * C + c) = pk1;
+        const float xv0[8] = {bf16_lo(pk0.x), bf16_hi(pk0.x), bf16_lo(pk0.y), bf16_hi(pk0.y),
+                              bf16_lo(pk0.z), bf16_hi(pk0.z), bf16_lo(pk0.w), bf16_hi(pk0.w)};
+        const float xv1[8] = {bf16_lo(pk1.x), bf16_hi(pk1.x), bf16_lo(pk1.y), bf16_hi(pk1.y),
+                              bf16_lo(pk1.z), bf16_hi(pk1.z), bf16_lo(pk1.w), bf16_hi(pk1.w)};
+        router_dot8<E>(xv0, w_s, C, c, acc0);     // the same shared-memory words: the compiler loads them once
+        router_dot8<E>(xv1, w_s, C, c, acc1);
       }
     }
 #pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] = warp_sum(acc[e]);
-    router_finish<E>(acc, lane, tok, topk_idx, gates, nullptr, h_acc, p_local);
+    for (int e = 0; e < E; ++e) { acc0[e] = warp_sum(acc0[e]); acc1[e] = warp_sum(acc1[e]); }
+    router_finish<E>(acc0, lane, tok, topk_idx, gates, nullptr, h_acc, p_local);
+    if (two) router_finish<E>(acc1, lane, tok + 1, topk_idx, gates, nullptr, h_acc, p_local);
   }
   if (lane == 0) {
 #pragma unroll
@@ -461,16 +483,19 @@ int launch_rmsnorm_router(const float* x, const float* w_norm, float eps, void* 
   JB_REQUIRE(aligned16(x) && aligned16(w_norm) && aligned16(xn_bf16) && aligned16(w_router),
              "rmsnorm_router: pointers must be 16-byte aligned");
   if (n_tokens == 0) return JB200_OK;
-  const int tpc = n_tokens <= 4096 ? ROUTER_THREADS / 32 : ROUTER_TOKENS_PER_CTA;
-  const int blocks = (n_tokens + tpc - 1) / tpc;
+  // persistent CTAs, two per SM, striding over the token pairs (one pair per warp and pass)
+  const int sms = sm_count();
+  if (sms <= 0) return JB200_ERR_CUDA;
+  const int pair_blocks = ((n_tokens + 1) / 2 + ROUTER_THREADS / 32 - 1) / (ROUTER_THREADS / 32);
+  const int blocks = pair_blocks < 2 * sms ? pair_blocks : 2 * sms;
   const size_t smem = size_t(E) * C * sizeof(float);
   __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(xn_bf16);
   if (E == 4)
-    launch_dep(rmsnorm_router_kernel<4>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
-                                                                       topk_idx, gates, probs_sum, top1_hist);
+    launch_dep(rmsnorm_router_kernel<4>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C,
+               topk_idx, gates, probs_sum, top1_hist);
   else
-    launch_dep(rmsnorm_router_kernel<8>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C, tpc,
-                                                                       topk_idx, gates, probs_sum, top1_hist);
+    launch_dep(rmsnorm_router_kernel<8>, blocks, ROUTER_THREADS, smem, stream, x, w_norm, eps, xn, w_router, n_tokens, C,
+               topk_idx, gates, probs_sum, top1_hist);
   JB_LAUNCH_CHECK("rmsnorm_router_kernel");
   return JB200_OK;
 }

@@ -294,12 +294,17 @@ class SparseMoELayer(nn.Module):
             if norm is not None:
                 xn_rows = ops.rmsnorm(xn_rows, norm[0], norm[1])
             idx, gates, _ = ops.router_top2(xn_rows, w_r, probs_sum=acc[2:], top1_hist=hist)
-        meta = ops.moe_metadata(idx, E)
+        # expert parallel: the gather map and the expert offsets are written where the other ranks read them
+        meta_in_slab = ep is not None and N <= ep.ex.n_max
+        if meta_in_slab:
+            meta = ops.moe_metadata(idx, E, gather_out=ep.ex.gmap[:N * self.top_k], offsets_out=ep.ex.offs[:E + 1])
+        else:
+            meta = ops.moe_metadata(idx, E)
         counts, offsets, scatter, gather, gate_idx = meta
         if ep is not None:
             # the owners of the experts pull their rows from every rank, the home ranks pull the results back
-            out = ep.run_routed(xn_rows, idx, gates, offsets, scatter, gather, x_in_slab=in_slab, out_dtype=out_dtype,
-                                stats=acc[:2])
+            out = ep.run_routed(xn_rows, idx, gates, offsets, scatter, gather, x_in_slab=in_slab,
+                                meta_in_slab=meta_in_slab, out_dtype=out_dtype, stats=acc[:2])
         else:
             (p1, a1), (p2, a2) = self.packed()
             disp = ops.dispatch_gather(xn_rows, gather)

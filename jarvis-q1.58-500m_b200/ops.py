@@ -371,17 +371,30 @@ def rmsnorm_router(x: torch.Tensor, w_norm: torch.Tensor, eps: float, w_router: 
     return xn, idx, gates
 
 
-def moe_metadata(topk_idx: torch.Tensor, num_experts: int):
-    """compute_metadata(topk_idx, E) -> (counts, offsets, scatter_map, gather_map, gate_idx_map), int32."""
+def moe_metadata(topk_idx: torch.Tensor, num_experts: int, *, gather_out: torch.Tensor | None = None,
+                 offsets_out: torch.Tensor | None = None):
+    """compute_metadata(topk_idx, E) -> (counts, offsets, scatter_map, gather_map, gate_idx_map), int32.
+    gather_out (N*K,) / offsets_out (E+1,): caller-owned int32 buffers to write those two maps into (the expert-
+    parallel exchange publishes them to the other ranks from its own buffer)."""
     lib = _lib.load()
     _need(topk_idx, torch.int64, "moe_metadata.topk_idx")
     N, K = topk_idx.shape
     dev = topk_idx.device
     i32 = torch.int32
     counts = torch.empty((num_experts,), dtype=i32, device=dev)
-    offsets = torch.empty((num_experts + 1,), dtype=i32, device=dev)
+    if offsets_out is not None:
+        offsets = _need(offsets_out, i32, "moe_metadata.offsets_out")
+        if offsets.numel() != num_experts + 1:
+            raise RuntimeError("moe_metadata: offsets_out must hold E + 1 entries")
+    else:
+        offsets = torch.empty((num_experts + 1,), dtype=i32, device=dev)
     scatter = torch.empty((N, K), dtype=i32, device=dev)
-    gather = torch.empty((N * K,), dtype=i32, device=dev)
+    if gather_out is not None:
+        gather = _need(gather_out, i32, "moe_metadata.gather_out")
+        if gather.numel() != N * K:
+            raise RuntimeError("moe_metadata: gather_out must hold N * K entries")
+    else:
+        gather = torch.empty((N * K,), dtype=i32, device=dev)
     gate_idx = torch.empty((N * K,), dtype=i32, device=dev)
     nbytes = lib.jb200_moe_metadata_scratch_bytes(N, K, num_experts)
     scratch = torch.empty((max(nbytes, 4) // 4,), dtype=i32, device=dev)

@@ -302,6 +302,7 @@ class PeerExchange:
         self.y = view("y", torch.bfloat16, (self.max_rows, C))
         self.gmap = view("gmap", torch.int32, (max_tokens * K,))
         self.offs = view("offs", torch.int32, (E + 2,))
+        self.n_published = -1          # the token count last written behind the offsets
         self.meta = view("meta", torch.int32, (self.per * (self.world + 1) + self.per + 1,))
         self.ptrs = {name: torch.tensor([b + layout[name] for b in bases], dtype=torch.int64, device=device) for name in layout}
         self.disp = torch.empty((self.max_rows, C), dtype=torch.bfloat16, device=device)
@@ -379,9 +380,11 @@ class PeerExpertParallelMoE:
         if self._own_exchange:
             self.ex.close()
 
-    def run_routed(self, x, idx, gates, offsets, scatter, gather, *, x_in_slab=False, out_dtype=None, stats=None):
+    def run_routed(self, x, idx, gates, offsets, scatter, gather, *, x_in_slab=False, meta_in_slab=False, out_dtype=None,
+                   stats=None):
         """The exchange for rows that are already routed: x bf16 (N, C) (or already sitting in the exchange's row
-        buffer), idx / gates / offsets / scatter / gather = this rank's router and dispatch-metadata results."""
+        buffer), idx / gates / offsets / scatter / gather = this rank's router and dispatch-metadata results
+        (meta_in_slab: gather and offsets ARE the exchange's own buffers, written there by the metadata kernels)."""
         from . import ops
         ex = self.ex
         lib, C, E, K = self._lib.load(), ex.C, ex.E, ex.K
@@ -391,9 +394,12 @@ class PeerExpertParallelMoE:
         stream = torch.cuda.current_stream().cuda_stream
         if not x_in_slab:
             ex.xn[:N].copy_(x)
-        ex.gmap[:N * K].copy_(gather)
-        ex.offs[:E + 1].copy_(offsets)
-        ex.offs[E + 1:].fill_(N)
+        if not meta_in_slab:
+            ex.gmap[:N * K].copy_(gather)
+            ex.offs[:E + 1].copy_(offsets)
+        if ex.n_published != N:                         # the row count of this rank, read by the peers' gathers
+            ex.offs[E + 1:].fill_(N)
+            ex.n_published = N
         ex.barrier()                                    # every rank's rows and routing are in place
         self._lib.check(lib.jb200_ep_pull_gather(ex.ptrs["offs"].data_ptr(), ex.ptrs["gmap"].data_ptr(),
                                                  ex.ptrs["xn"].data_ptr(), ex.world, ex.rank, E, C, K, ex.n_max,

@@ -211,7 +211,8 @@ def test_fused_rmsnorm_router_is_bit_identical_to_the_two_kernels():
         idx1, gates1, _ = ops.router_top2(xn1, wr, probs_sum=ps1, top1_hist=h1)
         xn2, idx2, gates2 = ops.rmsnorm_router(x, wn, 1e-6, wr, probs_sum=ps2, top1_hist=h2)
         assert torch.equal(xn1, xn2) and torch.equal(idx1, idx2) and torch.equal(gates1, gates2)
-        assert torch.equal(h1, h2) and torch.allclose(ps1, ps2, rtol=1e-12)
+        # P_e is summed per warp in f32 before the f64 atomics: the two kernels group the tokens differently
+        assert torch.equal(h1, h2) and torch.allclose(ps1, ps2, rtol=1e-6)
 
 
 def test_router_ties_go_to_lower_expert():
