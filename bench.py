@@ -397,6 +397,10 @@ def multi_gpu_records(model, device, rank, world, barrier):
             x = x.to(device)
             n_loc = N // world
             x_loc = x[rank * n_loc:(rank + 1) * n_loc].contiguous()
+            if peer:
+                # as in the model, where the fused norm + router kernel leaves the rows in the exchange's own buffer
+                ep.ex.xn[:n_loc].copy_(x_loc)
+                x_loc = ep.ex.xn[:n_loc]
             got, _ = ep.run_rows(x_loc)
             ref, _ = moe.run_rows(x_loc)
             err = float((got.float() - ref.float()).norm() / ref.float().norm())

@@ -426,6 +426,14 @@ class PeerExpertParallelMoE:
     def run_rows(self, x, stats=None):
         """x: bf16 (N_local, C) rows of this rank -> ((N_local, C) MoE output, (topk_idx, gates))."""
         from . import ops
+        ex = self.ex
         idx, gates, _ = ops.router_top2(x, self.moe.router.weight.detach().float().contiguous())
-        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, self.ex.E)
-        return self.run_routed(x, idx, gates, offsets, scatter, gather, stats=stats), (idx, gates)
+        N = idx.shape[0]
+        if N > ex.n_max:
+            raise RuntimeError(f"PeerExpertParallelMoE: {N} tokens exceed max_tokens={ex.n_max}")
+        # the gather map and the offsets go straight into the buffers the other ranks read; rows that the caller
+        # already keeps in the exchange's row buffer (x is ex.xn[:N]) are not copied either
+        counts, offsets, scatter, gather, _ = ops.moe_metadata(idx, ex.E, gather_out=ex.gmap[:N * ex.K],
+                                                               offsets_out=ex.offs[:ex.E + 1])
+        return self.run_routed(x, idx, gates, offsets, scatter, gather, x_in_slab=x.data_ptr() == ex.xn.data_ptr(),
+                               meta_in_slab=True, stats=stats), (idx, gates)
