@@ -36,6 +36,8 @@ def peaks():
 
 
 def timeit(fn, iters, flush=True):
+    # L2 flush: a 256 MiB buffer is written twice before every timed launch (~90 us of device work, so the host has
+    # queued the launch, with its allocations, tensor maps and ctypes call, before the device gets there)
     scratch = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(3):
         fn()
@@ -43,8 +45,8 @@ def timeit(fn, iters, flush=True):
     total = 0.0
     for _ in range(iters):
         if flush:
-            scratch.fill_(1)     # twice: ~90 us of device work, so the host has queued the launch
-            scratch.fill_(2)     # (allocations, tensor maps, ctypes) before the device reaches it
+            scratch.fill_(1)
+            scratch.fill_(2)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         fn()
@@ -103,6 +105,19 @@ def case_attn(a):
     fr = torch.outer(t, inv)
     cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
     o = torch.empty(a.B * a.T, C, dtype=torch.bfloat16, device="cuda")
+    if a.T == 1:
+        # the decode step: carried f32 state (B, H, 64, 64) updated in place, ragged positions
+        S = torch.randn(a.B, a.H, 64, 64, generator=g, device="cuda")
+        pos = torch.randint(0, 4096, (a.B,), generator=g, device="cuda", dtype=torch.int32)
+        t = torch.arange(4097, dtype=torch.float32, device="cuda")
+        fr = torch.outer(t, inv)
+        cos, sin = fr.cos().contiguous(), fr.sin().contiguous()
+        fn = lambda: ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, a.B, 1, a.H,  # noqa: E731
+                                   start_pos=pos, state_in=S, want_state=True, state_out=S, out=o)
+        ms = timeit(fn, a.iters)
+        report("attn_decode_stream_kernel" if a.B * a.H >= 64 else "attn_decode_kernel", ms,
+               bytes_=2.0 * a.B * a.H * 64 * 64 * 4 + 512.0 * a.B * a.H, extra={"B": a.B, "H": a.H, "T": 1})
+        return
     fn = lambda: ops.attn_scan(qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, a.B, a.T, a.H,  # noqa: E731
                                want_state=True, out=o)
     ms = timeit(fn, a.iters)
