@@ -95,9 +95,13 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.samples.append((time.time(), parts))
 
-    def stop(self):
+    def stop(self, t0=None, t1=None):
+        """Summary of the samples read between the host times t0 and t1 (the timed region).  nvidia-smi needs a
+        few hundred ms to deliver its first line, so the sampler is started before the warm-up steps; a timed
+        region shorter than the sampling period takes the samples up to 0.3 s either side of it (the same
+        workload runs there: warm-up before, the end-to-end steps after)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         time.sleep(0.15)
@@ -106,12 +110,17 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        clocks = [int(s[0]) for s in self.samples if s[0].isdigit()]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        rows = [s for t, s in self.samples if t0 is None or t0 <= t <= t1]
+        window = "timed region"
+        if not rows and t0 is not None:
+            rows = [s for t, s in self.samples if t0 - 0.3 <= t <= t1 + 0.3]
+            window = "timed region +- 0.3 s"
+        clocks = [int(s[0]) for s in rows if s[0].isdigit()]
+        mx = [int(s[1]) for s in rows if s[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in self.samples)]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower() == "active" for s in rows)]
         return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(clocks)}
+                "reasons": reasons, "samples": len(clocks), "window": window}
 
 
 # --------------------------------------------------------------------------------------------
@@ -244,23 +253,25 @@ def run_ours(args, rank, world, local_rank):
         last_host.copy_(logits[:, -1, :], non_blocking=True)
         return logits
 
+    sampler = ClockSampler(local_rank)      # started here: its first line takes a few hundred ms
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step_device()
     barrier()
     assert _lib.device_status() == 0, "a bounded wait ran out during warm-up"
 
     # ---- device-resident throughput: nothing but the forward inside the timed loop ---------------
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     _lib.kernel_launches(reset=True)
+    t_begin = time.time()
     ms = _time_steps(step_device, args.steps, barrier)
+    t_end = time.time()
     launches = _lib.kernel_launches(reset=True)
-    clocks = sampler.stop()
 
     # ---- end to end through the module API with host buffers ----------------------------------
     for _ in range(2):
         step_e2e()
     ms_e2e = _time_steps(step_e2e, args.steps, barrier)
+    clocks = sampler.stop(t_begin, t_end)
 
     # ---- per-kernel pass: events around every GEMM / attention-scan / LSF-scan launch ------------
     timers = KernelTimers(ops)
