@@ -45,6 +45,7 @@ extern "C" {
 #define JB200_STATUS_GEMM_EPILOGUE 0x14u
 #define JB200_STATUS_ATTN_LOAD 0x21u
 #define JB200_STATUS_ATTN_MMA 0x22u
+#define JB200_STATUS_ATTN_HANDOFF 0x23u   /* the second part of a cut sequence never saw the first part's state */
 #define JB200_STATUS_LSF_LOAD 0x31u
 #define JB200_STATUS_PEER_BARRIER 0x41u
 #define JB200_STATUS_SELFTEST_WAIT 0x7Fu

@@ -65,6 +65,13 @@ struct AttnParams {
   int n_pieces;            // pieces stored per (sequence, head): nseg - 1, or nseg in a state-only call
   int qk_prepared;         // q, k already hold phi(.) + RoPE with the head dim interleaved (d, d+32 adjacent)
   int wide_store;          // output rows are 32-byte aligned: 256-bit stores
+  // Balanced launch (more sequence-heads than SMs, a partly filled last wave): the first n_split sequence-heads are
+  // cut in two at chunk split_chunk.  CTAs take tickets from ctrl[0]; tickets [0, n_split) are the first parts,
+  // [n_split, B*H) whole sequence-heads, [B*H, B*H + n_split) the second parts, which find the state after the
+  // first part in handoff[unit] once ctrl[1 + unit] has counted the eight consumer warps that wrote it.
+  int n_split, split_chunk;
+  float* handoff;          // [n_split][64][64] f32
+  int* ctrl;               // [1 + n_split], zeroed before the launch
   unsigned int* status;
 };
 
@@ -353,6 +360,7 @@ struct PipeSmem {
   uint64_t bar_s, s_done, p_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
+  int ticket;
 };
 constexpr size_t PIPE_SMEM_BYTES = sizeof(PipeSmem) + 1024;
 
@@ -374,14 +382,8 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   PipeSmem* sm = reinterpret_cast<PipeSmem*>(smem_raw + (base - raw_addr));
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int h = blockIdx.x, b = blockIdx.y;
   const int T = p.T;
   const int n_chunks = (T + CH - 1) / CH;
-  const int seg = blockIdx.z;
-  const int ck_begin = seg * p.seg_chunks;
-  const int ck_end = min(n_chunks, ck_begin + p.seg_chunks);
-  const int n_loc = ck_end - ck_begin;
-  const int row0 = b * T;
 
   if (tid == 0) {
     for (int s = 0; s < NST; ++s) {
@@ -412,6 +414,25 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
   pdl_wait();        // everything above overlapped the kernel before this one; global memory is read from here on
   pdl_trigger();
+  // Which chunks of which sequence-head this CTA scans.  piece: 0 a whole sequence-head or a pre-passed segment,
+  // 1 the first part of a cut one (leaves its end state in handoff), 2 the second part (starts from it).
+  int h = blockIdx.x, b = blockIdx.y, seg = blockIdx.z, piece = 0;
+  int ck_begin = seg * p.seg_chunks, ck_end = min(n_chunks, ck_begin + p.seg_chunks);
+  if (p.n_split > 0) {
+    // a ticket instead of the block index: whoever holds a second part started after every first part was taken
+    if (tid == 0) sm->ticket = atomicAdd(p.ctrl, 1);
+    __syncthreads();
+    const int t = sm->ticket, U = p.B * p.H;
+    seg = 0;
+    int unit = t;                                     // = b * H + h
+    if (t < p.n_split) { piece = 1; ck_begin = 0; ck_end = p.split_chunk; }
+    else if (t < U) { ck_begin = 0; ck_end = n_chunks; }
+    else { unit = t - U; piece = 2; ck_begin = p.split_chunk; ck_end = n_chunks; }
+    b = unit / p.H;
+    h = unit - b * p.H;
+  }
+  const int n_loc = ck_end - ck_begin;
+  const int row0 = b * T;
   const float log_g = logf(__ldg(p.gamma + h));
   for (int n = tid; n <= CH; n += PIPE_THREADS) sm->pw[n] = expf(log_g * float(n));
   for (int n = tid; n < 2 * CH; n += PIPE_THREADS) {
@@ -677,7 +698,33 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       tmem_st_wait();
     }
     float S[16];
-    {
+    if (piece == 2) {
+      // second part of a cut sequence-head: the state after the first part, written by the eight consumer warps of
+      // the CTA that scanned it (in this kernel's own element order).  Bounded wait on their count.
+      int* flag = p.ctrl + 1 + bh;
+      if (lane == 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        int seen;
+        for (;;) {
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+          if (seen >= 8 || *abort_flag) break;
+          if (globaltimer_ns() - t0 > JB_WAIT_LIMIT_NS) {
+            *abort_flag = 1u;
+            atomicCAS(p.status, 0u, JB200_STATUS_ATTN_HANDOFF);
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+      __syncwarp();
+      __threadfence();
+      const float* hp = p.handoff + bh * D * D + s_row * D + 16 * s_cg;
+#pragma unroll
+      for (int e4 = 0; e4 < 4; ++e4) {
+        const float4 v4 = __ldcg(reinterpret_cast<const float4*>(hp) + e4);
+        S[4 * e4] = v4.x; S[4 * e4 + 1] = v4.y; S[4 * e4 + 2] = v4.z; S[4 * e4 + 3] = v4.w;
+      }
+    } else {
       const float* sin_p = p.s_in ? p.s_in + bh * D * D + s_row * D : nullptr;
 #pragma unroll
       for (int e = 0; e < 16; ++e) {
@@ -789,7 +836,18 @@ attn_scan_pipe_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       JB_T_MARK(7)
     }
     JB_T_FLUSH(warp)
-    if (ok && p.s_out && seg == p.nseg - 1) {
+    if (piece == 1) {
+      // first part of a cut sequence-head: its end state for the CTA that takes the second part
+      if (ok) {
+        float* hp = p.handoff + bh * D * D + s_row * D + 16 * s_cg;
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4)
+          __stcg(reinterpret_cast<float4*>(hp) + e4, make_float4(S[4 * e4], S[4 * e4 + 1], S[4 * e4 + 2], S[4 * e4 + 3]));
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.ctrl + 1 + bh, 1);
+      }
+    } else if (ok && p.s_out && seg == p.nseg - 1) {
       float* sp = p.s_out + bh * D * D + s_row * D;
       if (p.qk_prepared) {
 #pragma unroll
@@ -1046,12 +1104,28 @@ static void pick_segments(int B, int T, int H, int sms, int* seg_chunks, int* ns
   *nseg = (n_chunks + sc - 1) / sc;
 }
 
+// Balanced launch: with more sequence-heads than SMs and a last wave that is at most half full, that many
+// sequence-heads are cut in two; the first parts run first, the second parts last, and the makespan drops by half
+// a sequence (B=32 x 16 heads on 148 SMs: 64 -> 56 chunk times).  A sequence's chunks are serial, so nothing is to be
+// gained when every SM holds at most one sequence-head.
+static int pick_split(int B, int T, int H, int sms) {
+  const long U = long(B) * H;
+  const int n_chunks = (T + CH - 1) / CH;
+  if (U <= sms || n_chunks < 8) return 0;      // short sequences: the ticket and the hand-off cost more than they save
+  const int R = int(U % sms);
+  return (R > 0 && 2 * R <= sms) ? R : 0;
+}
+
 size_t attn_scan_scratch_bytes(int B, int T, int H) {
   if (B <= 0 || T <= 0 || H <= 0) return 0;
-  const int sms = sm_count();
+  int sms = sm_count();
+  if (sms <= 0) sms = 148;
   int sc, ns;
-  pick_segments(B, T, H, sms > 0 ? sms : 148, &sc, &ns);
-  return size_t(B) * H * size_t(ns) * D * D * sizeof(float);   // ns - 1 pieces for a full call, ns for a state-only one
+  pick_segments(B, T, H, sms, &sc, &ns);
+  const size_t seg_bytes = size_t(B) * H * size_t(ns) * D * D * sizeof(float);   // ns - 1 pieces for a full call, ns for a state-only one
+  const int n_split = pick_split(B, T, H, sms);
+  const size_t split_bytes = n_split ? size_t(n_split) * D * D * sizeof(float) + (size_t(n_split) + 1) * sizeof(int) : 0;
+  return seg_bytes > split_bytes ? seg_bytes : split_bytes;
 }
 
 int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, const float* gamma,
@@ -1124,6 +1198,7 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
   JB_REQUIRE(p.nseg <= 65535, "attn_scan: too many segments");
   JB_REQUIRE(!scratch || aligned16(scratch), "attn_scan: scratch pointer must be 16-byte aligned");
   p.n_pieces = o ? p.nseg - 1 : p.nseg;
+  p.n_split = 0; p.split_chunk = 0; p.handoff = nullptr; p.ctrl = nullptr;
   if (!o) {
     // state only: the k/v pass over every piece, then the fold
     JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
@@ -1138,6 +1213,16 @@ int launch_attn_scan(const void* q, const void* k, const void* v, int ld_qkv, co
     JB_CUDA(cudaFuncSetAttribute(attn_state_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(STATE_SMEM_BYTES)));
     launch_dep(attn_state_pass_kernel, dim3(H, B, p.nseg - 1), STATE_THREADS, STATE_SMEM_BYTES, stream, tk, tv, p);
     JB_LAUNCH_CHECK("attn_state_pass_kernel");
+  }
+  if (scratch && p.nseg == 1 && (p.n_split = pick_split(B, T, H, sms)) > 0) {
+    p.split_chunk = ((T + CH - 1) / CH) / 2;
+    p.handoff = reinterpret_cast<float*>(scratch);
+    p.ctrl = reinterpret_cast<int*>(p.handoff + size_t(p.n_split) * D * D);
+    JB_CUDA(cudaMemsetAsync(p.ctrl, 0, (size_t(p.n_split) + 1) * sizeof(int), stream));
+    launch_dep(attn_scan_pipe_kernel, dim3(unsigned(long(B) * H + p.n_split)), PIPE_THREADS, PIPE_SMEM_BYTES, stream, tq, tk,
+               tv, p);
+    JB_LAUNCH_CHECK("attn_scan_pipe_kernel");
+    return JB200_OK;
   }
   launch_dep(attn_scan_pipe_kernel, dim3(H, B, p.nseg), PIPE_THREADS, PIPE_SMEM_BYTES, stream, tq, tk, tv, p);
   JB_LAUNCH_CHECK("attn_scan_pipe_kernel");

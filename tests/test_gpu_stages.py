@@ -87,6 +87,31 @@ def test_attn_scan_carried_state_and_positions():
     assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
 
 
+@pytest.mark.parametrize("B,H,T", [(10, 16, 1100), (19, 8, 1025), (38, 4, 1500)])
+def test_attn_scan_balanced_launch_cuts_sequences_in_two(B, H, T):
+    """A few more sequence-heads than SMs (a last wave at most half full): that many are cut in two inside ONE
+    launch, the second part starting from the state the first part's CTA leaves behind.  Same results as any
+    other launch: outputs and final state against the fp64 recurrence, with a carried state and ragged positions;
+    and bit-identical to the call without scratch memory (which never cuts)."""
+    props = torch.cuda.get_device_properties(0)
+    U, sms = B * H, props.multi_processor_count
+    pos = torch.randint(0, 500, (B,), generator=torch.Generator().manual_seed(B), dtype=torch.int32)
+    eo, es = _scan_case(B, H, T, seed=B + T, start_pos=pos, with_state=True)
+    assert eo <= TOL_BF16 and es <= TOL_BF16, (eo, es)
+    g = torch.Generator(device="cuda").manual_seed(T)
+    C = H * 64
+    qkv = torch.randn(B * T, 3 * C, generator=g, device="cuda").bfloat16()
+    gamma = torch.rand(H, generator=g, device="cuda") * 0.099 + 0.9
+    cos, sin = rope_tabs(T)
+    args = (qkv[:, :C], qkv[:, C:2 * C], qkv[:, 2 * C:], gamma, cos, sin, B, T, H)
+    o1, S1 = ops.attn_scan(*args, want_state=True)
+    o2, S2 = ops.attn_scan(*args, want_state=True, segmented=False)
+    assert torch.equal(o1, o2) and torch.equal(S1, S2)
+    if sms == 148:
+        assert U > sms and 0 < U % sms <= sms // 2      # the shapes above are meant to take the balanced launch
+    assert _lib.device_status() == 0
+
+
 @pytest.mark.parametrize("B,H", [(3, 2), (40, 4), (301, 16)])
 def test_attn_single_token_steps_with_carried_state(B, H):
     """T = 1 with a carried state and ragged positions: a handful of (sequence, head) pairs take the per-pair
