@@ -364,12 +364,12 @@ struct LsfTma {
   static constexpr size_t smem_bytes(int stages) { return size_t(stages) * STAGE_BYTES + CTL_BYTES + 128 /* alignment slack */; }
   // Stages: enough CTAs to put two (fused) or three (plain) on every SM -> a short ring each; a grid that leaves
   // SMs with one CTA -> that CTA gets a ring of four stages (and sequences are not cut into segments).
-  static constexpr int STAGES_SHARED = FUSED ? 2 : 4;
+  static constexpr int STAGES_SHARED = FUSED ? 2 : 3;   // plain: four CTAs per SM (64 registers), so 512 CTAs (B=32 x 16 channel tiles) are one wave
   static constexpr int STAGES_ALONE = 4;
 };
 
 template <bool FUSED>
-__global__ void __launch_bounds__(LSF_THREADS, FUSED ? 2 : 3)
+__global__ void __launch_bounds__(LSF_THREADS, FUSED ? 2 : 4)
 lsf_tma_kernel(const __grid_constant__ CUtensorMap tm_m, const __grid_constant__ CUtensorMap tm_io, const LsfParams p,
                const int n_stages, unsigned int* status) {
   pdl_wait();
