@@ -367,6 +367,7 @@ def multi_gpu_records(model, device, rank, world, barrier):
         whole = torch.randint(0, CFG["vocab"], (B, T), generator=torch.Generator().manual_seed(77)).to(device)
         per = B // world
         mine = whole[rank * per:(rank + 1) * per].contiguous()
+        strong_mine, strong_tokens = mine, B * T
         model.set_batch_split(dist.group.WORLD, global_tokens=B * T)
         for _ in range(2):
             model(mine)
@@ -459,6 +460,23 @@ def multi_gpu_records(model, device, rank, world, barrier):
     except Exception as exc:  # noqa: BLE001
         model.set_context_parallel(None)
         out["cp"] = {"error": f"{type(exc).__name__}: {exc}"}
+
+    # ---- strong scaling again, the split forward captured in a CUDA graph (last: a failed capture ends the records) --
+    # From Python the ~340 launches of a forward cost several ms of host time, which a 14 ms step hides and a split
+    # batch does not; a replay is one launch (the per-layer NCCL all-reduce is captured with it).
+    if "ms_per_step" in out.get("strong", {}):
+        try:
+            model.set_batch_split(dist.group.WORLD, global_tokens=strong_tokens)
+            sess = jm.PrefillSession(model, strong_mine.shape[0], strong_mine.shape[1], device).capture()
+            for _ in range(2):
+                sess(strong_mine)
+            n = 5
+            ms = _max_over_ranks([_time_steps(lambda: sess(strong_mine), n, barrier)], device, world)[0] / n
+            out["strong"]["ms_per_step_cuda_graph"] = ms
+            out["strong"]["tok_per_s_cuda_graph"] = strong_tokens / (ms * 1e-3)
+        except Exception as exc:  # noqa: BLE001
+            out["strong"]["cuda_graph_error"] = f"{type(exc).__name__}: {exc}"
+        model.set_batch_split(None)
     return out
 
 

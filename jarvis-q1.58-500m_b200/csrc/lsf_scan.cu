@@ -375,7 +375,7 @@ lsf_tma_kernel(const __grid_constant__ CUtensorMap tm_m, const __grid_constant__
   pdl_wait();
   pdl_trigger();
   using Cfg = LsfTma<FUSED>;
-  constexpr int TPW = 16;
+  constexpr int TPW = LT_TOK / LSF_WARPS;    // 16 (sixteen warps of 8 tokens were measured: slower)
   extern __shared__ uint8_t lsf_smem_raw[];
   const uint32_t raw_addr = smem_u32(lsf_smem_raw);
   const uint32_t base = (raw_addr + 127u) & ~127u;
@@ -488,7 +488,14 @@ lsf_tma_kernel(const __grid_constant__ CUtensorMap tm_m, const __grid_constant__
     if (threadIdx.x == 0) {
       tma_store_3d(&tm_io, ch0, t_begin + i * LT_TOK, b, smem_u32(FUSED ? r_tile : m_tile));
       bulk_commit_group();
-      if (i + n_stages < n_tiles) {
+      if (n_stages >= 4) {
+        // deep ring: refill the stage of the tile BEFORE this one, whose store has had a whole tile's time to read
+        // it, so that this thread does not sit out the latency of the store it has just issued
+        if (i >= 1 && i - 1 + n_stages < n_tiles) {
+          bulk_wait_group_read<1>();
+          issue(i - 1 + n_stages);
+        }
+      } else if (i + n_stages < n_tiles) {
         bulk_wait_group_read<0>();   // the store has read the stage: it may be filled again
         issue(i + n_stages);
       }
@@ -544,9 +551,9 @@ int launch_tma(LsfParams p, cudaStream_t stream) {
     launch_dep(lsf_scan_kernel<false, __nv_bfloat16, __nv_bfloat16, LSF_TPW, true>, grid_a, LSF_THREADS, 0, stream, p);
     JB_LAUNCH_CHECK("lsf_scan_kernel<ends>");
   }
+  dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
   JB_CUDA(cudaFuncSetAttribute(lsf_tma_kernel<FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                int(Cfg::smem_bytes(Cfg::STAGES_ALONE))));
-  dim3 grid((p.D + LSF_CH - 1) / LSF_CH, p.B, p.nseg);
   launch_dep(lsf_tma_kernel<FUSED>, grid, LSF_THREADS, Cfg::smem_bytes(stages), stream, tm_m, tm_io, p, stages, status);
   JB_LAUNCH_CHECK("lsf_tma_kernel");
   return JB200_OK;

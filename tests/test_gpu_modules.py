@@ -187,6 +187,20 @@ def test_dependent_launch_on_and_off_give_the_same_results():
         assert rel_l2(a, b) < 1e-6
 
 
+def test_prefill_session_graph_replay_matches_the_eager_forward():
+    torch.manual_seed(9)
+    model = jm.ternary_init_(jm.Jarvis(vocab_size=256, d_model=128, n_layers=2, n_heads=2, max_seq_len=512)).cuda().eval()
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    sess = jm.PrefillSession(model, 3, 200).capture()
+    for _ in range(2):
+        idx = torch.randint(0, 256, (3, 200), generator=gen, device="cuda")
+        got = sess(idx).float().clone()
+        with torch.no_grad():
+            want = model(idx)[0].float()
+        assert rel_l2(got, want) < 1e-5
+    assert _lib.device_status() == 0
+
+
 def test_attention_state_handoff_matches_single_call():
     """Beyond the reference: carrying S makes prefill(T1) + prefill(T2) equal one prefill of the
     attention stage (the LSF decay stays per call, so the comparison is at the attention module)."""
