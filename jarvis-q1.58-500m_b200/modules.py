@@ -22,6 +22,18 @@ from . import ops
 # ----------------------------------------------------------------------------------------------
 
 
+def _f32(p: torch.Tensor, scalar: bool = False) -> torch.Tensor:
+    """`p.detach().float().contiguous()` (reshaped to (1,) for scalars), cached on the parameter until it changes
+    (in-place update or new storage): the views cost a few microseconds each, several times per layer."""
+    key = (p.data_ptr(), p._version, scalar)
+    c = getattr(p, "_jb_f32", None)
+    if c is None or c[0] != key:
+        t = p.detach().float().contiguous()
+        c = (key, t.reshape(1) if scalar else t)
+        p._jb_f32 = c
+    return c[1]
+
+
 class RMSNorm(nn.Module):
     """jarvis_engine/jarvis_model.py:19-26."""
 
@@ -282,7 +294,7 @@ class SparseMoELayer(nn.Module):
             hist = torch.zeros(E, dtype=torch.int32, device=dev)
         # norm=(weight, eps): `xn_rows` is the un-normalised f32 residual stream and RMSNorm is fused into
         # the router kernel (one pass over the row, routing bit-identical to the separate kernels)
-        w_r = self.router.weight.detach().float().contiguous()
+        w_r = _f32(self.router.weight)
         ep = self._ep
         in_slab = False
         if norm is not None and C <= 1024:
@@ -354,7 +366,7 @@ class LiquidStateFusion(nn.Module):
         m = x.contiguous()
         if m.dtype not in (torch.float32, torch.bfloat16):
             m = m.float()
-        out, last = ops.lsf_scan(m, act_var=act_var, var_scale=self.var_scale.detach().float().reshape(1),
+        out, last = ops.lsf_scan(m, act_var=act_var, var_scale=_f32(self.var_scale, scalar=True),
                                  alpha_min=self.alpha_min, alpha_max=self.alpha_max, h0=h0)
         return out.to(x.dtype), last.to(x.dtype)
 
@@ -427,11 +439,11 @@ class JarvisBlock(nn.Module):
         [l_balance, act_mean, act_var], attention state or None).  cp (parallel.ContextParallel): this rank
         holds one T-token slice of every sequence; states returned are those after the whole sequence."""
         C = x.shape[1]
-        xn = ops.rmsnorm(x, self.norm1.weight.detach().float(), self.norm1.eps)
+        xn = ops.rmsnorm(x, _f32(self.norm1.weight), self.norm1.eps)
         o, state = self.attn.scan_rows(xn, B, T, start_pos, attn_state, want_attn_state, inplace_state, cp=cp)
         po, ao = self.attn.out_proj.packed()
         ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)          # x += attn(norm1(x))
-        norm2 = (self.norm2.weight.detach().float(), self.norm2.eps)
+        norm2 = (_f32(self.norm2.weight), self.norm2.eps)
         if scratch is None:
             moe_out, scalars = self.moe.run_rows(x, norm=norm2)
         else:
@@ -443,16 +455,16 @@ class JarvisBlock(nn.Module):
             alpha = lq.alpha_min + (lq.alpha_max - lq.alpha_min) * torch.sigmoid(-lq.var_scale.detach().float() * scalars[2])
 
             def scan(h_in):
-                ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=lq.var_scale.detach().float().reshape(1),
+                ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=_f32(lq.var_scale, scalar=True),
                              alpha_min=lq.alpha_min, alpha_max=lq.alpha_max, h0=h_in.contiguous(),
                              resid=x.view(B, T, C), want_out=False)
             # the slice's end value from a zero carry: the scan kernel asked for its last value only (reads m once)
-            _, end = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=lq.var_scale.detach().float().reshape(1),
+            _, end = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3], var_scale=_f32(lq.var_scale, scalar=True),
                                   alpha_min=lq.alpha_min, alpha_max=lq.alpha_max, want_out=False)
             _, h_last = cp.lsf(scan, end, alpha, T, None if h_prev is None else h_prev.float())
             return h_last, scalars, state
         _, h_last = ops.lsf_scan(moe_out.view(B, T, C), act_var=scalars[2:3],
-                                 var_scale=self.liquid.var_scale.detach().float().reshape(1),
+                                 var_scale=_f32(self.liquid.var_scale, scalar=True),
                                  alpha_min=self.liquid.alpha_min, alpha_max=self.liquid.alpha_max,
                                  h0=None if h_prev is None else h_prev.float().contiguous(),
                                  resid=x.view(B, T, C), want_out=False,
@@ -472,11 +484,11 @@ class JarvisBlock(nn.Module):
         ops.ternary_linear(o, po, ao, epilogue=ops.EPI_RESID_F32, out=x, prepared=True)
         acc, hist, scalars = scratch
         moe, lq = self.moe, self.liquid
-        moe_out, n_total = moe.run_rows(x, acc=acc, hist=hist, norm=(self.norm2.weight.detach().float(), self.norm2.eps),
+        moe_out, n_total = moe.run_rows(x, acc=acc, hist=hist, norm=(_f32(self.norm2.weight), self.norm2.eps),
                                         finalize=False)
         xn_next, h_last = ops.lsf_step_norm(
             moe_out, acc[:2], acc[2:], hist, moe.num_experts, n_total, n_total * C, moe.balance_alpha, scalars,
-            lq.var_scale.detach().float().reshape(1), lq.alpha_min, lq.alpha_max,
+            _f32(lq.var_scale, scalar=True), lq.alpha_min, lq.alpha_max,
             None if h_prev is None else h_prev.float().contiguous(), x, norm=next_norm,
             h_out=h_prev if (inplace_state and h_prev is not None and h_prev.dtype == torch.float32) else None)
         return h_last, scalars, state, xn_next
@@ -558,7 +570,7 @@ class Jarvis(nn.Module):
         if self.training:
             raise RuntimeError("Jarvis (sm_100a): inference only; call .eval() first")
         B, T = idx.shape
-        x = ops.embedding(idx.contiguous(), self.tok_emb.weight.detach().float()).view(B * T, self.d_model)
+        x = ops.embedding(idx.contiguous(), _f32(self.tok_emb.weight)).view(B * T, self.d_model)
         start_pos = self._token_pos if persist_state else 0
         if persist_state:
             self._token_pos += T * (self._cp.world if self._cp is not None else 1)
@@ -585,7 +597,7 @@ class Jarvis(nn.Module):
         self._h_states = new_h
         self._attn_states = new_s
         self.last_aux = aux
-        return ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
+        return ops.rmsnorm(x, _f32(self.final_norm.weight), self.final_norm.eps)
 
     @torch.no_grad()
     def step(self, idx, positions=None, state=None, max_position=None, inplace=False):
@@ -598,7 +610,7 @@ class Jarvis(nn.Module):
             raise RuntimeError("Jarvis (sm_100a): inference only; call .eval() first")
         B, T = idx.shape
         n = len(self.blocks)
-        x = ops.embedding(idx.contiguous(), self.tok_emb.weight.detach().float()).view(B * T, self.d_model)
+        x = ops.embedding(idx.contiguous(), _f32(self.tok_emb.weight)).view(B * T, self.d_model)
         pos = 0 if positions is None else positions
         hs = state["h"] if state is not None else [None] * n
         Ss = state["S"] if state is not None else [None] * n
@@ -607,11 +619,11 @@ class Jarvis(nn.Module):
         if T == 1 and self.d_model <= 1024 and self.d_model % 8 == 0:
             # decode: every block's tail (MoE scalars + LSF step + the norm that follows) is one launch
             norms = [b.norm1 for b in self.blocks[1:]] + [self.final_norm]
-            xn = ops.rmsnorm(x, self.blocks[0].norm1.weight.detach().float(), self.blocks[0].norm1.eps)
+            xn = ops.rmsnorm(x, _f32(self.blocks[0].norm1.weight), self.blocks[0].norm1.eps)
             for i, block in enumerate(self.blocks):
                 block.attn.max_position = max_position
                 h_last, _, S, xn = block.step_rows(x, xn, B, hs[i], pos, Ss[i], inplace and state is not None, scratch[i],
-                                                   (norms[i].weight.detach().float(), norms[i].eps))
+                                                   (_f32(norms[i].weight), norms[i].eps))
                 new_h.append(h_last)
                 new_s.append(S)
             hidden = xn
@@ -622,7 +634,7 @@ class Jarvis(nn.Module):
                                                   inplace_state=inplace and state is not None, scratch=scratch[i])
                 new_h.append(h_last)
                 new_s.append(S)
-            hidden = ops.rmsnorm(x, self.final_norm.weight.detach().float(), self.final_norm.eps)
+            hidden = ops.rmsnorm(x, _f32(self.final_norm.weight), self.final_norm.eps)
         vocab = self.lm_head.weight.shape[0]
         logits = ops.dense_linear(hidden, self._lm_head_weight()).view(B, T, -1)[..., :vocab]
         return logits, {"h": new_h, "S": new_s}

@@ -22,6 +22,11 @@ import torch
 import torch.distributed as dist
 
 
+def ops_stream() -> int:
+    from . import ops
+    return ops._stream()
+
+
 def owner_plan(world: int, num_experts: int):
     """-> (rounds, plan) with plan[round][dst_rank] = (expert, part, nparts): which slice of which
     expert's rows a source sends to `dst_rank` in that all-to-all round."""
@@ -320,7 +325,7 @@ class PeerExchange:
         visible to the peers) before any rank's later kernels start.  Flags in the peer-mapped slabs
         (jb200_peer_barrier), not a collective of the communication library: a few microseconds."""
         self._lib.check(self._lib.load().jb200_peer_barrier(self.ptrs["flags"].data_ptr(), self.world, self.rank,
-                                                           torch.cuda.current_stream().cuda_stream), "jb200_peer_barrier")
+                                                           ops_stream()), "jb200_peer_barrier")
 
     def close(self):
         """Unmap the peers' slabs and free this rank's (call on every rank before the process group goes away)."""
@@ -391,7 +396,7 @@ class PeerExpertParallelMoE:
         N = idx.shape[0]
         if N > ex.n_max:
             raise RuntimeError(f"PeerExpertParallelMoE: {N} tokens exceed max_tokens={ex.n_max}")
-        stream = torch.cuda.current_stream().cuda_stream
+        stream = ops_stream()
         if not x_in_slab:
             ex.xn[:N].copy_(x)
         if not meta_in_slab:
