@@ -159,7 +159,7 @@ def test_dependent_launch_on_and_off_give_the_same_results():
               "S": [torch.randn(B, 2, 64, 64, generator=gen, device="cuda") for _ in range(3)]}
     toks = torch.randint(0, 256, (4, B, 1), generator=gen, device="cuda")
     results = {}
-    assert _lib.set_dependent_launch(True) is True          # on by default
+    before = _lib.set_dependent_launch(True)                # on unless JB200_DEPENDENT_LAUNCH=0 started the process
     try:
         for on in (False, True):
             _lib.set_dependent_launch(on)
@@ -177,7 +177,7 @@ def test_dependent_launch_on_and_off_give_the_same_results():
             torch.cuda.synchronize()
             results[on] = (logits, steps, graph_steps, [t.clone() for t in st["S"]])
     finally:
-        _lib.set_dependent_launch(True)
+        _lib.set_dependent_launch(before)
     assert _lib.device_status() == 0
     off, on = results[False], results[True]
     assert rel_l2(on[0], off[0]) < 1e-5
