@@ -461,6 +461,44 @@ def multi_gpu_records(model, device, rank, world, barrier):
         model.set_context_parallel(None)
         out["cp"] = {"error": f"{type(exc).__name__}: {exc}"}
 
+    # ---- ragged state-carrying decode: 256 sequences, one token per step, sequences data parallel ----------------
+    # Every rank keeps 256 / world sequences with their carried states (attention state (H, 64, 64) f32 and LSF
+    # membrane per layer, prior lengths ~ U[1, 4096]); the step is one CUDA graph per rank, the per-layer all-reduce
+    # of the MoE statistics inside it keeps the LSF decay that of the whole batch of 256.
+    try:
+        Bd = 256
+        if Bd % world:
+            raise ValueError(f"world size {world} does not divide {Bd} sequences")
+        H, Cm, L = CFG["n_heads"], CFG["d_model"], len(model.blocks)
+
+        def decode_ms(n_seq, seed, split):
+            g = torch.Generator(device=device).manual_seed(seed)
+            pos = torch.randint(1, 4097, (n_seq,), generator=g, device=device, dtype=torch.int32)
+            state = {"h": [torch.randn(n_seq, Cm, generator=g, device=device) for _ in range(L)],
+                     "S": [torch.randn(n_seq, H, 64, 64, generator=g, device=device) for _ in range(L)]}
+            toks = torch.randint(0, CFG["vocab"], (4, n_seq, 1), generator=g, device=device)
+            model.set_batch_split(dist.group.WORLD if split else None, global_tokens=Bd if split else None)
+            sess = jm.DecodeSession(model, state, pos, max_position=4096 + 64).capture()
+            for i in range(2):
+                sess.step(toks[i])
+            n = 16
+            ms = _max_over_ranks([_time_steps(lambda: sess.step(toks[0]), n, barrier)], device, world)[0] / n
+            model.set_batch_split(None)
+            del sess, state
+            torch.cuda.empty_cache()
+            return ms
+
+        ms = decode_ms(Bd // world, 900 + rank, True)
+        ms_one = decode_ms(Bd, 900, False)        # one GPU holding all 256 sequences, timed on every rank at once
+        out["decode"] = {"workload": "606M model, 256 sequences x 1 token per step, carried f32 state, ragged positions, "
+                                     "sequences split over the ranks (CUDA-graphed step, per-layer NCCL all-reduce of the "
+                                     "MoE statistics inside the graph)",
+                         "ms_per_step": ms, "tok_per_s": Bd / (ms * 1e-3), "sequences_per_gpu": Bd // world,
+                         "ms_per_step_one_gpu": ms_one, "speedup_vs_one_gpu": ms_one / ms}
+    except Exception as exc:  # noqa: BLE001
+        model.set_batch_split(None)
+        out["decode"] = {"error": f"{type(exc).__name__}: {exc}"}
+
     # ---- strong scaling again, the split forward captured in a CUDA graph (last: a failed capture ends the records) --
     # From Python the ~340 launches of a forward cost several ms of host time, which a 14 ms step hides and a split
     # batch does not; a replay is one launch (the per-layer NCCL all-reduce is captured with it).
