@@ -136,3 +136,28 @@ def test_read_tbin_container_written_by_the_reference():
             ck.read_tbin(bad)
         finally:
             os.remove(bad)
+
+
+def test_cached_parameter_views_follow_in_place_updates_and_new_storage():
+    """modules._f32 keeps `p.detach().float()` on the parameter until the parameter changes."""
+    import torch
+    from jarvis_b200 import modules as jm
+    p = torch.nn.Parameter(torch.arange(6, dtype=torch.float32).reshape(2, 3))
+    a = jm._f32(p)
+    assert a is jm._f32(p) and a.data_ptr() == p.data_ptr() and not a.requires_grad
+    with torch.no_grad():
+        p.mul_(2.0)
+    b = jm._f32(p)
+    assert torch.equal(b, p.detach())
+    p.data = torch.ones(2, 3)
+    c = jm._f32(p)
+    assert c is not b and torch.equal(c, torch.ones(2, 3))
+    h = torch.nn.Parameter(torch.tensor([1.5, 2.5], dtype=torch.bfloat16))       # a host model kept in bf16
+    f = jm._f32(h)
+    assert f.dtype == torch.float32 and torch.equal(f, torch.tensor([1.5, 2.5]))
+    with torch.no_grad():
+        h.add_(1.0)
+    assert torch.equal(jm._f32(h), torch.tensor([2.5, 3.5]))
+    s = torch.nn.Parameter(torch.tensor(0.75))
+    assert tuple(jm._f32(s, scalar=True).shape) == (1,)
+
